@@ -1,0 +1,79 @@
+"""ctypes loader of ``libb200eagle.so``.
+
+There is no fallback: if the library has not been built (``python -m`` of
+``build.py`` in this directory, or ``__graft_entry__.build()``), importing an
+operator raises.  All tensors handed to the library are CUDA tensors owned by
+torch; the library only sees raw device pointers and the current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200eagle.so")
+
+E_NAMES = {-1: "EINVAL (bad shape/size/flags)", -2: "EALIGN (pointer not 16-byte aligned)",
+           -3: "EUNSUPPORTED (dtype/group size)", -4: "EWORKSPACE (workspace too small)",
+           -5: "ECUDA (CUDA runtime error)", -6: "ELIMIT (size beyond a fixed maximum)"}
+
+_lib = None
+
+
+class B200Error(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise B200Error(
+                f"{LIB_PATH} is missing: build it first (python {os.path.join(_HERE, 'build.py')}). "
+                "There is no CPU or PyTorch fallback for this path.")
+        _lib = ctypes.CDLL(LIB_PATH)
+        _declare(_lib)
+    return _lib
+
+
+def _declare(l: ctypes.CDLL) -> None:
+    vp, i32, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+    l.b200_version.restype = i32
+    l.b200_last_cuda_error.restype = i32
+    l.b200_qmm_workspace_bytes.restype = sz
+    l.b200_qmm_workspace_bytes.argtypes = [i32, i32, i32]
+    l.b200_qmm.restype = i32
+    l.b200_qmm.argtypes = [vp] * 6 + [i32] * 5 + [vp, sz, vp]
+    l.b200_qmm_fused.restype = i32
+    l.b200_qmm_fused.argtypes = [vp] * 10 + [i32] * 6 + [vp, sz, vp]
+    for name, sig in _EXTRA_SIGNATURES.items():
+        fn = getattr(l, name)
+        fn.restype, fn.argtypes = sig
+
+
+# name -> (restype, argtypes); filled by the operator modules before the first lib() call.
+_EXTRA_SIGNATURES: dict = {}
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        extra = ""
+        if rc == -5:
+            extra = f" (cudaError {lib().b200_last_cuda_error()})"
+        raise B200Error(f"{what} failed: {E_NAMES.get(rc, rc)}{extra}")
+
+
+def ptr(t: torch.Tensor | None):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def stream_ptr(device=None):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise B200Error("this operator only runs on CUDA tensors (no CPU path is provided)")
