@@ -77,6 +77,94 @@ int b200_qmm_fused(const void* x, const uint32_t* wq, const void* scales, const 
                    int group_size, int dtype, int epilogue,
                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Per-token model kernels (one decoder layer = rms_norm, qmm(+bias), rope_kv_append,
+ * tree_attention, qmm(residual), rms_norm, qmm(silu-mul), qmm(residual)).
+ * ------------------------------------------------------------------------------------------ */
+
+/* Quantised embedding lookup, h[m,:] = dequant(E[tokens[m],:]).  Replaces `self.embed_tokens(inputs)`
+ * (mlx_llama.py:273) on a 4-bit nn.QuantizedEmbedding.  out [M,H] fp16; H % 64 == 0. */
+int b200_embed_gather(const int* tokens, const uint32_t* wq, const void* scales, const void* biases,
+                      void* out, int M, int H, int V, void* stream);
+
+/* RMSNorm, y = fp16((x * rsqrt(mean(x^2)+eps)) * w) with fp32 math.  Replaces nn.RMSNorm /
+ * mx.fast.rms_norm (mlx_llama.py:225-228,240,247,263,286).  If row_index != NULL (device int),
+ * output row i is computed from input row row_index[0] + i (used to pick the catch-up pass row,
+ * mlx_eagle.py:404,408). */
+int b200_rms_norm(const void* x, const void* w, void* y, const int* row_index, int M, int H, float eps,
+                  void* stream);
+
+/* Tree-position RoPE fused with the KV-cache append.  qkv [M,(Hq+2Hkv)*hd] fp16 holds q|k|v of M
+ * tokens; q is rotated in place, k rotated and v copied into cache row prefix[0]+write_off+m of
+ * kcache / vcache ([Hkv][cache_rows][hd] fp16 each).  pos[m] is the rotary position of token m.
+ * Replaces the two rope_positions calls (mlx_llama.py:150-161), the flat_rope path (:141-143,
+ * 162-176) and cache.update_and_fetch (:178). */
+int b200_rope_kv_append(void* qkv, const int* pos, const float* inv_freq, float scaling, void* kcache,
+                        void* vcache, const int* prefix, int write_off, int M, int Hq, int Hkv, int hd,
+                        int cache_rows, void* stream);
+
+/* Stand-alone RoPE with per-(batch, token) integer positions, tensors laid out (B,H,L,D) fp16,
+ * offsets (B,L) int32, inv_freqs (D/2) fp32.  Replaces mlx_arrayed_rope_kernel.py:46-152
+ * `rope_positions(inp, offsets, inv_freqs, scaling_factor)` (non-traditional layout, forward). */
+int b200_rope_positions(const void* in, const int* offsets, const float* inv_freqs, float scaling_factor,
+                        void* out, int B, int H, int L, int D, void* stream);
+
+/* Tree-masked attention of M <= 32 query tokens, GQA.  Query m sees every cache row < prefix[0]
+ * and cache row prefix[0]+j (j < tail <= 64) iff bit j of mask[m] is set; the new tokens' K/V
+ * must already be in the cache.  q points at the rotated queries (token stride q_stride halves),
+ * out is [M,Hq*hd] fp16.  max_kv bounds prefix+tail over the lifetime of the workspace (it sizes the
+ * grid, so one launch shape serves a growing cache); workspace from
+ * b200_tree_attention_workspace_bytes, first 256 bytes zero before first use.  hd in {64,128}.
+ * Replaces mx.fast.scaled_dot_product_attention with the additive tree mask
+ * (mlx_llama.py:185-192; masks built at mlx_eagle.py:143-146,171,207,336-338). */
+size_t b200_tree_attention_workspace_bytes(int M, int Hq, int Hkv, int hd, int max_kv);
+int b200_tree_attention(const void* q, int q_stride, const void* kcache, const void* vcache,
+                        const unsigned long long* mask, const int* prefix, int tail, void* out,
+                        int M, int Hq, int Hkv, int hd, int cache_rows, int max_kv, float scale,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Draft tree, acceptance and compaction.  One request; k = 8 children per node.
+ * ctl is int32[16]: [0] committed length of the target cache, [1] of the draft cache, [2] accept
+ * length of the previous step, [3] tokens generated, [4] step, [5] draft cache length after the
+ * catch-up pass, [6] capacity of out_tokens, [7] best path of the last step.
+ * Ordering keys: (order-preserving image of the fp32 value) << 32 | (0xffffffff - index).
+ * ------------------------------------------------------------------------------------------ */
+int b200_topk_blocks(int V);
+int b200_logits_rowstats(const void* logits, int R, int V, uint32_t* row_max, unsigned long long* row_sum,
+                         void* stream);
+int b200_logits_topk_candidates(const void* logits, int R, int V, const uint32_t* row_max,
+                                const unsigned long long* row_sum, int by_score,
+                                unsigned long long* cand, void* stream);
+/* Root expansion (level < 0; mlx_eagle.py:410-412) or one tree level (level = i >= 0;
+ * process_generate_tree_iteration, mlx_eagle.py:97-115, plus the per-level bookkeeping of
+ * generate_draft_tree, :157-207).  Writes the candidate pool and the inputs (tokens, positions,
+ * tail masks, prefix) of the next draft forward. */
+int b200_tree_expand(const void* logits, int V, int level, const unsigned long long* cand, uint32_t* row_max,
+                     unsigned long long* row_sum, int* ctl, float* pool_scores, int* pool_tokens,
+                     uint32_t* pool_parents, float* cur_scores, uint32_t* topk_cs_index, int* fwd_tokens,
+                     int* fwd_pos, unsigned long long* fwd_mask, int* fwd_prefix, void* stream);
+/* Inputs of the draft catch-up pass: y padded to 8 tokens (mlx_eagle.py:400-408). */
+int b200_prep_catchup(const int* ctl, const int* y, int* fwd_tokens, int* fwd_pos, unsigned long long* fwd_mask,
+                      int* fwd_prefix, int* sel_row, void* stream);
+/* process_draft_tree + search_sorted + post_process_draft_tree (mlx_eagle.py:61-93,217-295): stable
+ * top-T of the pool, parents, ancestor masks, depths, verify inputs, root-to-leaf paths
+ * (retrieve is [T][9] int32, -1 padded; tree_info[0] = leaves, [1] = max depth + 1). */
+int b200_tree_finalize(int depth, int T, const float* pool_scores, const int* pool_tokens,
+                       const uint32_t* pool_parents, const int* ctl, const int* y, int* fwd_tokens,
+                       int* fwd_pos, unsigned long long* fwd_mask, int* fwd_prefix, int* tree_position_ids,
+                       int* mask_index, int* draft_tokens, int* retrieve, int* tree_info, void* stream);
+int b200_logits_argmax(const void* logits, int R, int V, unsigned long long* best_key, void* stream);
+/* evaluate_posterior_greedy (mlx_eagle.py:311-326) on per-node argmaxes, plus the loop bookkeeping of
+ * generate_step (:587-599): next y, accept length, lengths of both caches, generated-token log.
+ * accept_rows[0] = accept length, [1..] = accepted node indices (retrieve_indices[best, 1:1+a]). */
+int b200_tree_accept(int T, unsigned long long* argmax_key, const int* draft_tokens, const int* retrieve,
+                     const int* tree_info, int* ctl, int* y, int* accept_rows, int* out_tokens,
+                     int* step_log, void* stream);
+/* accept_candidate (mlx_eagle.py:349-376) over all layers; cache is [layers][2][Hkv][cache_rows][hd]. */
+int b200_kv_compact(void* cache, int layers, int Hkv, int cache_rows, int hd, const int* accept_rows,
+                    const int* ctl, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

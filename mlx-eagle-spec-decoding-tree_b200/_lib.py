@@ -48,13 +48,37 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_qmm.argtypes = [vp] * 6 + [i32] * 5 + [vp, sz, vp]
     l.b200_qmm_fused.restype = i32
     l.b200_qmm_fused.argtypes = [vp] * 10 + [i32] * 6 + [vp, sz, vp]
-    for name, sig in _EXTRA_SIGNATURES.items():
-        fn = getattr(l, name)
-        fn.restype, fn.argtypes = sig
-
-
-# name -> (restype, argtypes); filled by the operator modules before the first lib() call.
-_EXTRA_SIGNATURES: dict = {}
+    f32, u64 = ctypes.c_float, ctypes.c_ulonglong
+    l.b200_embed_gather.restype = i32
+    l.b200_embed_gather.argtypes = [vp] * 5 + [i32] * 3 + [vp]
+    l.b200_rms_norm.restype = i32
+    l.b200_rms_norm.argtypes = [vp] * 4 + [i32, i32, f32, vp]
+    l.b200_rope_kv_append.restype = i32
+    l.b200_rope_kv_append.argtypes = [vp, vp, vp, f32, vp, vp, vp] + [i32] * 6 + [vp]
+    l.b200_rope_positions.restype = i32
+    l.b200_rope_positions.argtypes = [vp, vp, vp, f32, vp] + [i32] * 4 + [vp]
+    l.b200_tree_attention_workspace_bytes.restype = sz
+    l.b200_tree_attention_workspace_bytes.argtypes = [i32] * 5
+    l.b200_tree_attention.restype = i32
+    l.b200_tree_attention.argtypes = [vp, i32, vp, vp, vp, vp, i32, vp] + [i32] * 6 + [f32, vp, sz, vp]
+    l.b200_topk_blocks.restype = i32
+    l.b200_topk_blocks.argtypes = [i32]
+    l.b200_logits_rowstats.restype = i32
+    l.b200_logits_rowstats.argtypes = [vp, i32, i32, vp, vp, vp]
+    l.b200_logits_topk_candidates.restype = i32
+    l.b200_logits_topk_candidates.argtypes = [vp, i32, i32, vp, vp, i32, vp, vp]
+    l.b200_tree_expand.restype = i32
+    l.b200_tree_expand.argtypes = [vp, i32, i32] + [vp] * 14
+    l.b200_prep_catchup.restype = i32
+    l.b200_prep_catchup.argtypes = [vp] * 8
+    l.b200_tree_finalize.restype = i32
+    l.b200_tree_finalize.argtypes = [i32, i32] + [vp] * 15
+    l.b200_logits_argmax.restype = i32
+    l.b200_logits_argmax.argtypes = [vp, i32, i32, vp, vp]
+    l.b200_tree_accept.restype = i32
+    l.b200_tree_accept.argtypes = [i32] + [vp] * 10
+    l.b200_kv_compact.restype = i32
+    l.b200_kv_compact.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp]
 
 
 def check(rc: int, what: str) -> None:

@@ -1,0 +1,362 @@
+"""EAGLE-2-style tree speculative decoding loop, greedy, one request per GPU.
+
+Keeps the generate-loop API of the reference's ``mlx_eagle.py`` (``generate_step``,
+``spec_step``, ``tree_decoding``, ``post_process_draft_tree``,
+``evaluate_posterior_greedy``, ``accept_candidate``, the CLI flags), but one
+decode step is a fixed sequence of kernel launches whose every data-dependent
+quantity (cache lengths, accept length, tree shape, tokens) lives in device
+memory: the host never waits for the device inside a step, and the whole step is
+replayed as one CUDA graph.
+
+Step (``mlx_eagle.py:379-463`` then ``:576-599``):
+  catch-up pass of the draft on the last accepted tokens (always padded to 8 rows)
+  -> root expansion -> ``depth`` draft passes of 8 tokens, each followed by one
+  tree level -> selection of the ``verify_num_tokens`` best nodes, ancestor masks,
+  depths, root-to-leaf paths -> one target pass on the tree -> per-node argmax ->
+  longest accepted path -> KV compaction of the target cache, both cache lengths,
+  next input tokens.
+"""
+from __future__ import annotations
+
+import argparse
+import time
+from typing import List, Optional
+
+import torch
+
+from . import _lib
+from .llama import KVCache, Model, ModelArgs, MAX_ROWS, shape_preset
+
+K = 8                      # children per node (mlx_eagle.py:750)
+RETRIEVE_W = 9             # row width of the retrieve-index matrix (max depth 7 + 2)
+CTL_BASE_LEN, CTL_DRAFT_LEN, CTL_ACCEPT, CTL_NGEN, CTL_STEP, CTL_DRAFT_OFF, CTL_OUT_CAP, CTL_BEST = range(8)
+
+
+class SpecDecoder:
+    """Device-resident state and launch sequence of the speculative decoding loop."""
+
+    def __init__(self, base_model: Model, draft_model: Model, depth: int, verify_num_tokens: int,
+                 cache_rows: int, max_out_tokens: int = 4096, max_steps: int = 4096, k: int = K):
+        if k != K:
+            raise _lib.B200Error("k is fixed to 8, as in the reference (mlx_eagle.py:750)")
+        if not (0 <= depth <= 6):
+            raise _lib.B200Error("depth must be in 0..6 (accepted tokens + 1 must fit the 8-row catch-up pass)")
+        T = verify_num_tokens
+        if not (1 <= T <= 31) or T > K + K * K * depth:
+            raise _lib.B200Error("verify_num_tokens must be <= 31 and <= pool size (README: 7, 15, 23 or 31)")
+        self.base, self.draft = base_model, draft_model
+        self.depth, self.T = depth, T
+        dev = base_model.device
+        self.device = dev
+        self.base_cache = base_model.make_cache(cache_rows)
+        self.draft_cache = draft_model.make_cache(cache_rows)
+        i32 = dict(dtype=torch.int32, device=dev)
+        i64 = dict(dtype=torch.int64, device=dev)
+        pool = K + K * K * max(depth, 1)
+        self.ctl = torch.zeros(16, **i32)
+        self.y = torch.zeros(K, **i32)
+        self.sel_row = torch.zeros(1, **i32)
+        self.pool_scores = torch.zeros(pool, dtype=torch.float32, device=dev)
+        self.pool_tokens = torch.zeros(pool, **i32)
+        self.pool_parents = torch.zeros(64, **i32)
+        self.cur_scores = torch.zeros(K, dtype=torch.float32, device=dev)
+        self.topk_cs_index = torch.zeros(K, **i32)
+        self.row_max = torch.zeros(MAX_ROWS, **i32)
+        self.row_sum = torch.zeros(MAX_ROWS, **i64)
+        nblk = _lib.lib().b200_topk_blocks(draft_model.args.vocab_size)
+        self.cand = torch.zeros(K * nblk * K, **i64)
+        self.argmax_key = torch.zeros(MAX_ROWS, **i64)
+        self.tree_position_ids = torch.zeros(MAX_ROWS, **i32)
+        self.mask_index = torch.zeros(MAX_ROWS, **i32)
+        self.draft_tokens = torch.zeros(MAX_ROWS, **i32)
+        self.retrieve = torch.full((MAX_ROWS * RETRIEVE_W,), -1, **i32)
+        self.tree_info = torch.zeros(2, **i32)
+        self.accept_rows = torch.zeros(16, **i32)
+        self.out_tokens = torch.zeros(max_out_tokens, **i32)
+        self.step_log = torch.zeros(2 * max_steps, **i32)
+        self.max_steps = max_steps
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.base_logits = None
+        self.kernel_launches_per_step = (
+            (depth + 1) * draft_model.launches_per_forward + base_model.launches_per_forward
+            + 1 + (depth + 1) * 4 + 1 + 1 + 1 + 1)
+
+    # ------------------------------------------------------------------ prompt ingestion
+    def prefill(self, prompt: torch.Tensor, prefill_step_size: int = 512) -> int:
+        """Feed the prompt to both models (``mlx_eagle.py:522-535``) and take the first token greedily."""
+        prompt = prompt.reshape(-1).to(torch.int32).to(self.device)
+        n = prompt.numel()
+        need = n + 8 * (self.depth + 1) + 40
+        if need > self.base_cache.rows:
+            raise _lib.B200Error(f"cache of {self.base_cache.rows} rows cannot hold a {n}-token prompt")
+        self.base_cache.offset = 0
+        self.draft_cache.offset = 0
+        self.draft(prompt[None], cache=self.draft_cache, logits_last_only=True)
+        logits = self.base(prompt[None], cache=self.base_cache, logits_last_only=True)
+        first = int(torch.argmax(logits[0, -1].float()).item())
+        self.ctl.zero_()
+        host = torch.zeros(16, dtype=torch.int32)
+        host[CTL_BASE_LEN] = n
+        host[CTL_DRAFT_LEN] = n
+        host[CTL_OUT_CAP] = self.out_tokens.numel()
+        self.ctl.copy_(host)
+        self.y.zero_()
+        self.y[0] = first
+        self.step_log.zero_()
+        self.out_tokens.zero_()
+        self.row_max.zero_()
+        self.row_sum.zero_()
+        self.argmax_key.zero_()
+        return first
+
+    # ------------------------------------------------------------------ one step, device only
+    def _draft_tree(self):
+        L, p, ck = _lib.lib(), _lib.ptr, _lib.check
+        st = _lib.stream_ptr(self.device)
+        d, f = self.draft, self.draft.fwd
+        V = d.args.vocab_size
+        ck(L.b200_prep_catchup(p(self.ctl), p(self.y), p(f.tokens), p(f.pos), p(f.mask), p(f.prefix),
+                               p(self.sel_row), st), "b200_prep_catchup")
+        logits = d.forward_device(K, self.draft_cache, 0, K, logits_rows=1, row_index=self.sel_row)
+        self._expand(logits, 1, V, -1, st)
+        for i in range(self.depth):
+            logits = d.forward_device(K, self.draft_cache, K * i, K * (i + 1))
+            self._expand(logits, K, V, i, st)
+
+    def _expand(self, logits, R, V, level, st):
+        L, p, ck = _lib.lib(), _lib.ptr, _lib.check
+        f = self.draft.fwd
+        ck(L.b200_logits_rowstats(p(logits), R, V, p(self.row_max), p(self.row_sum), st), "b200_logits_rowstats")
+        ck(L.b200_logits_topk_candidates(p(logits), R, V, p(self.row_max), p(self.row_sum),
+                                         0 if level < 0 else 1, p(self.cand), st), "b200_logits_topk_candidates")
+        ck(L.b200_tree_expand(p(logits), V, level, p(self.cand), p(self.row_max), p(self.row_sum), p(self.ctl),
+                              p(self.pool_scores), p(self.pool_tokens), p(self.pool_parents), p(self.cur_scores),
+                              p(self.topk_cs_index), p(f.tokens), p(f.pos), p(f.mask), p(f.prefix), st),
+           "b200_tree_expand")
+
+    def _finalize_and_verify(self):
+        L, p, ck = _lib.lib(), _lib.ptr, _lib.check
+        st = _lib.stream_ptr(self.device)
+        f = self.base.fwd
+        ck(L.b200_tree_finalize(self.depth, self.T, p(self.pool_scores), p(self.pool_tokens), p(self.pool_parents),
+                                p(self.ctl), p(self.y), p(f.tokens), p(f.pos), p(f.mask), p(f.prefix),
+                                p(self.tree_position_ids), p(self.mask_index), p(self.draft_tokens),
+                                p(self.retrieve), p(self.tree_info), st), "b200_tree_finalize")
+        self.base_logits = self.base.forward_device(self.T + 1, self.base_cache, 0, self.T + 1)
+        return self.base_logits
+
+    def _accept(self):
+        L, p, ck = _lib.lib(), _lib.ptr, _lib.check
+        st = _lib.stream_ptr(self.device)
+        a = self.base.args
+        ck(L.b200_logits_argmax(p(self.base_logits), self.T + 1, a.vocab_size, p(self.argmax_key), st),
+           "b200_logits_argmax")
+        ck(L.b200_tree_accept(self.T, p(self.argmax_key), p(self.draft_tokens), p(self.retrieve), p(self.tree_info),
+                              p(self.ctl), p(self.y), p(self.accept_rows), p(self.out_tokens), p(self.step_log), st),
+           "b200_tree_accept")
+        ck(L.b200_kv_compact(p(self.base_cache.data), a.num_hidden_layers, a.num_key_value_heads,
+                             self.base_cache.rows, a.head_dim, p(self.accept_rows), p(self.ctl), st),
+           "b200_kv_compact")
+
+    def step(self):
+        """Launch one whole speculative step (no host synchronisation)."""
+        self._draft_tree()
+        self._finalize_and_verify()
+        self._accept()
+
+    def capture(self):
+        """Record ``step`` into a CUDA graph (after at least one eager step, which also sets the
+        kernels' shared-memory attributes).  Shapes are static; lengths are read on the device."""
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.step()
+        self.graph = g
+        return g
+
+    def replay(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step()
+
+    # ------------------------------------------------------------------ host views
+    def read_ctl(self) -> List[int]:
+        return self.ctl.cpu().tolist()
+
+    def sync_offsets(self):
+        c = self.read_ctl()
+        self.base_cache.offset = c[CTL_BASE_LEN]
+        self.draft_cache.offset = c[CTL_DRAFT_LEN]
+        return c
+
+
+# ---------------------------------------------------------------------- reference-style functions
+def post_process_draft_tree(tree_position_ids: torch.Tensor, total_tokens: int, mask_index: torch.Tensor) -> torch.Tensor:
+    """Root-to-leaf index paths ``(leaf_num, max_depth)``, -1 padded (``mlx_eagle.py:254-295``).
+
+    Host-side helper for callers that hold the tree on the host; the decode loop gets the same matrix
+    from ``b200_tree_finalize`` without leaving the device."""
+    pos = tree_position_ids.reshape(-1).tolist()
+    mi = mask_index.reshape(-1).tolist()
+    max_depth = max(pos) + 1
+    nonleaf = set(mi)
+    leaf_num = total_tokens - (len(nonleaf) - 1)
+    out = [[-1] * max_depth for _ in range(leaf_num)]
+    rid = 0
+    for i in range(total_tokens + 1):
+        if i not in nonleaf:
+            cid = i
+            for j in range(pos[i], -1, -1):
+                out[rid][j] = cid
+                cid = mi[-1] if cid == 0 else mi[cid - 1]
+            rid += 1
+    return torch.tensor(out, dtype=torch.int32).reshape(leaf_num, max_depth)
+
+
+def tree_decoding(token_ids: torch.Tensor, tree_mask: torch.Tensor, tree_position_ids: torch.Tensor,
+                  base_model: Model, cache: KVCache) -> torch.Tensor:
+    """One target pass over the tree (``mlx_eagle.py:329-346``); ``tree_mask`` is additive 0/-inf
+    or boolean ``(T+1, T+1)``."""
+    offset = cache.offset
+    tm = tree_mask
+    if tm.dtype == torch.bool:
+        tm = torch.where(tm, 0.0, float("-inf"))
+    tm = tm.float().cpu()
+    mask = torch.cat([torch.zeros(tm.shape[0], offset), tm], dim=-1)[None, None]
+    return base_model(token_ids, cache, position_ids=tree_position_ids.reshape(1, -1).cpu() + offset, mask=mask)
+
+
+def evaluate_posterior_greedy(logits: torch.Tensor, candidates: torch.Tensor):
+    """``mlx_eagle.py:311-326``: logits ``(leaf, depth, V)``, candidates ``(leaf, depth)``."""
+    posterior_mask = (candidates[:, 1:] == torch.argmax(logits[:, :-1].float(), dim=-1)).to(torch.int32)
+    lens = torch.cumprod(posterior_mask, dim=1).sum(dim=1)
+    accept_length = lens.max()
+    best = torch.where(accept_length == 0, torch.zeros((), dtype=torch.int64, device=lens.device), torch.argmax(lens))
+    return best, accept_length, logits[best, accept_length]
+
+
+def accept_candidate(cache: KVCache, accept_indices: torch.Tensor, accept_length: int, offset: int):
+    """``mlx_eagle.py:349-376`` on the single-allocation cache."""
+    if accept_length > 0:
+        src = (offset + accept_indices.reshape(-1).to(torch.int64)).to(cache.data.device)
+        rows = cache.data[:, :, :, src].clone()
+        cache.data[:, :, :, offset + 1: offset + accept_length + 1] = rows
+    cache.offset = offset + accept_length + 1
+
+
+def spec_step(dec: SpecDecoder):
+    """Device graph of one step up to the target logits, like ``mlx_eagle.py:379-463``.
+
+    Returns ``(tree_position_ids, mask_index, draft_tokens, base_logits, base_offset, draft_offset)``
+    as device tensors / device scalars (no synchronisation)."""
+    dec._draft_tree()
+    logits = dec._finalize_and_verify()
+    T = dec.T
+    return (dec.tree_position_ids[: T + 1], dec.mask_index[:T], dec.draft_tokens[None, : T + 1], logits[None],
+            dec.ctl[CTL_BASE_LEN], dec.ctl[CTL_DRAFT_OFF])
+
+
+def generate_step(prompt: torch.Tensor, base_model: Model, draft_model: Model, prefill_step_size: int = 512,
+                  k: int = 8, depth: int = 5, verify_num_tokens: int = 31, max_tokens: int = 128, tokenizer=None,
+                  N: int = 20, use_graph: bool = True, verbose: bool = True, return_stats: bool = True):
+    """Greedy tree-speculative generation (``mlx_eagle.py:503-606``).
+
+    Same arguments as the reference (``verify_num_tokens`` is capped at 31 here).  Runs at most ``N``
+    steps and stops at the first step boundary where ``max_tokens`` were generated; the timer starts
+    after prompt ingestion, as in the reference (``:541``).  Returns a dict with the generated tokens
+    (first token from the prompt pass, then each step's accepted tokens + bonus token), the
+    per-step accept lengths, tokens per step and tokens per second.
+    """
+    rows = prompt.numel() + max_tokens + 8 * (depth + 2) + verify_num_tokens + 128
+    rows = ((rows + 63) // 64) * 64
+    dec = SpecDecoder(base_model, draft_model, depth, verify_num_tokens, rows,
+                      max_out_tokens=max_tokens + N * 8 + 64, max_steps=N + 8, k=k)
+    first = dec.prefill(prompt, prefill_step_size)
+    if use_graph and N > 1:
+        dec.step()                     # eager warm-up step (counts as step 0)
+        dec.capture()
+        done_steps = 1
+    else:
+        done_steps = 0
+    torch.cuda.synchronize(dec.device)
+    tic = time.perf_counter()
+    # Steps are enqueued ahead of the host; the stop test reads a pinned copy of the counters that
+    # trails the device by a couple of steps, so the device never waits for the host.
+    lead = 2
+    pinned = [torch.zeros(16, dtype=torch.int32).pin_memory() for _ in range(4)]
+    events = [torch.cuda.Event() for _ in range(4)]
+    i = done_steps
+    while i < N:
+        dec.replay()
+        pinned[i % 4].copy_(dec.ctl, non_blocking=True)
+        events[i % 4].record()
+        i += 1
+        j = i - 1 - lead
+        if j >= done_steps:
+            events[j % 4].synchronize()
+            if int(pinned[j % 4][CTL_NGEN]) >= max_tokens:
+                break
+    torch.cuda.synchronize(dec.device)
+    total = time.perf_counter() - tic
+    log = dec.step_log.cpu().tolist()
+    toks = dec.out_tokens.cpu().tolist()
+    steps_run = i
+    steps = steps_run
+    # the reference stops at the first step boundary with n >= max_tokens (mlx_eagle.py:544-546)
+    n = 0
+    accept_lengths = []
+    for s in range(steps):
+        if n >= max_tokens:
+            steps = s
+            break
+        accept_lengths.append(log[2 * s])
+        n += 1 + log[2 * s]
+    tokens = [first] + toks[:n]
+    stats = dict(tokens=tokens, generated=n, steps=steps, steps_launched=steps_run, accept_lengths=accept_lengths,
+                 mean_tokens_per_step=n / max(steps, 1), seconds=total,
+                 tokens_per_second=(sum(1 + log[2 * s] for s in range(done_steps, steps_run)) / total) if total > 0 else 0.0)
+    if verbose:
+        if tokenizer is not None:
+            print(tokenizer.decode(tokens))
+        print("Generated Tokens", n)
+        print("Mean Tokens Per Step:", stats["mean_tokens_per_step"])
+        print("Tokens Per Second:", round(stats["tokens_per_second"], 1))
+    dec.sync_offsets()
+    stats["decoder"] = dec
+    return stats
+
+
+def parse_args(argv=None):
+    """CLI flags of ``mlx_eagle.py:620-681``; model names are shape presets (random-init weights),
+    since no checkpoint or tokenizer can be downloaded here, and the prompt is a token count."""
+    p = argparse.ArgumentParser(description="Tree speculative decoding on B200 with seeded random-init models.")
+    p.add_argument("--draft-model", type=str, default="qwen2-0.5b")
+    p.add_argument("--base-model", type=str, default="qwen2-7b")
+    p.add_argument("--prompt", type=str, required=True,
+                   help="number of seeded random prompt tokens, or comma-separated token ids")
+    p.add_argument("--depth", type=int, default=1)
+    p.add_argument("--verify-num-tokens", type=int, default=15, help="7, 15, 23 or 31")
+    p.add_argument("--max-tokens", type=int, default=300)
+    p.add_argument("--max-generation-steps", "-N", type=int, default=300)
+    p.add_argument("--seed", type=int, default=0)
+    return p.parse_args(argv)
+
+
+def main(argv=None):
+    args = parse_args(argv)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    draft = Model.random_init(shape_preset(args.draft_model), args.seed + 1, dev)
+    base = Model.random_init(shape_preset(args.base_model), args.seed + 2, dev)
+    if "," in args.prompt or not args.prompt.isdigit():
+        ids = torch.tensor([int(t) for t in args.prompt.split(",")], dtype=torch.int32)
+    else:
+        g = torch.Generator().manual_seed(args.seed)
+        ids = torch.randint(0, min(draft.args.vocab_size, base.args.vocab_size), (int(args.prompt),), generator=g,
+                            dtype=torch.int32)
+    generate_step(ids, base, draft, k=8, depth=args.depth, verify_num_tokens=args.verify_num_tokens,
+                  max_tokens=args.max_tokens, prefill_step_size=512, N=args.max_generation_steps)
+
+
+if __name__ == "__main__":
+    main()

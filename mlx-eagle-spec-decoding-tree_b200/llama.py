@@ -1,0 +1,387 @@
+"""Llama-3 / Qwen2 decoder with the tree hooks of the reference's ``mlx_llama.py``.
+
+``Model(inputs, cache, mask, position_ids, flat_rope)`` keeps the reference's call
+(``mlx_llama.py:298-313``): explicit additive mask, integer or per-token array
+positions, ``flat_rope`` giving every token of the call the same position.  All
+linear layers are 4-bit / group-64 quantised and run through ``libb200eagle.so``;
+q/k/v are stored as one fused matrix, so one layer is eight kernel launches:
+
+    rms_norm -> qmm(+bias) -> rope_kv_append -> tree_attention -> qmm(+residual)
+    -> rms_norm -> qmm(SiLU(gate)*up) -> qmm(+residual)
+
+The decode loop does not go through ``__call__`` but through ``forward_device``,
+whose inputs (tokens, positions, tail masks, committed length) are read from
+device memory, so that a whole speculative step can be replayed as a CUDA graph.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Union
+
+import torch
+
+from . import _lib
+from . import qmm_kernel as qk
+from .quantize import quantize
+
+MAX_ROWS = 32          # tokens per forward pass (tree size + 1 <= 32)
+MAX_TAIL = 64          # uncommitted cache rows a query can address through its bit mask
+
+
+@dataclass
+class ModelArgs:
+    """Same fields as ``mlx_llama.py:21-38``."""
+    model_type: str
+    hidden_size: int
+    num_hidden_layers: int
+    intermediate_size: int
+    num_attention_heads: int
+    rms_norm_eps: float
+    vocab_size: int
+    head_dim: Optional[int] = None
+    max_position_embeddings: Optional[int] = None
+    num_key_value_heads: Optional[int] = None
+    attention_bias: bool = False
+    mlp_bias: bool = False
+    rope_theta: float = 10000
+    rope_traditional: bool = False
+    rope_scaling: Optional[Dict[str, Union[float, str]]] = None
+    tie_word_embeddings: bool = True
+
+    def __post_init__(self):
+        if self.num_key_value_heads is None:
+            self.num_key_value_heads = self.num_attention_heads
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+        if self.model_type == "qwen2":
+            self.attention_bias = True          # mlx_utils.py:116-117
+        if self.rope_traditional:
+            raise ValueError("only the non-traditional (half-split) RoPE layout is implemented")
+        if self.rope_scaling:
+            rope_type = self.rope_scaling.get("type") or self.rope_scaling.get("rope_type")
+            if rope_type not in ("linear", "llama3", "default"):
+                raise ValueError("rope_scaling type must be linear, llama3 or default")
+
+
+def rope_inv_freqs(args: ModelArgs):
+    """``(inv_freqs fp32 [hd/2], scaling_factor)`` as ``mlx_llama.py:98-116`` builds them."""
+    hd = args.head_dim
+    idx = torch.arange(0, hd, 2, dtype=torch.float32)
+    rope_type = "default"
+    if args.rope_scaling:
+        rope_type = args.rope_scaling.get("type") or args.rope_scaling.get("rope_type", "default")
+    if rope_type in ("default", "linear"):
+        scaling = 1.0 / float(args.rope_scaling["factor"]) if rope_type == "linear" else 1.0
+        inv = torch.pow(torch.tensor(2.0, dtype=torch.float32), -math.log2(args.rope_theta) * idx / hd)
+        return inv.float(), scaling
+    # llama3: frequency-dependent rescaling of the base frequencies (mlx_lm rope_utils, Llama3RoPE)
+    rs = args.rope_scaling
+    factor = float(rs["factor"])
+    low = float(rs.get("low_freq_factor", 1.0))
+    high = float(rs.get("high_freq_factor", 4.0))
+    old_len = float(rs.get("original_max_position_embeddings", 8192))
+    freqs = args.rope_theta ** (idx / hd)
+    wavelens = 2 * math.pi * freqs
+    low_wl, high_wl = old_len / low, old_len / high
+    scaled = torch.where(wavelens > low_wl, freqs * factor, freqs)
+    smooth = (old_len / wavelens - low) / (high - low)
+    mid = freqs / ((1 - smooth) / factor + smooth)
+    freqs = torch.where((wavelens > high_wl) & (wavelens < low_wl), mid, scaled)
+    return (1.0 / freqs).float(), 1.0
+
+
+class QLinear:
+    """A 4-bit quantised linear layer: packed weights, fp16 scales / biases, optional fp16 bias."""
+
+    def __init__(self, wq, scales, biases, bias=None):
+        self.weight, self.scales, self.biases, self.bias = wq, scales, biases, bias
+        self.out_features = wq.shape[0]
+        self.in_features = wq.shape[1] * 8
+        self.group_size, self.bits = 64, 4
+
+    def nbytes(self) -> int:
+        n = self.weight.numel() * 4 + self.scales.numel() * 2 + self.biases.numel() * 2
+        return n + (self.bias.numel() * 2 if self.bias is not None else 0)
+
+    def __call__(self, x):
+        """Stand-alone use, like ``NewQuantizedLinear.__call__`` (``mlx_model_fwd_bench.py:65-73``)."""
+        return qk.matmul(x, self.weight, self.scales, self.biases, self.group_size, bias=self.bias)[0]
+
+
+class FwdInputs:
+    """Device-resident inputs of one forward pass (what the tree kernels write)."""
+
+    def __init__(self, device):
+        self.tokens = torch.zeros(MAX_ROWS, dtype=torch.int32, device=device)
+        self.pos = torch.zeros(MAX_ROWS, dtype=torch.int32, device=device)
+        self.mask = torch.zeros(MAX_ROWS, dtype=torch.int64, device=device)   # uint64 bit masks
+        self.prefix = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+class KVCache:
+    """K/V of every layer in one allocation ``[layers][2][Hkv][rows][hd]`` plus the committed length.
+
+    ``offset`` has the meaning of ``mlx_lm``'s ``KVCache.offset`` (rows in use); the reference
+    rewinds it directly (``mlx_eagle.py:376,405-406,593-594``), and so may callers here.
+    """
+
+    def __init__(self, args: ModelArgs, rows: int, device):
+        self.rows = int(rows)
+        self.data = torch.zeros(args.num_hidden_layers, 2, args.num_key_value_heads, self.rows, args.head_dim,
+                                dtype=torch.float16, device=device)
+        self.offset = 0
+
+    def layer(self, i):
+        return self.data[i, 0], self.data[i, 1]
+
+    @property
+    def state(self):
+        return self.data[:, 0, :, : self.offset], self.data[:, 1, :, : self.offset]
+
+
+class Model:
+    def __init__(self, args: ModelArgs, layers: List[dict], embed: QLinear, norm: torch.Tensor,
+                 lm_head: Optional[QLinear], device):
+        self.args = args
+        self.model_type = args.model_type
+        self.device = torch.device(device)
+        self.layers = layers
+        self.embed = embed
+        self.norm = norm
+        self.lm_head = lm_head if lm_head is not None else embed      # tied: as_linear (mlx_llama.py:309-310)
+        inv, scaling = rope_inv_freqs(args)
+        self.inv_freqs = inv.to(self.device)
+        self.rope_scaling_factor = float(scaling)
+        self.scale = args.head_dim ** -0.5
+        H, hd = args.hidden_size, args.head_dim
+        self.nq, self.nkv = args.num_attention_heads * hd, args.num_key_value_heads * hd
+        f16 = dict(dtype=torch.float16, device=self.device)
+        self.h = torch.zeros(MAX_ROWS, H, **f16)
+        self.xn = torch.zeros(MAX_ROWS, H, **f16)
+        self.qkv = torch.zeros(MAX_ROWS, self.nq + 2 * self.nkv, **f16)
+        self.attn = torch.zeros(MAX_ROWS, self.nq, **f16)
+        self.act = torch.zeros(MAX_ROWS, args.intermediate_size, **f16)
+        self.logits = torch.zeros(MAX_ROWS, args.vocab_size, **f16)
+        self._attn_ws = None
+        self._attn_ws_rows = 0
+        self.fwd = FwdInputs(self.device)
+        self.launches_per_forward = 8 * args.num_hidden_layers + 3
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def random_init(args: ModelArgs, seed: int, device, gen_device=None) -> "Model":
+        """Seeded N(0, 0.02) weights quantised to 4 bit / group 64 (stands in for a checkpoint).
+
+        ``gen_device`` is where the random numbers are drawn ("cpu" gives the same weights on any
+        machine, which the parity tests use; the default draws on ``device``, which is what a
+        multi-GB model needs to be built in seconds)."""
+        device = torch.device(device)
+        gdev = torch.device(gen_device) if gen_device is not None else device
+        gen = torch.Generator(device=gdev).manual_seed(seed)
+        H, I, hd = args.hidden_size, args.intermediate_size, args.head_dim
+        nq, nkv = args.num_attention_heads * hd, args.num_key_value_heads * hd
+
+        def qlin(n, k, bias=False):
+            w = torch.randn(n, k, generator=gen, device=gdev) * 0.02
+            wq, s, b = (t.to(device) for t in quantize(w))
+            bv = (torch.randn(n, generator=gen, device=gdev) * 0.02).half().to(device) if bias else None
+            return QLinear(wq, s, b, bv)
+
+        def norm_w():
+            return (1.0 + 0.1 * torch.randn(H, generator=gen, device=gdev)).half().to(device)
+
+        layers = []
+        for _ in range(args.num_hidden_layers):
+            layers.append(dict(
+                qkv=qlin(nq + 2 * nkv, H, bias=args.attention_bias), o=qlin(H, nq), gate=qlin(I, H), up=qlin(I, H),
+                down=qlin(H, I), input_norm=norm_w(), post_norm=norm_w()))
+        embed = qlin(args.vocab_size, H)
+        lm_head = None if args.tie_word_embeddings else qlin(args.vocab_size, H)
+        return Model(args, layers, embed, norm_w(), lm_head, device)
+
+    def state_numpy(self) -> dict:
+        """All weights as numpy arrays (packed weights as uint32), for a CPU checker."""
+        import numpy as np
+
+        def lin(q: QLinear):
+            d = dict(weight=q.weight.cpu().numpy().view(np.uint32), scales=q.scales.cpu().numpy(),
+                     biases=q.biases.cpu().numpy())
+            d["bias"] = q.bias.cpu().numpy() if q.bias is not None else None
+            return d
+
+        layers = []
+        for L in self.layers:
+            layers.append({k: (lin(v) if isinstance(v, QLinear) else v.cpu().numpy()) for k, v in L.items()})
+        return dict(layers=layers, embed=lin(self.embed), norm=self.norm.cpu().numpy(),
+                    lm_head=None if self.lm_head is self.embed else lin(self.lm_head),
+                    inv_freqs=self.inv_freqs.cpu().numpy(), rope_scaling_factor=self.rope_scaling_factor)
+
+    def linear_weight_bytes(self) -> int:
+        """Bytes of quantised weights one forward pass streams (all layers + lm_head)."""
+        n = 0
+        for L in self.layers:
+            n += sum(L[k].nbytes() for k in ("qkv", "o", "gate", "up", "down"))
+        return n + self.lm_head.nbytes()
+
+    def make_cache(self, rows: int) -> KVCache:
+        return KVCache(self.args, rows, self.device)
+
+    # ------------------------------------------------------------------ device-side forward
+    def _attention_workspace(self, cache: KVCache):
+        if self._attn_ws is None or self._attn_ws_rows < cache.rows:
+            a = self.args
+            nbytes = _lib.lib().b200_tree_attention_workspace_bytes(
+                MAX_ROWS, a.num_attention_heads, a.num_key_value_heads, a.head_dim, cache.rows)
+            self._attn_ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+            self._attn_ws_rows = cache.rows
+        return self._attn_ws
+
+    def forward_device(self, M: int, cache: KVCache, write_off: int, tail: int, fwd: Optional[FwdInputs] = None,
+                       logits_rows: Optional[int] = None, row_index: Optional[torch.Tensor] = None):
+        """One forward pass of ``M`` tokens whose ids / positions / masks / committed length sit in
+        ``fwd`` (device memory).  New K/V rows go to cache row ``prefix + write_off + m``; query m sees
+        rows ``< prefix`` and tail row j iff bit j of ``fwd.mask[m]``.  Returns fp16 logits
+        ``(logits_rows or M, V)`` (a view of an internal buffer); with ``row_index`` (device int) only
+        rows ``row_index .. row_index+logits_rows-1`` of the hidden state reach the head."""
+        if not (1 <= M <= MAX_ROWS and 1 <= tail <= MAX_TAIL and write_off + M <= tail):
+            raise _lib.B200Error("forward_device: need 1 <= M <= 32, tail <= 64, write_off + M <= tail")
+        fwd = fwd or self.fwd
+        a, L, lib = self.args, _lib.lib(), _lib.lib()
+        st, p = _lib.stream_ptr(self.device), _lib.ptr
+        ws = qk.workspace(self.device)
+        aws = self._attention_workspace(cache)
+        H, I, hd = a.hidden_size, a.intermediate_size, a.head_dim
+        Hq, Hkv = a.num_attention_heads, a.num_key_value_heads
+        nqkv = self.nq + 2 * self.nkv
+        eps = float(a.rms_norm_eps)
+        ck = _lib.check
+        ck(L.b200_embed_gather(p(fwd.tokens), p(self.embed.weight), p(self.embed.scales), p(self.embed.biases),
+                               p(self.h), M, H, a.vocab_size, st), "b200_embed_gather")
+        for li, lw in enumerate(self.layers):
+            kc, vc = cache.layer(li)
+            ck(L.b200_rms_norm(p(self.h), p(lw["input_norm"]), p(self.xn), None, M, H, eps, st), "b200_rms_norm")
+            q = lw["qkv"]
+            ck(L.b200_qmm_fused(p(self.xn), p(q.weight), p(q.scales), p(q.biases), None, None, None, p(q.bias),
+                                None, p(self.qkv), M, nqkv, H, 64, 0, qk.EPI_NONE, p(ws), ws.numel(), st), "qmm qkv")
+            ck(L.b200_rope_kv_append(p(self.qkv), p(fwd.pos), p(self.inv_freqs), self.rope_scaling_factor, p(kc),
+                                     p(vc), p(fwd.prefix), write_off, M, Hq, Hkv, hd, cache.rows, st), "rope")
+            ck(L.b200_tree_attention(p(self.qkv), nqkv, p(kc), p(vc), p(fwd.mask), p(fwd.prefix), tail,
+                                     p(self.attn), M, Hq, Hkv, hd, cache.rows, cache.rows, self.scale,
+                                     p(aws), aws.numel(), st), "b200_tree_attention")
+            o = lw["o"]
+            ck(L.b200_qmm_fused(p(self.attn), p(o.weight), p(o.scales), p(o.biases), None, None, None, None,
+                                p(self.h), p(self.h), M, H, self.nq, 64, 0, qk.EPI_RESIDUAL, p(ws), ws.numel(), st),
+               "qmm o")
+            ck(L.b200_rms_norm(p(self.h), p(lw["post_norm"]), p(self.xn), None, M, H, eps, st), "b200_rms_norm")
+            g, u = lw["gate"], lw["up"]
+            ck(L.b200_qmm_fused(p(self.xn), p(g.weight), p(g.scales), p(g.biases), p(u.weight), p(u.scales),
+                                p(u.biases), None, None, p(self.act), M, I, H, 64, 0, qk.EPI_SILU_MUL, p(ws),
+                                ws.numel(), st), "qmm gate/up")
+            d = lw["down"]
+            ck(L.b200_qmm_fused(p(self.act), p(d.weight), p(d.scales), p(d.biases), None, None, None, None,
+                                p(self.h), p(self.h), M, H, I, 64, 0, qk.EPI_RESIDUAL, p(ws), ws.numel(), st),
+               "qmm down")
+        rows = M if logits_rows is None else logits_rows
+        ck(L.b200_rms_norm(p(self.h), p(self.norm), p(self.xn), p(row_index), rows, H, eps, st), "final norm")
+        hd_ = self.lm_head
+        ck(L.b200_qmm_fused(p(self.xn), p(hd_.weight), p(hd_.scales), p(hd_.biases), None, None, None, None, None,
+                            p(self.logits), rows, a.vocab_size, H, 64, 0, qk.EPI_NONE, p(ws), ws.numel(), st),
+           "qmm lm_head")
+        return self.logits[:rows]
+
+    # ------------------------------------------------------------------ reference-style call
+    def __call__(self, inputs: torch.Tensor, cache: Optional[KVCache] = None, mask: Optional[torch.Tensor] = None,
+                 position_ids: Optional[Union[torch.Tensor, int]] = None, flat_rope: bool = False,
+                 logits_last_only: bool = False) -> torch.Tensor:
+        """``logits (1, L, V)``; the argument meanings follow ``mlx_llama.py:298-313`` / ``:121-196``.
+
+        ``mask`` is the additive matrix ``(1,1,L,cache.offset+L)`` of 0 / -inf the reference passes
+        (``mlx_eagle.py:177,338``); ``None`` means causal.  Calls longer than 32 tokens (prompt
+        ingestion) are split into passes of 32, which is only possible with the causal mask.
+        ``logits_last_only`` (an addition) returns only the last token's logits ``(1, 1, V)``.
+        """
+        if cache is None:
+            raise _lib.B200Error("a KVCache is required (the reference's cache-less branch is not on this path)")
+        inputs = inputs.reshape(-1).to(torch.int32)
+        Ltot = inputs.numel()
+        if Ltot > MAX_ROWS and (mask is not None or position_ids is not None):
+            raise _lib.B200Error("explicit masks / positions are limited to 32 tokens per call")
+        outs = []
+        for c0 in range(0, Ltot, MAX_ROWS):
+            chunk = inputs[c0:c0 + MAX_ROWS]
+            L = chunk.numel()
+            off = cache.offset
+            if off + L > cache.rows:
+                raise _lib.B200Error("KV cache is full")
+            if position_ids is None:
+                pos = off + torch.arange(L, dtype=torch.int32)
+            elif isinstance(position_ids, int):
+                pos = torch.full((L,), position_ids, dtype=torch.int32) if flat_rope else \
+                    position_ids + torch.arange(L, dtype=torch.int32)
+            else:
+                pos = position_ids.reshape(-1).to(torch.int32).cpu()
+            if mask is None:
+                prefix, write_off, tail = off, 0, L
+                bits = [(2 << m) - 1 for m in range(L)]
+            else:
+                vis = (mask.reshape(L, -1).float().cpu() == 0)
+                cols = vis.shape[1]
+                if cols != off + L:
+                    raise _lib.B200Error("mask must have cache.offset + L columns")
+                all_vis = vis.all(dim=0)
+                first_hidden = int((~all_vis).nonzero()[0]) if (~all_vis).any() else cols
+                prefix = max(min(first_hidden, off), cols - MAX_TAIL)
+                if not bool(vis[:, :prefix].all()):
+                    raise _lib.B200Error("mask hides a column more than 64 rows before the end of the cache")
+                tail, write_off = cols - prefix, off - prefix
+                bits = []
+                for m in range(L):
+                    v = 0
+                    for j in range(tail):
+                        if vis[m, prefix + j]:
+                            v |= 1 << j
+                    bits.append(v)
+            f = self.fwd
+            f.tokens[:L].copy_(chunk)
+            f.pos[:L].copy_(pos.to(self.device) if isinstance(pos, torch.Tensor) else pos)
+            f.mask[:L].copy_(torch.tensor([b - (1 << 64) if b >= (1 << 63) else b for b in bits], dtype=torch.int64))
+            f.prefix.fill_(prefix)
+            logits = self.forward_device(L, cache, write_off, tail)
+            cache.offset = off + L
+            if logits_last_only:
+                outs = [logits[L - 1:L].clone()]
+            else:
+                outs.append(logits.clone())
+        return torch.cat(outs, 0).unsqueeze(0)
+
+
+def shape_preset(name: str) -> ModelArgs:
+    """Architectures named by the benchmark configurations (random-init stand-ins for checkpoints)."""
+    presets = {
+        "qwen2-0.5b": dict(model_type="qwen2", hidden_size=896, num_hidden_layers=24, intermediate_size=4864,
+                           num_attention_heads=14, num_key_value_heads=2, head_dim=64, vocab_size=151936,
+                           rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True),
+        "qwen2-7b": dict(model_type="qwen2", hidden_size=3584, num_hidden_layers=28, intermediate_size=18944,
+                         num_attention_heads=28, num_key_value_heads=4, head_dim=128, vocab_size=152064,
+                         rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False),
+        "llama3.2-1b": dict(model_type="llama", hidden_size=2048, num_hidden_layers=16, intermediate_size=8192,
+                            num_attention_heads=32, num_key_value_heads=8, head_dim=64, vocab_size=128256,
+                            rms_norm_eps=1e-5, rope_theta=5e5, tie_word_embeddings=True),
+        "llama3-8b": dict(model_type="llama", hidden_size=4096, num_hidden_layers=32, intermediate_size=14336,
+                          num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=128256,
+                          rms_norm_eps=1e-5, rope_theta=5e5, tie_word_embeddings=False),
+        "llama3-70b": dict(model_type="llama", hidden_size=8192, num_hidden_layers=80, intermediate_size=28672,
+                           num_attention_heads=64, num_key_value_heads=8, head_dim=128, vocab_size=128256,
+                           rms_norm_eps=1e-5, rope_theta=5e5, tie_word_embeddings=False),
+        # small shapes for tests (same structure, seconds on a CPU oracle)
+        "tiny-qwen2": dict(model_type="qwen2", hidden_size=256, num_hidden_layers=2, intermediate_size=512,
+                           num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=1024,
+                           rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True),
+        "tiny-llama": dict(model_type="llama", hidden_size=512, num_hidden_layers=2, intermediate_size=1024,
+                           num_attention_heads=4, num_key_value_heads=1, head_dim=128, vocab_size=2048,
+                           rms_norm_eps=1e-5, rope_theta=5e5, tie_word_embeddings=False),
+    }
+    if name not in presets:
+        raise KeyError(f"unknown shape preset {name!r}; known: {sorted(presets)}")
+    return ModelArgs(**presets[name])
