@@ -27,9 +27,11 @@ def test_rms_norm(be, cuda):
     x = (torch.randn(5, 896, generator=g) * 3).half()
     w = (1 + 0.1 * torch.randn(896, generator=g)).half()
     y = torch.empty_like(x, device=cuda)
-    rc = be._lib.lib().b200_rms_norm(be._lib.ptr(x.to(cuda)), be._lib.ptr(w.to(cuda)), be._lib.ptr(y), None, 5, 896,
+    xd, wd = x.to(cuda), w.to(cuda)
+    rc = be._lib.lib().b200_rms_norm(be._lib.ptr(xd), be._lib.ptr(wd), be._lib.ptr(y), None, 5, 896,
                                      1e-6, be._lib.stream_ptr(cuda))
     assert rc == 0
+    torch.cuda.synchronize()
     _close(y.cpu().numpy(), model_ref.rms_norm(x.numpy(), w.numpy(), 1e-6), 2.0 ** -10, 1e-4)
 
 
