@@ -1,0 +1,355 @@
+"""Benchmark of the tree speculative decoding hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Workload (N = 1 and every rank at N > 1): full speculative decode steps, greedy, Qwen2-7B-shape
+4-bit target + Qwen2-0.5B-shape 4-bit draft (random-init weights, seeded), 256-token seeded random
+prompt, depth 3, 15 verify tokens; one "step" is one speculative step (draft catch-up pass, 3 draft
+tree passes, tree finalisation, one target pass on 16 tokens, acceptance, KV compaction).
+Metric: accepted tokens per second (tokens produced by the timed steps / device time).
+
+The JSON line also carries: the end-to-end number through ``SpecDecoder.generate`` with a pinned
+host prompt (``e2e``), the roofline of the dominant kernel (the 4-bit quantised matmul, timed on a
+sweep over all target-model linears at 16 rows), and a CPU baseline (the CPU restatement of the
+reference's path, timed on a bounded sample on this host's cores).
+
+``--impl reference`` times the CPU restatement only (the reference itself is MLX/Metal and cannot
+run on Linux), on the same configuration, and prints the same line with ``"impl": "reference"``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "accepted tokens/s (7B-shape 4-bit target + 0.5B draft, 15-node tree)"
+UNIT = "tokens/s"
+WORKLOAD = "spec-decode qwen2-7b-shape target + qwen2-0.5b-shape draft, prompt 256, depth 3, verify 15, greedy"
+DEPTH, VERIFY, PROMPT = 3, 15, 256
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s)"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [v for v in sm if v > 500] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def _qmm_bytes(m, n, k, bias=False):
+    return n * k // 2 + 4 * n * k // 64 + 2 * m * k + 2 * m * n + (2 * n if bias else 0)
+
+
+def qmm_roofline(be, torch, model, rows, reps):
+    """Time the quantised-matmul launches of one target pass (all layers + head) as one CUDA graph."""
+    qk, L, p = be.qmm_kernel, be._lib.lib(), be._lib.ptr
+    a = model.args
+    H, I = a.hidden_size, a.intermediate_size
+    nqkv = model.nq + 2 * model.nkv
+    ws = qk.workspace(model.device)
+    launches, alg = 0, 0
+
+    def sweep():
+        nonlocal launches, alg
+        st = be._lib.stream_ptr(model.device)
+        for lw in model.layers:
+            q, o, g, u, d = lw["qkv"], lw["o"], lw["gate"], lw["up"], lw["down"]
+            L.b200_qmm_fused(p(model.xn), p(q.weight), p(q.scales), p(q.biases), None, None, None, p(q.bias), None,
+                             p(model.qkv), rows, nqkv, H, 64, 0, 0, p(ws), ws.numel(), st)
+            L.b200_qmm_fused(p(model.attn), p(o.weight), p(o.scales), p(o.biases), None, None, None, None,
+                             p(model.h), p(model.h), rows, H, model.nq, 64, 0, 1, p(ws), ws.numel(), st)
+            L.b200_qmm_fused(p(model.xn), p(g.weight), p(g.scales), p(g.biases), p(u.weight), p(u.scales),
+                             p(u.biases), None, None, p(model.act), rows, I, H, 64, 0, 2, p(ws), ws.numel(), st)
+            L.b200_qmm_fused(p(model.act), p(d.weight), p(d.scales), p(d.biases), None, None, None, None,
+                             p(model.h), p(model.h), rows, H, I, 64, 0, 1, p(ws), ws.numel(), st)
+        hd = model.lm_head
+        L.b200_qmm_fused(p(model.xn), p(hd.weight), p(hd.scales), p(hd.biases), None, None, None, None, None,
+                         p(model.logits), rows, a.vocab_size, H, 64, 0, 0, p(ws), ws.numel(), st)
+
+    nl = len(model.layers)
+    resid = 2 * rows * H                                         # residual rows read by the epilogue
+    per_layer = (_qmm_bytes(rows, nqkv, H, a.attention_bias)       # q|k|v with bias
+                 + _qmm_bytes(rows, H, model.nq) + resid           # o_proj + residual
+                 + 2 * _qmm_bytes(rows, I, H) - 2 * rows * H - 2 * rows * I   # gate & up share x, one output
+                 + _qmm_bytes(rows, H, I) + resid)                 # down_proj + residual
+    alg = nl * per_layer + _qmm_bytes(rows, a.vocab_size, H)
+    launches = 4 * nl + 1
+    model.h.zero_()
+    model.xn.normal_(0, 1)
+    model.attn.normal_(0, 1)
+    model.act.normal_(0, 1)
+    sweep()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        sweep()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) / 1e3 / reps
+    return alg, launches, sec
+
+
+def cpu_sample(steps, warm=0, seed=0):
+    """The CPU restatement on a bounded sample: `warm` untimed + `steps` timed speculative steps at the
+    full shapes, with the 256 committed KV rows pre-filled (prompt ingestion is outside the metric's
+    timer).  Returns (tokens produced by the timed steps, their seconds, host threads used)."""
+    import numpy as np
+    import b200_eagle as be
+    from oracle import eagle_ref, model_ref, qmm_c
+
+    rng = np.random.default_rng(seed)
+
+    def lin(n, k, bias=False):
+        s = (rng.random((n, k // 64), dtype=np.float32) * 0.004 + 0.002).astype(np.float16)
+        return dict(weight=rng.integers(0, 2 ** 32, (n, k // 8), dtype=np.uint32), scales=s,
+                    biases=(-7.5 * s.astype(np.float32)).astype(np.float16),
+                    bias=(rng.standard_normal(n) * 0.02).astype(np.float16) if bias else None)
+
+    def state(args):
+        H, I, hd = args.hidden_size, args.intermediate_size, args.head_dim
+        nq, nkv = args.num_attention_heads * hd, args.num_key_value_heads * hd
+        layers = [dict(qkv=lin(nq + 2 * nkv, H, args.attention_bias), o=lin(H, nq), gate=lin(I, H), up=lin(I, H),
+                       down=lin(H, I), input_norm=np.ones(H, np.float16), post_norm=np.ones(H, np.float16))
+                  for _ in range(args.num_hidden_layers)]
+        inv, sc = be.llama.rope_inv_freqs(args)
+        return dict(layers=layers, embed=lin(args.vocab_size, H), norm=np.ones(H, np.float16),
+                    lm_head=None if args.tie_word_embeddings else lin(args.vocab_size, H),
+                    inv_freqs=inv.numpy(), rope_scaling_factor=sc)
+
+    da, ba = be.shape_preset("qwen2-0.5b"), be.shape_preset("qwen2-7b")
+    draft = model_ref.OracleModel(da, state(da))
+    base = model_ref.OracleModel(ba, state(ba))
+    rows = PROMPT + 8 * (steps + DEPTH + 2) + VERIFY + 64
+    bc, dc = model_ref.make_prompt_cache(base, rows), model_ref.make_prompt_cache(draft, rows)
+    for caches in (bc, dc):
+        for c in caches:
+            c.keys[:, :, :PROMPT] = (rng.standard_normal(c.keys[:, :, :PROMPT].shape) * 0.5).astype(np.float16)
+            c.values[:, :, :PROMPT] = (rng.standard_normal(c.values[:, :, :PROMPT].shape) * 0.5).astype(np.float16)
+            c.offset = PROMPT
+    from oracle import tree_ref as tr
+    y, a, n, sec = np.array([1]), 0, 0, 0.0
+    for it in range(warm + steps):
+        tic = time.perf_counter()
+        tpi, mi, dt, logits, bo, do = eagle_ref.spec_step(y, base, draft, bc, dc, a, 8, DEPTH, VERIFY)
+        retrieve = tr.post_process_draft_tree(tpi, VERIFY, mi)
+        cand = dt[0][retrieve]
+        best, a, sample = tr.evaluate_posterior_greedy(logits[retrieve], cand)
+        idx, acc = retrieve[best, 1:1 + a], cand[best, 1:1 + a]
+        tr.accept_candidate([c.keys for c in bc], [c.values for c in bc], idx, a, bo)
+        for c in bc:
+            c.offset = bo + a + 1
+        for c in dc:
+            c.offset = do
+        y = np.concatenate([acc.astype(np.int64), [min(int(sample.argmax()), da.vocab_size - 1)]])
+        if it >= warm:
+            n += 1 + a
+            sec += time.perf_counter() - tic
+    return n, sec, qmm_c.num_threads()
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 4))
+    warm = 1 if args.warmup > 0 else 0
+    n, sec, cores = cpu_sample(steps, warm)
+    value = n / sec
+    sample = (f"{steps} of the requested {args.steps} steps at the full shapes on {cores} host threads; weights drawn "
+              "directly in packed 4-bit form, 256 committed KV rows pre-filled (prompt ingestion untimed)")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sec / steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference path (MLX/Metal cannot run "
+                       "on Linux)"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import b200_eagle as be
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    warmup = max(args.warmup, 3)
+    K = args.steps
+
+    draft = be.Model.random_init(be.shape_preset("qwen2-0.5b"), seed=1000 + rank, device=dev)
+    base = be.Model.random_init(be.shape_preset("qwen2-7b"), seed=2000 + rank, device=dev)
+    rows = ((PROMPT + 8 * (warmup + K + DEPTH + 8) + VERIFY + 128 + 63) // 64) * 64
+    dec = be.SpecDecoder(base, draft, DEPTH, VERIFY, cache_rows=rows, max_out_tokens=8 * (warmup + K) + 512,
+                         max_steps=warmup + K + 64)
+    dec.warmup(capture=True)
+    g = torch.Generator().manual_seed(1234 + rank)
+    prompt_host = torch.randint(0, draft.args.vocab_size, (PROMPT,), generator=g, dtype=torch.int32).pin_memory()
+
+    # ---- device-resident number: K graph replays after W warm-up steps -------------------------
+    dec.prefill(prompt_host)
+    for _ in range(warmup):
+        dec.replay()
+    torch.cuda.synchronize()
+    n0 = int(dec.ctl[3])
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        dec.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sec = e0.elapsed_time(e1) / 1e3
+    clocks = sampler.stop()
+    produced = int(dec.ctl[3]) - n0
+    log = dec.step_log[2 * warmup: 2 * (warmup + K)].cpu().view(-1, 2)
+    mean_accept = float(log[:, 0].float().mean())
+
+    # ---- end to end through the public call, pinned host prompt in, tokens out ----------------
+    n_e2e = min(K, 300)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    res = dec.generate(prompt_host, max_tokens=n_e2e, N=n_e2e)
+    torch.cuda.synchronize()
+    e2e_sec = time.perf_counter() - t0
+    e2e_tokens, e2e_steps = res["produced"], max(res["steps_launched"], 1)
+
+    tot = torch.tensor([float(produced), sec, float(e2e_tokens), e2e_sec], dtype=torch.float64, device=dev)
+    if world > 1:
+        sums, maxs = tot.clone(), tot.clone()
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+        dist.all_reduce(maxs, op=dist.ReduceOp.MAX)
+        produced_all, sec_all = float(sums[0]), float(maxs[1])
+        e2e_tokens_all, e2e_sec_all = float(sums[2]), float(maxs[3])
+    else:
+        produced_all, sec_all, e2e_tokens_all, e2e_sec_all = float(produced), sec, float(e2e_tokens), e2e_sec
+
+    line = None
+    if rank == 0:
+        peak, peak_src = _peaks()
+        alg, qmm_launches, qsec = qmm_roofline(be, torch, base, VERIFY + 1, reps=20)
+        achieved = alg / qsec / 1e9
+        step_bytes = base.linear_weight_bytes() + (DEPTH + 1) * draft.linear_weight_bytes()
+        line = {
+            "metric": METRIC, "value": produced_all / sec_all, "unit": UNIT, "n_gpus": world, "steps": K,
+            "warmup": warmup, "ms_per_step": 1e3 * sec_all / K, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "requests": world, "parallelism": f"{world} independent request stream(s)",
+                       "l2": "inputs larger than L2 (4.26 GB of weights streamed per step)",
+                       "mean_accept_length": mean_accept, "weight_bytes_per_step": step_bytes,
+                       "step_weight_stream_frac_of_peak": step_bytes / (sec_all / K) / 1e9 / peak},
+            "clocks": clocks,
+            "e2e": {"value": e2e_tokens_all / e2e_sec_all, "unit": UNIT,
+                    "h2d_bytes_per_step": res["h2d_bytes"] / e2e_steps, "d2h_bytes_per_step": res["d2h_bytes"] / e2e_steps,
+                    "region": "SpecDecoder.generate: pinned-host prompt copy, prompt ingestion, decode loop with a "
+                              "pinned read-back of the counters every step, token read-back"},
+            "gpu_launches": dec.kernel_launches_per_step * K,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src,
+                         "kernel": f"qmm_kernel, {qmm_launches} launches of one target pass at {VERIFY + 1} rows",
+                         "algorithmic_bytes_per_launch": alg / qmm_launches, "us_per_launch": 1e6 * qsec / qmm_launches},
+        }
+        if not args.no_cpu_baseline and world == 1:
+            n_cpu, cpu_sec, cores = cpu_sample(2, warm=1)
+            line["cpu_baseline"] = {"value": n_cpu / cpu_sec, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": "2 speculative steps (after 1 untimed) at the full shapes, weights drawn "
+                                              "directly in packed 4-bit form, 256 committed KV rows pre-filled"}
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

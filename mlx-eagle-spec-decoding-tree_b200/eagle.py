@@ -180,6 +180,70 @@ class SpecDecoder:
         else:
             self.step()
 
+    def warmup(self, capture: bool = True):
+        """One eager step on a dummy prompt (sets kernel attributes, sizes workspaces), then the graph
+        capture.  Call once after construction; ``generate`` then only replays."""
+        g = torch.Generator().manual_seed(0)
+        v = min(self.base.args.vocab_size, self.draft.args.vocab_size)
+        self.prefill(torch.randint(0, v, (8,), generator=g, dtype=torch.int32))
+        self.step()
+        if capture:
+            self.capture()
+        torch.cuda.synchronize(self.device)
+
+    def generate(self, prompt: torch.Tensor, max_tokens: int = 128, N: int = 20, prefill_step_size: int = 512):
+        """Greedy tree-speculative generation for one prompt (host or device tensor of token ids).
+
+        Runs at most ``N`` steps and stops at the first step boundary where ``max_tokens`` were generated
+        (``mlx_eagle.py:544-546``).  Steps are enqueued ahead of the host: the stop test reads a pinned
+        copy of the device counters that trails the device by two steps, so the device never waits for
+        the host; steps launched past the stop point are discarded from the result.
+        Returns a dict: tokens (first token + every step's accepted tokens and bonus token),
+        accept_lengths, generated, steps, steps_launched, seconds (decode loop only, as the reference
+        times it, ``:541``), tokens_per_second, and the byte counts copied between host and device.
+        """
+        if N + 4 > self.max_steps or max_tokens + 8 * 4 > self.out_tokens.numel():
+            raise _lib.B200Error("generate: N / max_tokens exceed the decoder's log capacity")
+        if prompt.numel() + max_tokens + 8 * (self.depth + 2) + self.T + 64 > self.base_cache.rows:
+            raise _lib.B200Error("generate: prompt + max_tokens do not fit the KV cache")
+        first = self.prefill(prompt, prefill_step_size)
+        torch.cuda.synchronize(self.device)
+        tic = time.perf_counter()
+        lead = 2
+        if not hasattr(self, "_pinned"):
+            self._pinned = [torch.zeros(16, dtype=torch.int32).pin_memory() for _ in range(4)]
+            self._events = [torch.cuda.Event() for _ in range(4)]
+        pinned, events = self._pinned, self._events
+        i = 0
+        while i < N:
+            self.replay()
+            pinned[i % 4].copy_(self.ctl, non_blocking=True)
+            events[i % 4].record()
+            i += 1
+            j = i - 1 - lead
+            if j >= 0:
+                events[j % 4].synchronize()
+                if int(pinned[j % 4][CTL_NGEN]) >= max_tokens:
+                    break
+        torch.cuda.synchronize(self.device)
+        total = time.perf_counter() - tic
+        steps_run = i
+        log = self.step_log[: 2 * steps_run].cpu().tolist()
+        produced = sum(1 + log[2 * s] for s in range(steps_run))
+        toks = self.out_tokens[:produced].cpu().tolist()
+        n, steps, accept_lengths = 0, 0, []
+        for s in range(steps_run):
+            if n >= max_tokens:
+                break
+            accept_lengths.append(log[2 * s])
+            n += 1 + log[2 * s]
+            steps += 1
+        d2h = steps_run * 64 + 8 * steps_run + 4 * produced
+        return dict(tokens=[first] + toks[:n], generated=n, steps=steps, steps_launched=steps_run,
+                    accept_lengths=accept_lengths, mean_tokens_per_step=n / max(steps, 1), seconds=total,
+                    tokens_per_second=produced / total if total > 0 else 0.0, produced=produced,
+                    h2d_bytes=int(prompt.numel()) * 4, d2h_bytes=d2h)
+
     # ------------------------------------------------------------------ host views
     def read_ctl(self) -> List[int]:
         return self.ctl.cpu().tolist()
@@ -259,67 +323,21 @@ def spec_step(dec: SpecDecoder):
 
 def generate_step(prompt: torch.Tensor, base_model: Model, draft_model: Model, prefill_step_size: int = 512,
                   k: int = 8, depth: int = 5, verify_num_tokens: int = 31, max_tokens: int = 128, tokenizer=None,
-                  N: int = 20, use_graph: bool = True, verbose: bool = True, return_stats: bool = True):
-    """Greedy tree-speculative generation (``mlx_eagle.py:503-606``).
-
-    Same arguments as the reference (``verify_num_tokens`` is capped at 31 here).  Runs at most ``N``
-    steps and stops at the first step boundary where ``max_tokens`` were generated; the timer starts
-    after prompt ingestion, as in the reference (``:541``).  Returns a dict with the generated tokens
-    (first token from the prompt pass, then each step's accepted tokens + bonus token), the
-    per-step accept lengths, tokens per step and tokens per second.
-    """
+                  N: int = 20, use_graph: bool = True, verbose: bool = True):
+    """Greedy tree-speculative generation (``mlx_eagle.py:503-606``), same arguments as the reference
+    (``verify_num_tokens`` is limited to 31 here).  Builds a ``SpecDecoder`` for the request, captures
+    its step graph and calls ``SpecDecoder.generate``; prints the reference's three summary lines.
+    Returns the result dict of ``generate`` plus the decoder under ``"decoder"``."""
     rows = prompt.numel() + max_tokens + 8 * (depth + 2) + verify_num_tokens + 128
     rows = ((rows + 63) // 64) * 64
     dec = SpecDecoder(base_model, draft_model, depth, verify_num_tokens, rows,
-                      max_out_tokens=max_tokens + N * 8 + 64, max_steps=N + 8, k=k)
-    first = dec.prefill(prompt, prefill_step_size)
-    if use_graph and N > 1:
-        dec.step()                     # eager warm-up step (counts as step 0)
-        dec.capture()
-        done_steps = 1
-    else:
-        done_steps = 0
-    torch.cuda.synchronize(dec.device)
-    tic = time.perf_counter()
-    # Steps are enqueued ahead of the host; the stop test reads a pinned copy of the counters that
-    # trails the device by a couple of steps, so the device never waits for the host.
-    lead = 2
-    pinned = [torch.zeros(16, dtype=torch.int32).pin_memory() for _ in range(4)]
-    events = [torch.cuda.Event() for _ in range(4)]
-    i = done_steps
-    while i < N:
-        dec.replay()
-        pinned[i % 4].copy_(dec.ctl, non_blocking=True)
-        events[i % 4].record()
-        i += 1
-        j = i - 1 - lead
-        if j >= done_steps:
-            events[j % 4].synchronize()
-            if int(pinned[j % 4][CTL_NGEN]) >= max_tokens:
-                break
-    torch.cuda.synchronize(dec.device)
-    total = time.perf_counter() - tic
-    log = dec.step_log.cpu().tolist()
-    toks = dec.out_tokens.cpu().tolist()
-    steps_run = i
-    steps = steps_run
-    # the reference stops at the first step boundary with n >= max_tokens (mlx_eagle.py:544-546)
-    n = 0
-    accept_lengths = []
-    for s in range(steps):
-        if n >= max_tokens:
-            steps = s
-            break
-        accept_lengths.append(log[2 * s])
-        n += 1 + log[2 * s]
-    tokens = [first] + toks[:n]
-    stats = dict(tokens=tokens, generated=n, steps=steps, steps_launched=steps_run, accept_lengths=accept_lengths,
-                 mean_tokens_per_step=n / max(steps, 1), seconds=total,
-                 tokens_per_second=(sum(1 + log[2 * s] for s in range(done_steps, steps_run)) / total) if total > 0 else 0.0)
+                      max_out_tokens=max_tokens + 128, max_steps=N + 8, k=k)
+    dec.warmup(capture=use_graph)
+    stats = dec.generate(prompt, max_tokens=max_tokens, N=N, prefill_step_size=prefill_step_size)
     if verbose:
         if tokenizer is not None:
-            print(tokenizer.decode(tokens))
-        print("Generated Tokens", n)
+            print(tokenizer.decode(stats["tokens"]))
+        print("Generated Tokens", stats["generated"])
         print("Mean Tokens Per Step:", stats["mean_tokens_per_step"])
         print("Tokens Per Second:", round(stats["tokens_per_second"], 1))
     dec.sync_offsets()

@@ -58,25 +58,34 @@ static void init_tables(void) {
     g_h2f_ready = 1;
 }
 
-/* Round a double to the nearest fp16 (ties to even), returned as its bit pattern. */
+/* Round a double to the nearest fp16 (ties to even), returned as its bit pattern.  Integer
+ * arithmetic on the double's bits: the 53-bit significand is shifted down to 11 bits (fewer for
+ * fp16 subnormals) and rounded on the discarded part. */
 uint16_t oracle_f64_to_f16(double d) {
-    uint16_t sign = 0;
-    if (d != d) return 0x7e00;
-    if (signbit(d)) { sign = 0x8000; d = -d; }
-    if (d >= 65520.0) return sign | 0x7c00;
-    if (d == 0.0) return sign;
-    int e;
-    frexp(d, &e);           /* d = f * 2^e, f in [0.5, 1)  ->  floor(log2 d) = e - 1 */
-    e -= 1;
-    int qexp = (e < -14) ? -24 : (e - 10);          /* exponent of one unit in the last place */
-    double r = nearbyint(ldexp(d, -qexp));           /* exact scaling, ties-to-even rounding   */
-    double v = ldexp(r, qexp);
-    if (v >= 65536.0) return sign | 0x7c00;
-    if (v < 6.103515625e-05) return sign | (uint16_t)r;      /* subnormal (r <= 1023) or zero */
-    frexp(v, &e);
-    e -= 1;
-    int man = (int)ldexp(v, 10 - e) - 1024;
-    return sign | (uint16_t)(((e + 15) << 10) | man);
+    uint64_t bits;
+    memcpy(&bits, &d, 8);
+    uint16_t sign = (uint16_t)((bits >> 48) & 0x8000u);
+    int bexp = (int)((bits >> 52) & 0x7ff);
+    uint64_t frac = bits & 0xfffffffffffffULL;
+    if (bexp == 0x7ff) return frac ? 0x7e00 : (uint16_t)(sign | 0x7c00);
+    if (bexp == 0) return sign;                       /* double zero / subnormal: far below fp16 range */
+    int e = bexp - 1023;
+    if (e >= 16) return sign | 0x7c00;
+    uint64_t mant = frac | (1ULL << 52);
+    int shift = 42;                                   /* keep 11 significant bits */
+    int hexp = e + 15;                                /* biased fp16 exponent */
+    if (e < -14) {                                    /* fp16 subnormal: fewer bits survive */
+        shift += -14 - e;
+        hexp = 0;
+        if (shift > 54) return sign;                  /* below half of the smallest subnormal */
+    }
+    uint64_t q = mant >> shift;
+    uint64_t rem = mant & ((1ULL << shift) - 1);
+    uint64_t half = 1ULL << (shift - 1);
+    if (rem > half || (rem == half && (q & 1))) q++;
+    uint32_t out = (hexp > 0) ? (uint32_t)(((uint32_t)hexp << 10) + (uint32_t)(q - 1024)) : (uint32_t)q;
+    if (out >= 0x7c00) out = 0x7c00;
+    return sign | (uint16_t)out;
 }
 
 float oracle_f16_to_f32(uint16_t h) {
