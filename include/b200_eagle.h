@@ -77,6 +77,23 @@ int b200_qmm_fused(const void* x, const uint32_t* wq, const void* scales, const 
                    int group_size, int dtype, int epilogue,
                    void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * Streaming ("tiled") weight layout and the matmul kernel that reads it.  b200_qmm_relayout is the
+ * one-off offline re-layout (counterpart of the reference's swizzle.py:41-57 /
+ * kernels/swizzle.metal): records of 16 rows x 128 k = 1152 contiguous bytes, packs in the order the
+ * lanes of a warp consume them followed by the {scale, bias} pairs; `out` needs b200_qmm_tiled_bytes.
+ * b200_qmm_tiled computes the same product and epilogues as b200_qmm_fused (same arithmetic, same
+ * rounding points) from that layout with persistent CTAs and bulk-copy rings; M <= 32, and a
+ * workspace of at least b200_qmm_tiled_workspace_bytes is required (first 4 KiB zero before first use;
+ * the last int of that block is an error flag set if a bounded wait on a bulk copy ever gives up).
+ */
+size_t b200_qmm_tiled_bytes(int N, int K);
+int b200_qmm_relayout(const uint32_t* wq, const void* scales, const void* biases, void* out, int N, int K,
+                      void* stream);
+size_t b200_qmm_tiled_workspace_bytes(int M, int N, int K);
+int b200_qmm_tiled(const void* x, const void* wt, const void* wt2, const void* bias, const void* extra, void* y,
+                   int M, int N, int K, int epilogue, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Per-token model kernels (one decoder layer = rms_norm, qmm(+bias), rope_kv_append,
  * tree_attention, qmm(residual), rms_norm, qmm(silu-mul), qmm(residual)).

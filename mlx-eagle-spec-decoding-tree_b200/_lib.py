@@ -49,6 +49,14 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_qmm_fused.restype = i32
     l.b200_qmm_fused.argtypes = [vp] * 10 + [i32] * 6 + [vp, sz, vp]
     f32, u64 = ctypes.c_float, ctypes.c_ulonglong
+    l.b200_qmm_tiled_bytes.restype = sz
+    l.b200_qmm_tiled_bytes.argtypes = [i32, i32]
+    l.b200_qmm_relayout.restype = i32
+    l.b200_qmm_relayout.argtypes = [vp, vp, vp, vp, i32, i32, vp]
+    l.b200_qmm_tiled_workspace_bytes.restype = sz
+    l.b200_qmm_tiled_workspace_bytes.argtypes = [i32, i32, i32]
+    l.b200_qmm_tiled.restype = i32
+    l.b200_qmm_tiled.argtypes = [vp] * 6 + [i32] * 4 + [vp, sz, vp]
     l.b200_embed_gather.restype = i32
     l.b200_embed_gather.argtypes = [vp] * 5 + [i32] * 3 + [vp]
     l.b200_rms_norm.restype = i32

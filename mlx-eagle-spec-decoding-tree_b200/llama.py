@@ -99,8 +99,18 @@ class QLinear:
         self.out_features = wq.shape[0]
         self.in_features = wq.shape[1] * 8
         self.group_size, self.bits = 64, 4
+        self.tiled = None
+
+    def relayout(self, keep_rowmajor: bool = False):
+        """Build the streaming layout of this layer's weights; drop the row-major tensors unless asked."""
+        self._nbytes = self.nbytes()
+        self.tiled = qk.relayout(self.weight, self.scales, self.biases)
+        if not keep_rowmajor:
+            self.weight = self.scales = self.biases = None
 
     def nbytes(self) -> int:
+        if self.weight is None:
+            return self._nbytes
         n = self.weight.numel() * 4 + self.scales.numel() * 2 + self.biases.numel() * 2
         return n + (self.bias.numel() * 2 if self.bias is not None else 0)
 
@@ -227,6 +237,31 @@ class Model:
     def make_cache(self, rows: int) -> KVCache:
         return KVCache(self.args, rows, self.device)
 
+    def relayout(self):
+        """Re-lay-out every linear layer for the streaming kernel (one-off, at load time).  The
+        embedding keeps its row-major form, which the token gather needs."""
+        for lw in self.layers:
+            for k in ("qkv", "o", "gate", "up", "down"):
+                lw[k].relayout()
+        self.lm_head.relayout(keep_rowmajor=self.lm_head is self.embed)
+        return self
+
+    def _linear(self, x, lin: QLinear, y, M, epilogue, lin2: Optional[QLinear] = None, extra=None):
+        L, p = _lib.lib(), _lib.ptr
+        ws = qk.workspace(self.device)
+        st = _lib.stream_ptr(self.device)
+        if lin.tiled is not None:
+            rc = L.b200_qmm_tiled(p(x), p(lin.tiled), p(lin2.tiled) if lin2 is not None else None, p(lin.bias),
+                                  p(extra), p(y), M, lin.out_features, lin.in_features, epilogue, p(ws), ws.numel(), st)
+            _lib.check(rc, "b200_qmm_tiled")
+        else:
+            l2 = lin2
+            rc = L.b200_qmm_fused(p(x), p(lin.weight), p(lin.scales), p(lin.biases),
+                                  p(l2.weight) if l2 else None, p(l2.scales) if l2 else None,
+                                  p(l2.biases) if l2 else None, p(lin.bias), p(extra), p(y), M, lin.out_features,
+                                  lin.in_features, 64, 0, epilogue, p(ws), ws.numel(), st)
+            _lib.check(rc, "b200_qmm_fused")
+
     # ------------------------------------------------------------------ device-side forward
     def _attention_workspace(self, cache: KVCache):
         if self._attn_ws is None or self._attn_ws_rows < cache.rows:
@@ -261,33 +296,19 @@ class Model:
         for li, lw in enumerate(self.layers):
             kc, vc = cache.layer(li)
             ck(L.b200_rms_norm(p(self.h), p(lw["input_norm"]), p(self.xn), None, M, H, eps, st), "b200_rms_norm")
-            q = lw["qkv"]
-            ck(L.b200_qmm_fused(p(self.xn), p(q.weight), p(q.scales), p(q.biases), None, None, None, p(q.bias),
-                                None, p(self.qkv), M, nqkv, H, 64, 0, qk.EPI_NONE, p(ws), ws.numel(), st), "qmm qkv")
+            self._linear(self.xn, lw["qkv"], self.qkv, M, qk.EPI_NONE)
             ck(L.b200_rope_kv_append(p(self.qkv), p(fwd.pos), p(self.inv_freqs), self.rope_scaling_factor, p(kc),
                                      p(vc), p(fwd.prefix), write_off, M, Hq, Hkv, hd, cache.rows, st), "rope")
             ck(L.b200_tree_attention(p(self.qkv), nqkv, p(kc), p(vc), p(fwd.mask), p(fwd.prefix), tail,
                                      p(self.attn), M, Hq, Hkv, hd, cache.rows, cache.rows, self.scale,
                                      p(aws), aws.numel(), st), "b200_tree_attention")
-            o = lw["o"]
-            ck(L.b200_qmm_fused(p(self.attn), p(o.weight), p(o.scales), p(o.biases), None, None, None, None,
-                                p(self.h), p(self.h), M, H, self.nq, 64, 0, qk.EPI_RESIDUAL, p(ws), ws.numel(), st),
-               "qmm o")
+            self._linear(self.attn, lw["o"], self.h, M, qk.EPI_RESIDUAL, extra=self.h)
             ck(L.b200_rms_norm(p(self.h), p(lw["post_norm"]), p(self.xn), None, M, H, eps, st), "b200_rms_norm")
-            g, u = lw["gate"], lw["up"]
-            ck(L.b200_qmm_fused(p(self.xn), p(g.weight), p(g.scales), p(g.biases), p(u.weight), p(u.scales),
-                                p(u.biases), None, None, p(self.act), M, I, H, 64, 0, qk.EPI_SILU_MUL, p(ws),
-                                ws.numel(), st), "qmm gate/up")
-            d = lw["down"]
-            ck(L.b200_qmm_fused(p(self.act), p(d.weight), p(d.scales), p(d.biases), None, None, None, None,
-                                p(self.h), p(self.h), M, H, I, 64, 0, qk.EPI_RESIDUAL, p(ws), ws.numel(), st),
-               "qmm down")
+            self._linear(self.xn, lw["gate"], self.act, M, qk.EPI_SILU_MUL, lin2=lw["up"])
+            self._linear(self.act, lw["down"], self.h, M, qk.EPI_RESIDUAL, extra=self.h)
         rows = M if logits_rows is None else logits_rows
         ck(L.b200_rms_norm(p(self.h), p(self.norm), p(self.xn), p(row_index), rows, H, eps, st), "final norm")
-        hd_ = self.lm_head
-        ck(L.b200_qmm_fused(p(self.xn), p(hd_.weight), p(hd_.scales), p(hd_.biases), None, None, None, None, None,
-                            p(self.logits), rows, a.vocab_size, H, 64, 0, qk.EPI_NONE, p(ws), ws.numel(), st),
-           "qmm lm_head")
+        self._linear(self.xn, self.lm_head, self.logits, rows, qk.EPI_NONE)
         return self.logits[:rows]
 
     # ------------------------------------------------------------------ reference-style call

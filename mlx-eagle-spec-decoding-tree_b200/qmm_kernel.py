@@ -82,3 +82,34 @@ def matmul_fused(x, w, s, b, *, epilogue=EPI_NONE, w2=None, s2=None, b2=None, bi
 
 def workspace_bytes(m: int, n: int, k: int) -> int:
     return int(_lib.lib().b200_qmm_workspace_bytes(m, n, k))
+
+
+def relayout(w, s, b) -> torch.Tensor:
+    """One-off re-layout of MLX-format 4-bit weights into the streaming ("tiled") layout the fast
+    kernel reads: records of 16 rows x 128 k, lane-ordered packs followed by {scale, bias} pairs.
+    The counterpart of the reference's offline ``swizzle`` (``swizzle.py:41-57``).  Returns a uint8
+    tensor; ``matmul_tiled`` consumes it."""
+    _lib.require_cuda(w, s, b)
+    n, k = w.shape[0], w.shape[1] * 8
+    out = torch.empty(_lib.lib().b200_qmm_tiled_bytes(n, k), dtype=torch.uint8, device=w.device)
+    rc = _lib.lib().b200_qmm_relayout(_lib.ptr(w), _lib.ptr(s), _lib.ptr(b), _lib.ptr(out), n, k,
+                                      _lib.stream_ptr(w.device))
+    _lib.check(rc, "b200_qmm_relayout")
+    return out
+
+
+def matmul_tiled(x, wt, n, *, epilogue=EPI_NONE, wt2=None, bias=None, extra=None, out=None):
+    """``x (M<=32, K) @ W.T`` on re-laid-out weights ``wt`` (from ``relayout``) of ``n`` output rows."""
+    _lib.require_cuda(x, wt)
+    m, k = x.shape
+    y = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=x.device)
+    ws = workspace(x.device)
+    rc = _lib.lib().b200_qmm_tiled(_lib.ptr(x), _lib.ptr(wt), _lib.ptr(wt2), _lib.ptr(bias), _lib.ptr(extra),
+                                   _lib.ptr(y), m, n, k, epilogue, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(x.device))
+    _lib.check(rc, "b200_qmm_tiled")
+    return y
+
+
+def stream_error(device) -> int:
+    """Non-zero if a bounded wait inside the tiled kernel ever gave up on this device (reads the flag)."""
+    return int(workspace(device)[4092:4096].view(torch.int32).item())

@@ -15,7 +15,10 @@ def models(be, cuda):
     draft = be.Model.random_init(args, seed=12, device=cuda, gen_device="cpu")
     base.norm.mul_(8.0)
     draft.norm.mul_(8.0)
-    return args, base, draft
+    states = (base.state_numpy(), draft.state_numpy())
+    base.relayout()          # both models on the streaming weight layout
+    draft.relayout()
+    return args, base, draft, states
 
 
 def _plain_greedy_gpu(model, prompt, n):
@@ -37,14 +40,14 @@ def _first_divergence(a, b):
 
 @pytest.mark.parametrize("self_draft,depth,T", [(False, 3, 15), (True, 3, 15), (True, 4, 31)])
 def test_generation_matches_the_cpu_oracle(be, models, self_draft, depth, T):
-    args, base, draft = models
+    args, base, draft, states = models
     d = base if self_draft else draft
     rng = np.random.default_rng(7)
     prompt = rng.integers(0, args.vocab_size, 33)
     res = be.generate_step(torch.from_numpy(prompt), base, d, depth=depth, verify_num_tokens=T, max_tokens=40, N=40,
                            verbose=False)
-    ob = model_ref.OracleModel(args, base.state_numpy())
-    od = ob if self_draft else model_ref.OracleModel(args, draft.state_numpy())
+    ob = model_ref.OracleModel(args, states[0])
+    od = ob if self_draft else model_ref.OracleModel(args, states[1])
     ref = eagle_ref.generate_step(prompt, ob, od, depth=depth, verify_num_tokens=T, max_tokens=40, N=40)
     div = _first_divergence(res["tokens"], ref["tokens"])
     # Free-running CPU and GPU differ in fp32 summation order; with the sharpened test models the
@@ -57,7 +60,7 @@ def test_generation_matches_the_cpu_oracle(be, models, self_draft, depth, T):
 
 
 def test_graph_replay_equals_eager_and_plain_greedy(be, models):
-    args, base, draft = models
+    args, base, draft, _ = models
     rng = np.random.default_rng(9)
     prompt = torch.from_numpy(rng.integers(0, args.vocab_size, 21))
     g = be.generate_step(prompt, base, draft, depth=3, verify_num_tokens=15, max_tokens=30, N=30, verbose=False)
@@ -69,7 +72,7 @@ def test_graph_replay_equals_eager_and_plain_greedy(be, models):
 
 
 def test_bad_configurations_are_rejected(be, models):
-    _, base, draft = models
+    _, base, draft, _ = models
     with pytest.raises(be._lib.B200Error):
         be.SpecDecoder(base, draft, depth=7, verify_num_tokens=15, cache_rows=256)
     with pytest.raises(be._lib.B200Error):

@@ -122,3 +122,52 @@ def test_rejects_bad_arguments(be, cuda):
         be.qmm_kernel.matmul(x, wq, s, b, 64)          # CPU tensor: no fallback
     with pytest.raises(be._lib.B200Error):
         be.qmm_kernel.matmul(x.to(cuda).float(), wq, s, b, 64)
+
+
+@pytest.mark.parametrize("n,k,m", SHAPES)
+def test_tiled_kernel_matches_oracle_and_rowmajor_kernel(be, cuda, n, k, m):
+    w, x = _case(n, k, m, seed=n * 7 + k + m)
+    wq, s, b = be.quantize.quantize(w)
+    dq = [t.to(cuda) for t in (wq, s, b)]
+    wt = be.qmm_kernel.relayout(*dq)
+    assert wt.numel() == ((n + 15) // 16) * (k // 128) * 1152
+    y = be.qmm_kernel.matmul_tiled(x.to(cuda), wt, n)
+    torch.cuda.synchronize()
+    assert be.qmm_kernel.stream_error(cuda) == 0
+    gold = qmm_ref.qmm_gold(x.numpy(), wq.numpy().view(np.uint32), s.numpy(), b.numpy())
+    got = y.cpu().numpy().astype(np.float64)
+    err = np.abs(got - gold)
+    assert np.all(err <= _tol(gold)), f"max err {err.max()} at {np.unravel_index(err.argmax(), err.shape)}"
+    y_rm = be.qmm_kernel.matmul(x.to(cuda), *dq, 64)[0]
+    assert np.mean(y_rm.cpu().numpy() != y.cpu().numpy()) < 0.05
+
+
+def test_tiled_fused_epilogues_equal_rowmajor_results(be, cuda):
+    qk = be.qmm_kernel
+    for (n, k, m) in [(4864, 896, 16), (18944 // 4, 3584, 32), (4864, 896, 3)]:
+        g = torch.Generator().manual_seed(n + m)
+        wg, wu = torch.randn(n, k, generator=g) * 0.02, torch.randn(n, k, generator=g) * 0.02
+        x = torch.randn(m, k, generator=g).half().to(cuda)
+        bias = torch.randn(n, generator=g).half().to(cuda)
+        res = torch.randn(m, n, generator=g).half().to(cuda)
+        dg = [t.to(cuda) for t in be.quantize.quantize(wg)]
+        du = [t.to(cuda) for t in be.quantize.quantize(wu)]
+        tg, tu = qk.relayout(*dg), qk.relayout(*du)
+        a = qk.matmul_fused(x, *dg, bias=bias)
+        b = qk.matmul_tiled(x, tg, n, bias=bias)
+        assert (a != b).float().mean() < 0.05 and torch.allclose(a.float(), b.float(), rtol=2e-3, atol=2e-3)
+        a = qk.matmul_fused(x, *dg, epilogue=qk.EPI_RESIDUAL, extra=res)
+        b = qk.matmul_tiled(x, tg, n, epilogue=qk.EPI_RESIDUAL, extra=res)
+        assert (a != b).float().mean() < 0.05 and torch.allclose(a.float(), b.float(), rtol=2e-3, atol=2e-3)
+        a = qk.matmul_fused(x, *dg, epilogue=qk.EPI_SILU_MUL, w2=du[0], s2=du[1], b2=du[2])
+        b = qk.matmul_tiled(x, tg, n, epilogue=qk.EPI_SILU_MUL, wt2=tu)
+        assert (a != b).float().mean() < 0.05 and torch.allclose(a.float(), b.float(), rtol=4e-3, atol=2e-3)
+    assert qk.stream_error(cuda) == 0
+
+
+def test_tiled_rows_do_not_depend_on_batch_size(be, cuda):
+    w, x = _case(1152, 896, 8, 21)
+    wt = be.qmm_kernel.relayout(*[t.to(cuda) for t in be.quantize.quantize(w)])
+    y8 = be.qmm_kernel.matmul_tiled(x.to(cuda), wt, 1152)
+    y1 = be.qmm_kernel.matmul_tiled(x[3:4].to(cuda), wt, 1152)
+    assert torch.equal(y8[3:4], y1)

@@ -18,6 +18,7 @@ def models(be, cuda):
     draft = be.Model.random_init(args, seed=12, device=cuda, gen_device="cpu")
     base.norm.mul_(8.0)      # sharper distributions: deep trees, long accepted paths
     draft.norm.mul_(8.0)
+    draft.relayout()         # draft on the streaming weight layout, target on the row-major one
     return args, base, draft
 
 
