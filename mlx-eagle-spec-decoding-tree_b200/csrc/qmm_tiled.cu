@@ -4,18 +4,24 @@
 // is cut into records of 16 rows x 128 k.  A record is 1152 contiguous bytes: 1024 bytes of packs
 // in exactly the order the 32 lanes of a warp consume them (lane (g,t) owns 16 bytes of row g and
 // 16 bytes of row g+8: the packs of k-blocks t, 4+t, 8+t, 12+t), then 128 bytes of {scale, bias}
-// pairs (row-major, two 64-k groups per row).  Records of one 16-row tile are consecutive along K,
-// so a warp streams one contiguous region.
+// pairs (row-major, two 64-k groups per row).  Inside a pack the nibbles are re-ordered so that
+// the mask pairs 0x000f000f, 0x00f000f0 (and the same after >> 8) yield ADJACENT k pairs
+// (k0,k1) (k2,k3) (k4,k5) (k6,k7): the activations can then stay in their natural order.  Records are ordered [64-row block][k chunk][16-row
+// tile of the block], so everything a CTA needs for one k chunk of a 64-row block is one
+// contiguous 4.5 KiB run, and consecutive chunks follow each other.
 //
-// Kernel: persistent CTAs (at most two per SM) loop over (row block, K split) items.  Every warp
-// owns a private ring of shared-memory stages filled by bulk asynchronous copies
-// (cp.async.bulk global -> shared, completion counted on an mbarrier): lane 0 keeps 3-4 stages of
-// 2 records in flight, all lanes wait on the stage's barrier (bounded), read their 16-byte pieces
-// conflict-free, expand nibbles and feed mma.sync m16n8k16 (weights = A operand, tokens = B
-// operand, fp32 accumulate) exactly as the row-major kernel does.  No block-wide barrier sits
-// inside the stream of an item; activations are staged once per item in shared memory.
-// Split-K partial sums, deterministic last-arriver reduction and the fused epilogues are shared
-// with the row-major kernel.  No load in this file uses cluster multicast.
+// Kernel: persistent CTAs (two per SM) loop over (row block, K split) items.  One extra producer
+// warp streams the weights with bulk asynchronous copies (cp.async.bulk global -> shared, completion
+// counted on an mbarrier) into a ring of stages shared by the CTA and runs ahead across item
+// boundaries, so the stream never drains; the consumer warps wait on a stage's "full" barrier
+// (bounded), read their own record conflict-free, expand nibbles and feed mma.sync m16n8k16
+// (weights = A operand, tokens = B operand, fp32 accumulate) exactly as the row-major kernel does,
+// then release the stage on its "empty" barrier.  Split-K partial sums,
+// deterministic last-arriver reduction and the fused epilogues are shared with the row-major
+// kernel.  The activations of a stage's k range travel in the same stage (one bulk copy per token
+// row, issued by one producer lane each, counted on the same barrier), so consumers never synchronise
+// block-wide while streaming; results leave through registers.  Every wait is bounded: on a timeout the CTA raises an error flag in the workspace and
+// skips the remaining work instead of hanging.  No load in this file uses cluster multicast.
 #include "qmm_common.cuh"
 
 namespace b200 {
@@ -24,7 +30,8 @@ namespace {
 constexpr int kRec = 1152;            // bytes per 16-row x 128-k record
 constexpr int kCPS = 2;               // records (chunks) per ring stage and sub-tile
 constexpr int kErrWord = kMaxCounters - 1;   // workspace counter slot used as an error flag
-constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr uint32_t kWaitLimit = 1u << 18;
+constexpr int kBlockRows = 64;       // rows per layout block (4 records per chunk)
 
 struct TiledParams {
     const __half* x;
@@ -67,45 +74,119 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
                  : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+// Arrive on `bar` once all cp.async issued so far by this thread have landed (count pre-charged at init).
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_sync(int nthreads) {       // named barrier 1: consumer warps only
+    asm volatile("bar.sync 1, %0;\n" ::"r"(nthreads) : "memory");
+}
 
 template <int MT, int S, int WN, bool DUAL>
-__global__ void __launch_bounds__(WN * 32, 2) qmm_tiled_kernel(const TiledParams p) {
-    constexpr int KS = (MT == 1) ? 16 : (MT == 2 ? 8 : 4);      // chunks of x resident in smem
-    constexpr int kNST = (S == 1) ? 4 : 3;                      // ring stages per warp
+__global__ void __launch_bounds__((WN + 1) * 32, 2) qmm_tiled_kernel(const TiledParams p) {
     constexpr int RW = DUAL ? 16 : S * 16;
     constexpr int R = WN * RW;
+    constexpr int NB = DUAL ? 2 : R / kBlockRows;               // 64-row blocks a stage holds
+    constexpr int MP = MT * 8;
     constexpr int TW = DUAL ? 2 * R : R;
-    constexpr int XSTRIDE = KS * kChunkK * 2 + 64;
-    constexpr int XBYTES = MT * 8 * XSTRIDE;
-    constexpr int STAGE_BYTES = S * kCPS * kRec;
-    constexpr int RING_BYTES = kNST * STAGE_BYTES;
-    constexpr int TSTRIDE = TW + 1;
-    static_assert(!DUAL || S == 2, "dual mode needs two sub-tiles");
-    static_assert(MT * 8 * TSTRIDE * 4 <= XBYTES, "epilogue tile must fit in the activation slice");
-    static_assert(KS % kCPS == 0, "slice must hold whole stages");
+    constexpr int BLOCK_STAGE = kCPS * 4 * kRec;                // weight bytes of one block in a stage
+    constexpr int XPITCH = kCPS * kChunkK * 2 + 64;             // activation row pitch in a stage
+    constexpr int XOFF = NB * BLOCK_STAGE;
+    constexpr int STAGE_BYTES = XOFF + MP * XPITCH;
+    constexpr int kNST = (MT <= 2) ? 4 : 3;                     // ring stages
+    constexpr int NCONS = WN * 32;
+    static_assert(!DUAL || (S == 2 && WN == 4), "dual mode: two sub-tiles, four consumer warps");
+    static_assert(DUAL || R % kBlockRows == 0, "CTA rows must be whole layout blocks");
 
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_is_last;
-    unsigned char* xs = smem;
-    unsigned char* ring = smem + XBYTES + (threadIdx.x >> 5) * RING_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + XBYTES + WN * RING_BYTES) + (threadIdx.x >> 5) * kNST;
+    __shared__ int s_abort;
+    unsigned char* ring = smem;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kNST * STAGE_BYTES);
+    uint64_t* empty = full + kNST;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int nchunks_total = p.K / kChunkK;
-    const int tiles16 = (p.N + 15) / 16;
+    const int nblocks = (p.N + kBlockRows - 1) / kBlockRows;
     const int nitems = p.row_tiles * p.splits;
 
-    if (lane == 0) {
+    if (threadIdx.x == 0) {
+        s_abort = 0;
 #pragma unroll
-        for (int s = 0; s < kNST; s++) mbar_init(smem_u32(bars + s), 1);
+        for (int s = 0; s < kNST; s++) {
+            mbar_init(smem_u32(full + s), 1);      // lane 0's expect_tx arrive; bytes counted by the copies
+            mbar_init(smem_u32(empty + s), WN);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
+    volatile int* abort_flag = &s_abort;
 
-    uint32_t gstage = 0;     // stages issued == stages consumed at item boundaries (per warp)
-    const int MP = MT * 8;
-    float* tile = reinterpret_cast<float*>(xs);
+    if (warp == WN) {
+        // ------------------------------------------------------------------ producer warp
+        uint32_t ps = 0;
+        for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+            const int row_tile = item % p.row_tiles;
+            const int split = item / p.row_tiles;
+            const int c_begin = split * p.chunks_per_split;
+            const int n = min(p.chunks_per_split, nchunks_total - c_begin);
+            const int nst = (n + kCPS - 1) / kCPS;
+            const unsigned char* src[NB];
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                const int blk = min(DUAL ? row_tile : row_tile * NB + b, nblocks - 1);
+                src[b] = p.wt[DUAL ? b : 0] + ((size_t)blk * nchunks_total + c_begin) * 4 * kRec;
+            }
+            for (int st = 0; st < nst; st++, ps++) {
+                const uint32_t slot = ps % kNST, use = ps / kNST;
+                bool ok = !*abort_flag;
+                if (ok && use > 0 && !mbar_wait_bounded(smem_u32(empty + slot), (use - 1) & 1u)) {
+                    ok = false;
+                    *abort_flag = 1;
+                    if (lane == 0) atomicExch(p.counter + kErrWord, 2);
+                }
+                if (!ok) return;
+                const int recs = min(kCPS, n - st * kCPS);
+                const uint32_t fbar = smem_u32(full + slot);
+                unsigned char* stage = ring + slot * STAGE_BYTES;
+                const uint32_t xbytes = (uint32_t)(recs * kChunkK * 2);           // one activation row of this stage
+                const int xrows = min(p.M, MP);
+                if (lane == 0) {
+                    const uint32_t bytes = (uint32_t)(recs * 4 * kRec);
+                    fence_proxy_async();
+                    mbar_expect_tx(fbar, NB * bytes + (uint32_t)xrows * xbytes);
+#pragma unroll
+                    for (int b = 0; b < NB; b++)
+                        bulk_copy_g2s(smem_u32(stage + b * BLOCK_STAGE), src[b] + (size_t)st * kCPS * 4 * kRec, bytes, fbar);
+                }
+                __syncwarp();
+                // activations of this stage's k range: one bulk copy per token row, one lane per row
+                // (rows >= M are never written: their accumulator columns are discarded)
+                if (lane < xrows)
+                    bulk_copy_g2s(smem_u32(stage + XOFF + lane * XPITCH),
+                                  p.x + (size_t)lane * p.K + (size_t)(c_begin + st * kCPS) * kChunkK, xbytes, fbar);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- consumers
+    uint32_t cs = 0;
+    int rec_off[S];
+#pragma unroll
+    for (int s = 0; s < S; s++) {
+        const int tile_in_cta = DUAL ? warp : warp * S + s;
+        const int b = DUAL ? s : tile_in_cta / 4;
+        const int tib = DUAL ? warp : tile_in_cta % 4;
+        rec_off[s] = b * BLOCK_STAGE + tib * kRec;
+    }
 
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
         const int row_tile = item % p.row_tiles;
@@ -113,28 +194,6 @@ __global__ void __launch_bounds__(WN * 32, 2) qmm_tiled_kernel(const TiledParams
         const int c_begin = split * p.chunks_per_split;
         const int n = min(p.chunks_per_split, nchunks_total - c_begin);
         const int nst = (n + kCPS - 1) / kCPS;
-
-        const unsigned char* src[S];
-#pragma unroll
-        for (int s = 0; s < S; s++) {
-            int t16 = (row_tile * R + warp * RW) / 16 + (DUAL ? 0 : s);
-            t16 = min(t16, tiles16 - 1);
-            src[s] = p.wt[DUAL ? s : 0] + ((size_t)t16 * nchunks_total + c_begin) * kRec;
-        }
-        auto issue = [&](int st) {          // lane 0 only
-            const uint32_t slot = (gstage + st) % kNST;
-            const int recs = min(kCPS, n - st * kCPS);
-            const uint32_t bar = smem_u32(bars + slot);
-            mbar_expect_tx(bar, (uint32_t)(S * recs * kRec));
-#pragma unroll
-            for (int s = 0; s < S; s++)
-                bulk_copy_g2s(smem_u32(ring + slot * STAGE_BYTES + s * kCPS * kRec),
-                              src[s] + (size_t)st * kCPS * kRec, (uint32_t)(recs * kRec), bar);
-        };
-        if (lane == 0) {
-            fence_proxy_async();
-            for (int st = 0; st < min(kNST, nst); st++) issue(st);
-        }
 
         float acc[S][MT][4];
 #pragma unroll
@@ -144,49 +203,25 @@ __global__ void __launch_bounds__(WN * 32, 2) qmm_tiled_kernel(const TiledParams
 #pragma unroll
                 for (int i = 0; i < 4; i++) acc[s][mt][i] = 0.f;
 
-        bool failed = false;
-        for (int st = 0; st < nst; st++) {
-            if ((st * kCPS) % KS == 0) {
-                // activation slice for chunks [st*CPS, +KS) of this item: natural k order, halves of
-                // every 8-block reordered to (0,4,1,5,2,6,3,7) to match the nibble pairs of a pack
-                if (st > 0) __syncthreads();
-                const int c0 = st * kCPS;
-                const int slice_chunks = min(KS, n - c0);
-                const int blocks_per_row = slice_chunks * 16;
-                const int total = MP * blocks_per_row;
-                const __half* xbase = p.x + (size_t)(c_begin + c0) * kChunkK;
-                for (int i = threadIdx.x; i < total; i += WN * 32) {
-                    const int m = i / blocks_per_row;
-                    const int bb = i - m * blocks_per_row;
-                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                    if (m < p.M) v = *reinterpret_cast<const uint4*>(xbase + (size_t)m * p.K + bb * 8);
-                    uint4 o;
-                    o.x = __byte_perm(v.x, v.z, 0x5410);
-                    o.y = __byte_perm(v.x, v.z, 0x7632);
-                    o.z = __byte_perm(v.y, v.w, 0x5410);
-                    o.w = __byte_perm(v.y, v.w, 0x7632);
-                    *reinterpret_cast<uint4*>(xs + (size_t)m * XSTRIDE + bb * 16) = o;
-                }
-                __syncthreads();
-            }
-            const uint32_t gs = gstage + st;
-            const uint32_t slot = gs % kNST;
-            if (!failed && !mbar_wait_bounded(smem_u32(bars + slot), (gs / kNST) & 1u)) {
-                failed = true;
+        for (int st = 0; st < nst; st++, cs++) {
+            const uint32_t slot = cs % kNST;
+            bool ok = !*abort_flag;
+            if (ok && !mbar_wait_bounded(smem_u32(full + slot), (cs / kNST) & 1u)) {
+                ok = false;
+                *abort_flag = 1;
                 if (lane == 0) atomicExch(p.counter + kErrWord, 1);
             }
-            if (!failed) {
+            if (ok) {
                 const unsigned char* stage = ring + slot * STAGE_BYTES;
 #pragma unroll
                 for (int cc = 0; cc < kCPS; cc++) {
                     if (st * kCPS + cc < n) {
-                        const int cslice = (st * kCPS + cc) % KS;
-                        const unsigned char* xrow = xs + (size_t)g * XSTRIDE + cslice * (kChunkK * 2) + t * 16;
+                        const unsigned char* xrow = stage + XOFF + g * XPITCH + cc * (kChunkK * 2) + t * 16;
                         uint4 w[S][2];
                         uint2 sb[S][2];
 #pragma unroll
                         for (int s = 0; s < S; s++) {
-                            const unsigned char* rec = stage + (s * kCPS + cc) * kRec;
+                            const unsigned char* rec = stage + rec_off[s] + cc * 4 * kRec;
                             w[s][0] = *reinterpret_cast<const uint4*>(rec + lane * 16);
                             w[s][1] = *reinterpret_cast<const uint4*>(rec + 512 + lane * 16);
                             sb[s][0] = *reinterpret_cast<const uint2*>(rec + 1024 + g * 8);
@@ -197,16 +232,14 @@ __global__ void __launch_bounds__(WN * 32, 2) qmm_tiled_kernel(const TiledParams
                             uint4 xb[MT];
 #pragma unroll
                             for (int mt = 0; mt < MT; mt++)
-                                xb[mt] = *reinterpret_cast<const uint4*>(xrow + (size_t)mt * 8 * XSTRIDE + j * 64);
+                                xb[mt] = *reinterpret_cast<const uint4*>(xrow + mt * 8 * XPITCH + j * 64);
 #pragma unroll
                             for (int s = 0; s < S; s++) {
-                                const uint32_t p0 = (j < 2) ? sb[s][0].x : sb[s][0].y;
-                                const uint32_t p1 = (j < 2) ? sb[s][1].x : sb[s][1].y;
+                                const __half2 p0 = u32_as_h2((j < 2) ? sb[s][0].x : sb[s][0].y);   // {scale, bias}
+                                const __half2 p1 = u32_as_h2((j < 2) ? sb[s][1].x : sb[s][1].y);
                                 uint32_t d0[4], d1[4];
-                                dequant_pack(comp(w[s][0], j), u32_as_h2(__byte_perm(p0, p0, 0x1010)),
-                                             u32_as_h2(__byte_perm(p0, p0, 0x3232)), d0);
-                                dequant_pack(comp(w[s][1], j), u32_as_h2(__byte_perm(p1, p1, 0x1010)),
-                                             u32_as_h2(__byte_perm(p1, p1, 0x3232)), d1);
+                                dequant_pack(comp(w[s][0], j), __low2half2(p0), __high2half2(p0), d0);
+                                dequant_pack(comp(w[s][1], j), __low2half2(p1), __high2half2(p1), d1);
 #pragma unroll
                                 for (int mt = 0; mt < MT; mt++) {
                                     mma_m16n8k16(acc[s][mt], d0[0], d1[0], d0[1], d1[1], xb[mt].x, xb[mt].y);
@@ -218,20 +251,11 @@ __global__ void __launch_bounds__(WN * 32, 2) qmm_tiled_kernel(const TiledParams
                 }
             }
             __syncwarp();
-            if (lane == 0 && !failed && st + kNST < nst) {
-                fence_proxy_async();
-                issue(st + kNST);
-            }
+            if (lane == 0) mbar_arrive(smem_u32(empty + slot));     // stage free for the producer
         }
-        if (failed && lane == 0) {
-            // give copies still in flight a (bounded) chance to land before this warp moves on
-            for (int st = 0; st < kNST; st++) mbar_wait_bounded(smem_u32(bars + st), ((gstage + nst) / kNST) & 1u);
-        }
-        gstage += (uint32_t)nst;
 
-        // ---- split-K reduction and epilogue (tile overlays the activation slice) --------------
-        __syncthreads();
-        bool do_epilogue = true;
+        // ---- results leave through registers -------------------------------------------------
+        // lane (g,t) holds, per sub-tile and token tile: rows g / g+8 x tokens 2t / 2t+1
         if (p.splits > 1) {
             float* mine = p.partial + ((size_t)split * p.row_tiles + row_tile) * MP * TW;
 #pragma unroll
@@ -247,71 +271,88 @@ __global__ void __launch_bounds__(WN * 32, 2) qmm_tiled_kernel(const TiledParams
                 }
             }
             __threadfence();
-            __syncthreads();
+            consumer_sync(NCONS);
             if (threadIdx.x == 0) {
                 const int old = atomicAdd(p.counter + row_tile, 1);
                 s_is_last = (old == p.splits - 1);
                 if (s_is_last) p.counter[row_tile] = 0;
             }
-            __syncthreads();
-            do_epilogue = s_is_last;
-            if (do_epilogue) {
+            consumer_sync(NCONS);
+            if (s_is_last) {
                 __threadfence();
-                for (int i = threadIdx.x; i < MP * TW; i += WN * 32) {
-                    const int tok = i / TW, ri = i - tok * TW;
-                    float sum = 0.f;
-                    for (int sp = 0; sp < p.splits; sp++)
-                        sum += __ldcg(p.partial + ((size_t)sp * p.row_tiles + row_tile) * MP * TW + i);
-                    tile[tok * TSTRIDE + ri] = sum;
+                // last CTA of the row tile: add the splits in split order, 8 outputs per thread step
+                const int units_per_tok = R / 8;
+                for (int i = threadIdx.x; i < p.M * units_per_tok; i += NCONS) {
+                    const int tok = i / units_per_tok;
+                    const int c0 = (i - tok * units_per_tok) * 8;
+                    const int n0 = row_tile * R + c0;
+                    if (n0 >= p.N) continue;
+                    float a0[8], a1[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) a0[e] = a1[e] = 0.f;
+                    for (int sp = 0; sp < p.splits; sp++) {
+                        const float* src = p.partial + ((size_t)sp * p.row_tiles + row_tile) * MP * TW + (size_t)tok * TW + c0;
+                        const float4 u0 = __ldcg(reinterpret_cast<const float4*>(src));
+                        const float4 u1 = __ldcg(reinterpret_cast<const float4*>(src) + 1);
+                        a0[0] += u0.x; a0[1] += u0.y; a0[2] += u0.z; a0[3] += u0.w;
+                        a0[4] += u1.x; a0[5] += u1.y; a0[6] += u1.z; a0[7] += u1.w;
+                        if (DUAL) {
+                            const float4 v0 = __ldcg(reinterpret_cast<const float4*>(src + R));
+                            const float4 v1 = __ldcg(reinterpret_cast<const float4*>(src + R) + 1);
+                            a1[0] += v0.x; a1[1] += v0.y; a1[2] += v0.z; a1[3] += v0.w;
+                            a1[4] += v1.x; a1[5] += v1.y; a1[6] += v1.z; a1[7] += v1.w;
+                        }
+                    }
+                    __align__(16) __half out[8];
+                    if (DUAL) {
+#pragma unroll
+                        for (int e = 0; e < 8; e++) out[e] = __float2half_rn(silu_mul_f16(a0[e], a1[e]));
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; e++) out[e] = __float2half_rn(a0[e]);
+                        if (p.bias != nullptr) {
+                            uint4 bv = *reinterpret_cast<const uint4*>(p.bias + n0);
+                            const __half* bh = reinterpret_cast<const __half*>(&bv);
+#pragma unroll
+                            for (int e = 0; e < 8; e++) out[e] = __hadd(out[e], bh[e]);
+                        }
+                        if (p.epilogue == B200_EPI_RESIDUAL) {
+                            uint4 rv = __ldcg(reinterpret_cast<const uint4*>(p.extra + (size_t)tok * p.N + n0));
+                            const __half* rh = reinterpret_cast<const __half*>(&rv);
+#pragma unroll
+                            for (int e = 0; e < 8; e++) out[e] = __hadd(rh[e], out[e]);
+                        }
+                    }
+                    *reinterpret_cast<uint4*>(p.y + (size_t)tok * p.N + n0) = *reinterpret_cast<const uint4*>(out);
                 }
             }
+            consumer_sync(NCONS);     // s_is_last is rewritten by the next item
         } else {
+            constexpr int SS = DUAL ? 1 : S;
 #pragma unroll
-            for (int s = 0; s < S; s++) {
-                const int ri = DUAL ? (s * R + warp * 16) : (warp * RW + s * 16);
+            for (int s = 0; s < SS; s++) {
+                const int nbase = row_tile * R + (DUAL ? warp * 16 : warp * RW + s * 16) + g;
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++) {
-                    const int tok = mt * 8 + 2 * t;
-                    tile[tok * TSTRIDE + ri + g] = acc[s][mt][0];
-                    tile[(tok + 1) * TSTRIDE + ri + g] = acc[s][mt][1];
-                    tile[tok * TSTRIDE + ri + g + 8] = acc[s][mt][2];
-                    tile[(tok + 1) * TSTRIDE + ri + g + 8] = acc[s][mt][3];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int tok = mt * 8 + 2 * t + (i & 1);
+                        const int nn = nbase + ((i >> 1) ? 8 : 0);
+                        if (tok >= p.M || nn >= p.N) continue;
+                        __half o;
+                        if (DUAL) {
+                            o = __float2half_rn(silu_mul_f16(acc[0][mt][i], acc[S - 1][mt][i]));
+                        } else {
+                            o = __float2half_rn(acc[s][mt][i]);
+                            if (p.bias != nullptr) o = __hadd(o, p.bias[nn]);
+                            if (p.epilogue == B200_EPI_RESIDUAL)
+                                o = __hadd(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(p.extra) + (size_t)tok * p.N + nn)), o);
+                        }
+                        p.y[(size_t)tok * p.N + nn] = o;
+                    }
                 }
             }
         }
-        if (do_epilogue) {
-            __syncthreads();
-            const int units_per_tok = R / 8;
-            for (int i = threadIdx.x; i < p.M * units_per_tok; i += WN * 32) {
-                const int tok = i / units_per_tok;
-                const int c0 = (i - tok * units_per_tok) * 8;
-                const int n0 = row_tile * R + c0;
-                if (n0 >= p.N) continue;
-                __align__(16) __half out[8];
-                if (DUAL) {
-#pragma unroll
-                    for (int e = 0; e < 8; e++)
-                        out[e] = __float2half_rn(silu_mul_f16(tile[tok * TSTRIDE + c0 + e], tile[tok * TSTRIDE + R + c0 + e]));
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 8; e++) out[e] = __float2half_rn(tile[tok * TSTRIDE + c0 + e]);
-                    if (p.bias != nullptr) {
-                        uint4 bv = *reinterpret_cast<const uint4*>(p.bias + n0);
-                        const __half* bh = reinterpret_cast<const __half*>(&bv);
-#pragma unroll
-                        for (int e = 0; e < 8; e++) out[e] = __hadd(out[e], bh[e]);
-                    }
-                    if (p.epilogue == B200_EPI_RESIDUAL) {
-                        uint4 rv = *reinterpret_cast<const uint4*>(p.extra + (size_t)tok * p.N + n0);
-                        const __half* rh = reinterpret_cast<const __half*>(&rv);
-#pragma unroll
-                        for (int e = 0; e < 8; e++) out[e] = __hadd(rh[e], out[e]);
-                    }
-                }
-                *reinterpret_cast<uint4*>(p.y + (size_t)tok * p.N + n0) = *reinterpret_cast<const uint4*>(out);
-            }
-        }
-        __syncthreads();      // tile / activation slice free for the next item
     }
 }
 
@@ -319,14 +360,21 @@ __global__ void __launch_bounds__(WN * 32, 2) qmm_tiled_kernel(const TiledParams
 __global__ void relayout_kernel(const uint32_t* __restrict__ wq, const __half* __restrict__ scales,
                                 const __half* __restrict__ biases, uint32_t* __restrict__ out, int N, int K) {
     const int nchunks = K / kChunkK;
-    const int rec = blockIdx.x;                 // t16 * nchunks + c
-    const int t16 = rec / nchunks, c = rec - t16 * nchunks;
+    const int rec = blockIdx.x;                 // (block64 * nchunks + c) * 4 + tile in block
+    const int tib = rec & 3, bc = rec >> 2;
+    const int blk = bc / nchunks, c = bc - blk * nchunks;
+    const int t16 = blk * 4 + tib;
     const int i = threadIdx.x;                  // 0..287: u32 index inside the record
     uint32_t v = 0;
     if (i < 256) {
         const int hh = i >> 7, lane = (i >> 2) & 31, j = i & 3;
         const int row = t16 * 16 + (lane >> 2) + 8 * hh;
-        if (row < N) v = wq[(size_t)row * (K / 8) + c * 16 + j * 4 + (lane & 3)];
+        if (row < N) {
+            const uint32_t w = wq[(size_t)row * (K / 8) + c * 16 + j * 4 + (lane & 3)];
+            // element e (bits 4e..4e+3 in the MLX pack) moves to nibble (e >> 1) + 4 * (e & 1)
+#pragma unroll
+            for (int e = 0; e < 8; e++) v |= ((w >> (4 * e)) & 0xfu) << (4 * ((e >> 1) + 4 * (e & 1)));
+        }
     } else {
         const int q = i - 256, row = t16 * 16 + (q >> 1), grp = q & 1;
         if (row < N) {
@@ -384,10 +432,10 @@ TPlan make_tplan(int M, int N, int K, bool dual, long long ws_bytes) {
     pl.chunks_per_split = (nchunks + splits - 1) / splits;
     pl.splits = (nchunks + pl.chunks_per_split - 1) / pl.chunks_per_split;
     pl.partial_bytes = pbytes(pl.splits);
-    const int ks = pl.mt == 1 ? 16 : (pl.mt == 2 ? 8 : 4);
-    const int nst = S == 1 ? 4 : 3;
-    pl.smem_bytes = (size_t)pl.mt * 8 * (ks * kChunkK * 2 + 64) + (size_t)pl.wn * nst * S * kCPS * kRec +
-                    (size_t)pl.wn * nst * 8;
+    const int nb = dual ? 2 : pl.rows_per_cta / kBlockRows;
+    const int nst = pl.mt <= 2 ? 4 : 3;
+    pl.smem_bytes = (size_t)nst * ((size_t)nb * kCPS * 4 * kRec + (size_t)pl.mt * 8 * (kCPS * kChunkK * 2 + 64)) +
+                    (size_t)nst * 16;
     const int items = pl.row_tiles * pl.splits;
     pl.grid = items < slots ? items : slots;
     return pl;
@@ -398,19 +446,23 @@ int launch_t(const TiledParams& p, const TPlan& pl, cudaStream_t stream) {
     auto kern = qmm_tiled_kernel<MT, S, WN, DUAL>;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 111 * 1024) != cudaSuccess)
             return check_launch();
         attr_set = true;
     }
-    kern<<<pl.grid, WN * 32, pl.smem_bytes, stream>>>(p);
+    kern<<<pl.grid, (WN + 1) * 32, pl.smem_bytes, stream>>>(p);
     return check_launch();
 }
 
 template <int MT>
 int launch_tmt(const TiledParams& p, const TPlan& pl, bool dual, cudaStream_t stream) {
     constexpr int S = (MT >= 3) ? 2 : 1;
-    if (dual) return pl.wn == 8 ? launch_t<MT, 2, 8, true>(p, pl, stream) : launch_t<MT, 2, 4, true>(p, pl, stream);
-    return pl.wn == 8 ? launch_t<MT, S, 8, false>(p, pl, stream) : launch_t<MT, S, 4, false>(p, pl, stream);
+    if (dual) return launch_t<MT, 2, 4, true>(p, pl, stream);
+    if constexpr (S == 2) {
+        return launch_t<MT, S, 4, false>(p, pl, stream);
+    } else {
+        return pl.wn == 8 ? launch_t<MT, S, 8, false>(p, pl, stream) : launch_t<MT, S, 4, false>(p, pl, stream);
+    }
 }
 
 }  // namespace
@@ -420,14 +472,14 @@ extern "C" {
 
 size_t b200_qmm_tiled_bytes(int N, int K) {
     if (N < 1 || K < b200::kChunkK || (K % b200::kChunkK) != 0) return 0;
-    return (size_t)((N + 15) / 16) * (K / b200::kChunkK) * b200::kRec;
+    return (size_t)((N + b200::kBlockRows - 1) / b200::kBlockRows) * (K / b200::kChunkK) * 4 * b200::kRec;
 }
 
 int b200_qmm_relayout(const uint32_t* wq, const void* scales, const void* biases, void* out, int N, int K,
                       void* stream) {
     if (!wq || !scales || !biases || !out || N < 1 || K < b200::kChunkK || (K % b200::kChunkK) != 0) return B200_EINVAL;
     if (!b200::aligned16(out)) return B200_EALIGN;
-    const int recs = ((N + 15) / 16) * (K / b200::kChunkK);
+    const int recs = ((N + b200::kBlockRows - 1) / b200::kBlockRows) * (K / b200::kChunkK) * 4;
     b200::relayout_kernel<<<recs, b200::kRec / 4, 0, static_cast<cudaStream_t>(stream)>>>(
         wq, static_cast<const __half*>(scales), static_cast<const __half*>(biases), static_cast<uint32_t*>(out), N, K);
     return b200::check_launch();

@@ -130,7 +130,7 @@ def test_tiled_kernel_matches_oracle_and_rowmajor_kernel(be, cuda, n, k, m):
     wq, s, b = be.quantize.quantize(w)
     dq = [t.to(cuda) for t in (wq, s, b)]
     wt = be.qmm_kernel.relayout(*dq)
-    assert wt.numel() == ((n + 15) // 16) * (k // 128) * 1152
+    assert wt.numel() == ((n + 63) // 64) * (k // 128) * 4 * 1152
     y = be.qmm_kernel.matmul_tiled(x.to(cuda), wt, n)
     torch.cuda.synchronize()
     assert be.qmm_kernel.stream_error(cuda) == 0
