@@ -101,29 +101,18 @@ def _qmm_bytes(m, n, k, bias=False):
 
 def qmm_roofline(be, torch, model, rows, reps):
     """Time the quantised-matmul launches of one target pass (all layers + head) as one CUDA graph."""
-    qk, L, p = be.qmm_kernel, be._lib.lib(), be._lib.ptr
+    qk = be.qmm_kernel
     a = model.args
     H, I = a.hidden_size, a.intermediate_size
     nqkv = model.nq + 2 * model.nkv
-    ws = qk.workspace(model.device)
-    launches, alg = 0, 0
 
     def sweep():
-        nonlocal launches, alg
-        st = be._lib.stream_ptr(model.device)
         for lw in model.layers:
-            q, o, g, u, d = lw["qkv"], lw["o"], lw["gate"], lw["up"], lw["down"]
-            L.b200_qmm_fused(p(model.xn), p(q.weight), p(q.scales), p(q.biases), None, None, None, p(q.bias), None,
-                             p(model.qkv), rows, nqkv, H, 64, 0, 0, p(ws), ws.numel(), st)
-            L.b200_qmm_fused(p(model.attn), p(o.weight), p(o.scales), p(o.biases), None, None, None, None,
-                             p(model.h), p(model.h), rows, H, model.nq, 64, 0, 1, p(ws), ws.numel(), st)
-            L.b200_qmm_fused(p(model.xn), p(g.weight), p(g.scales), p(g.biases), p(u.weight), p(u.scales),
-                             p(u.biases), None, None, p(model.act), rows, I, H, 64, 0, 2, p(ws), ws.numel(), st)
-            L.b200_qmm_fused(p(model.act), p(d.weight), p(d.scales), p(d.biases), None, None, None, None,
-                             p(model.h), p(model.h), rows, H, I, 64, 0, 1, p(ws), ws.numel(), st)
-        hd = model.lm_head
-        L.b200_qmm_fused(p(model.xn), p(hd.weight), p(hd.scales), p(hd.biases), None, None, None, None, None,
-                         p(model.logits), rows, a.vocab_size, H, 64, 0, 0, p(ws), ws.numel(), st)
+            model._linear(model.xn, lw["qkv"], model.qkv, rows, qk.EPI_NONE)
+            model._linear(model.attn, lw["o"], model.h, rows, qk.EPI_RESIDUAL, extra=model.h)
+            model._linear(model.xn, lw["gate"], model.act, rows, qk.EPI_SILU_MUL, lin2=lw["up"])
+            model._linear(model.act, lw["down"], model.h, rows, qk.EPI_RESIDUAL, extra=model.h)
+        model._linear(model.xn, model.lm_head, model.logits, rows, qk.EPI_NONE)
 
     nl = len(model.layers)
     resid = 2 * rows * H                                         # residual rows read by the epilogue
@@ -260,8 +249,8 @@ def main():
     warmup = max(args.warmup, 3)
     K = args.steps
 
-    draft = be.Model.random_init(be.shape_preset("qwen2-0.5b"), seed=1000 + rank, device=dev)
-    base = be.Model.random_init(be.shape_preset("qwen2-7b"), seed=2000 + rank, device=dev)
+    draft = be.Model.random_init(be.shape_preset("qwen2-0.5b"), seed=1000 + rank, device=dev).relayout()
+    base = be.Model.random_init(be.shape_preset("qwen2-7b"), seed=2000 + rank, device=dev).relayout()
     rows = ((PROMPT + 8 * (warmup + K + DEPTH + 8) + VERIFY + 128 + 63) // 64) * 64
     dec = be.SpecDecoder(base, draft, DEPTH, VERIFY, cache_rows=rows, max_out_tokens=8 * (warmup + K) + 512,
                          max_steps=warmup + K + 64)
@@ -335,7 +324,7 @@ def main():
             "gpu_launches": dec.kernel_launches_per_step * K,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": peak_src,
-                         "kernel": f"qmm_kernel, {qmm_launches} launches of one target pass at {VERIFY + 1} rows",
+                         "kernel": f"qmm_tiled_kernel, {qmm_launches} launches of one target pass at {VERIFY + 1} rows",
                          "algorithmic_bytes_per_launch": alg / qmm_launches, "us_per_launch": 1e6 * qsec / qmm_launches},
         }
         if not args.no_cpu_baseline and world == 1:

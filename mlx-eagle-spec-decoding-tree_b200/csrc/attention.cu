@@ -10,8 +10,8 @@
 // Work split: grid (key blocks of 64, kv heads).  A CTA loads its K/V block once into shared
 // memory and serves all query heads of the group (M*G query rows, tiles of 16 rows per warp) with
 // mma.sync m16n8k16: S = Q K^T (fp32), masked softmax statistics in fp32, P rounded to fp16,
-// O = P V (fp32).  Partial (max, sum, O) go to a workspace; the last CTA of a kv head merges the
-// key blocks in block order and writes fp16.  Key blocks past the current length exit at once, so
+// O = P V (fp32).  Partial (max, sum, O) go to a workspace; a second small kernel (one warp per
+// token and query head) merges the key blocks in block order and writes fp16.  Key blocks past the current length exit at once, so
 // one launch shape serves a growing cache (CUDA-graph friendly: the length is read on the device).
 #include "common.cuh"
 
@@ -48,15 +48,12 @@ __global__ void __launch_bounds__(128) tree_attention_kernel(const AttnParams p)
     constexpr int KS = HD + 8;                       // padded smem row (halves)
     __shared__ __align__(16) __half sk[kKeyBlock * KS];
     __shared__ __align__(16) __half sv[kKeyBlock * KS];
-    __shared__ int s_is_last;
-
     const int kb = blockIdx.x;
     const int hk = blockIdx.y;
     const int prefix = p.prefix[0];
     const int total = prefix + p.tail;
     const int key0 = kb * kKeyBlock;
     if (key0 >= total) return;
-    const int nact = (total + kKeyBlock - 1) / kKeyBlock;
     const int G = p.Hq / p.Hkv;
     const int QR = p.M * G;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -186,43 +183,54 @@ __global__ void __launch_bounds__(128) tree_attention_kernel(const AttnParams p)
                 *reinterpret_cast<float2*>(po + (size_t)r1 * HD + nd * 8 + 2 * t) = make_float2(o[nd][2], o[nd][3]);
         }
     }
+}
 
-    // ---- merge of the key blocks by the last CTA of this kv head -------------------------------
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int old = atomicAdd(p.counter + hk, 1);
-        s_is_last = (old == nact - 1);
-        if (s_is_last) p.counter[hk] = 0;
-    }
-    __syncthreads();
-    if (!s_is_last) return;
-    __threadfence();
+// Merge of the key blocks: one warp per (token, query head) row.  Lanes first share the per-block
+// (max, sum) pairs to get the softmax weights of the blocks, then add the partial outputs in block
+// order and write fp16.
+template <int HD>
+__global__ void __launch_bounds__(128) tree_attention_merge_kernel(const AttnParams p) {
+    const int lane = threadIdx.x & 31;
+    const int row_global = blockIdx.x * 4 + (threadIdx.x >> 5);       // m * Hq + head
+    if (row_global >= p.M * p.Hq) return;
+    const int G = p.Hq / p.Hkv;
+    const int m = row_global / p.Hq, head = row_global - m * p.Hq;
+    const int hk = head / G, gq = head - hk * G;
+    const int r = m * G + gq;
+    const int total = p.prefix[0] + p.tail;
+    const int nact = (total + kKeyBlock - 1) / kKeyBlock;
     const float* ho = p.part_o + (size_t)hk * p.nkb * p.qrp * HD;
     const float* hml = p.part_ml + (size_t)hk * p.nkb * p.qrp * 2;
-    constexpr int CPT = HD / 32;                     // columns per lane
-    for (int r = warp; r < QR; r += 4) {
-        float mstar = -INFINITY;
-        for (int b = 0; b < nact; b++) mstar = fmaxf(mstar, __ldcg(hml + ((size_t)b * p.qrp + r) * 2));
-        float denom = 0.f;
-        float acc[CPT];
+    constexpr int CPT = HD / 32;
+    float mstar = -INFINITY;
+    for (int b = lane; b < nact; b += 32) mstar = fmaxf(mstar, __ldcg(hml + ((size_t)b * p.qrp + r) * 2));
 #pragma unroll
-        for (int c = 0; c < CPT; c++) acc[c] = 0.f;
-        for (int b = 0; b < nact; b++) {
+    for (int o = 16; o > 0; o >>= 1) mstar = fmaxf(mstar, __shfl_xor_sync(0xffffffffu, mstar, o));
+    float denom = 0.f;
+    float acc[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; c++) acc[c] = 0.f;
+    for (int b0 = 0; b0 < nact; b0 += 32) {
+        const int b = b0 + lane;
+        float wl = 0.f, ll = 0.f;
+        if (b < nact) {
             const float mb = __ldcg(hml + ((size_t)b * p.qrp + r) * 2);
-            const float lb = __ldcg(hml + ((size_t)b * p.qrp + r) * 2 + 1);
-            const float w = (mb == -INFINITY) ? 0.f : exp2f(mb - mstar);
-            denom += lb * w;
-#pragma unroll
-            for (int c = 0; c < CPT; c++)
-                acc[c] += w * __ldcg(ho + ((size_t)b * p.qrp + r) * HD + lane + 32 * c);
+            ll = __ldcg(hml + ((size_t)b * p.qrp + r) * 2 + 1);
+            wl = (mb == -INFINITY) ? 0.f : exp2f(mb - mstar);
         }
-        const float inv = denom > 0.f ? 1.f / denom : 0.f;
-        const int m = r / G, gq = r - m * G;
-        __half* orow = p.out + (size_t)m * p.Hq * HD + (size_t)(hk * G + gq) * HD;
+        const int cnt = min(32, nact - b0);
+        for (int i = 0; i < cnt; i++) {
+            const float w = __shfl_sync(0xffffffffu, wl, i);
+            denom += __shfl_sync(0xffffffffu, ll, i) * w;
+            const float* src = ho + ((size_t)(b0 + i) * p.qrp + r) * HD + lane;
 #pragma unroll
-        for (int c = 0; c < CPT; c++) orow[lane + 32 * c] = __float2half_rn(acc[c] * inv);
+            for (int c = 0; c < CPT; c++) acc[c] += w * __ldcg(src + 32 * c);
+        }
     }
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    __half* orow = p.out + (size_t)m * p.Hq * HD + (size_t)head * HD;
+#pragma unroll
+    for (int c = 0; c < CPT; c++) orow[lane + 32 * c] = __float2half_rn(acc[c] * inv);
 }
 
 }  // namespace
@@ -269,8 +277,14 @@ int b200_tree_attention(const void* q, int q_stride, const void* kcache, const v
     p.scale_log2 = scale * b200::kLog2e;
     dim3 grid(p.nkb, Hkv);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (hd == 128) b200::tree_attention_kernel<128><<<grid, 128, 0, st>>>(p);
-    else b200::tree_attention_kernel<64><<<grid, 128, 0, st>>>(p);
+    const int merge_blocks = (M * Hq + 3) / 4;
+    if (hd == 128) {
+        b200::tree_attention_kernel<128><<<grid, 128, 0, st>>>(p);
+        b200::tree_attention_merge_kernel<128><<<merge_blocks, 128, 0, st>>>(p);
+    } else {
+        b200::tree_attention_kernel<64><<<grid, 128, 0, st>>>(p);
+        b200::tree_attention_merge_kernel<64><<<merge_blocks, 128, 0, st>>>(p);
+    }
     return b200::check_launch();
 }
 

@@ -99,7 +99,7 @@ __global__ void __launch_bounds__((WN + 1) * 32, 2) qmm_tiled_kernel(const Tiled
     constexpr int XPITCH = kCPS * kChunkK * 2 + 64;             // activation row pitch in a stage
     constexpr int XOFF = NB * BLOCK_STAGE;
     constexpr int STAGE_BYTES = XOFF + MP * XPITCH;
-    constexpr int kNST = (MT <= 2) ? 4 : 3;                     // ring stages
+    constexpr int kNST = (NB == 4) ? 2 : ((MT <= 2 && S == 1) ? 4 : 3);   // ring stages
     constexpr int NCONS = WN * 32;
     static_assert(!DUAL || (S == 2 && WN == 4), "dual mode: two sub-tiles, four consumer warps");
     static_assert(DUAL || R % kBlockRows == 0, "CTA rows must be whole layout blocks");
@@ -387,7 +387,7 @@ __global__ void relayout_kernel(const uint32_t* __restrict__ wq, const __half* _
 }
 
 struct TPlan {
-    int mt, wn, splits, chunks_per_split, row_tiles, rows_per_cta, tile_width, grid;
+    int mt, wn, s, splits, chunks_per_split, row_tiles, rows_per_cta, tile_width, grid;
     size_t smem_bytes, partial_bytes;
 };
 
@@ -406,13 +406,19 @@ int sms() {
 TPlan make_tplan(int M, int N, int K, bool dual, long long ws_bytes) {
     TPlan pl{};
     pl.mt = (M + 7) / 8;
-    const int S = dual ? 2 : (pl.mt >= 3 ? 2 : 1);
+    const int slots0 = 2 * sms();
+    // 9..16 rows: two sub-tiles per warp halve the activation traffic from shared memory; worth it
+    // when 256-row blocks alone give every SM work (the vocabulary projection)
+    const bool wide16 = !dual && pl.mt == 2 && (N + 255) / 256 >= slots0 / 2;
+    const int S = dual ? 2 : ((pl.mt >= 3 || wide16) ? 2 : 1);
     const int rw = dual ? 16 : S * 16;
     const int slots = 2 * sms();                       // resident CTAs: one wave of the persistent grid
     const int nchunks = K / kChunkK;
     // two 16-row sub-tiles per warp need twice the ring: four warps then; otherwise eight warps when
     // that alone gives every SM a row block
     pl.wn = (S == 1 && (N + 8 * rw - 1) / (8 * rw) >= slots / 2) ? 8 : 4;
+    if (wide16) pl.wn = 8;
+    pl.s = S;
     pl.rows_per_cta = pl.wn * rw;
     pl.tile_width = dual ? 2 * pl.rows_per_cta : pl.rows_per_cta;
     pl.row_tiles = (N + pl.rows_per_cta - 1) / pl.rows_per_cta;
@@ -433,7 +439,7 @@ TPlan make_tplan(int M, int N, int K, bool dual, long long ws_bytes) {
     pl.splits = (nchunks + pl.chunks_per_split - 1) / pl.chunks_per_split;
     pl.partial_bytes = pbytes(pl.splits);
     const int nb = dual ? 2 : pl.rows_per_cta / kBlockRows;
-    const int nst = pl.mt <= 2 ? 4 : 3;
+    const int nst = nb == 4 ? 2 : ((pl.mt <= 2 && S == 1) ? 4 : 3);
     pl.smem_bytes = (size_t)nst * ((size_t)nb * kCPS * 4 * kRec + (size_t)pl.mt * 8 * (kCPS * kChunkK * 2 + 64)) +
                     (size_t)nst * 16;
     const int items = pl.row_tiles * pl.splits;
@@ -458,6 +464,9 @@ template <int MT>
 int launch_tmt(const TiledParams& p, const TPlan& pl, bool dual, cudaStream_t stream) {
     constexpr int S = (MT >= 3) ? 2 : 1;
     if (dual) return launch_t<MT, 2, 4, true>(p, pl, stream);
+    if constexpr (MT == 2) {
+        if (pl.s == 2) return pl.wn == 8 ? launch_t<2, 2, 8, false>(p, pl, stream) : launch_t<2, 2, 4, false>(p, pl, stream);
+    }
     if constexpr (S == 2) {
         return launch_t<MT, S, 4, false>(p, pl, stream);
     } else {

@@ -4,9 +4,9 @@
 (``mlx_llama.py:298-313``): explicit additive mask, integer or per-token array
 positions, ``flat_rope`` giving every token of the call the same position.  All
 linear layers are 4-bit / group-64 quantised and run through ``libb200eagle.so``;
-q/k/v are stored as one fused matrix, so one layer is eight kernel launches:
+q/k/v are stored as one fused matrix, so one layer is nine kernel launches:
 
-    rms_norm -> qmm(+bias) -> rope_kv_append -> tree_attention -> qmm(+residual)
+    rms_norm -> qmm(+bias) -> rope_kv_append -> tree_attention (+ merge) -> qmm(+residual)
     -> rms_norm -> qmm(SiLU(gate)*up) -> qmm(+residual)
 
 The decode loop does not go through ``__call__`` but through ``forward_device``,
@@ -176,7 +176,7 @@ class Model:
         self._attn_ws = None
         self._attn_ws_rows = 0
         self.fwd = FwdInputs(self.device)
-        self.launches_per_forward = 8 * args.num_hidden_layers + 3
+        self.launches_per_forward = 9 * args.num_hidden_layers + 3      # attention = 2 kernels
 
     # ------------------------------------------------------------------ construction
     @staticmethod
