@@ -28,6 +28,7 @@ extern "C" {
 #define B200_EUNSUPPORTED (-3) /* dtype / group size / bits not implemented      */
 #define B200_EWORKSPACE (-4)  /* workspace too small for the requested launch   */
 #define B200_ECUDA (-5)       /* CUDA runtime error; see b200_last_cuda_error() */
+#define B200_ELIMIT (-6)      /* problem larger than a fixed built-in limit       */
 
 #define B200_DTYPE_F16 0
 
@@ -76,6 +77,28 @@ int b200_qmm_fused(const void* x, const uint32_t* wq, const void* scales, const 
                    const void* bias, const void* extra, void* y, int M, int N, int K,
                    int group_size, int dtype, int epilogue,
                    void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * b200_qmm for callers that must not allocate.  (No counterpart in the reference: it exists for
+ * hosts that embed this library where device allocation is off limits - a serving process whose
+ * memory pool is owned by another runtime and handed out in full at start-up, a plug-in loaded into
+ * a process that forbids cudaMalloc after initialisation, or code that runs where the CUDA
+ * allocator may not be entered.)  Same product and arguments as b200_qmm with at most 32 rows, but
+ * the split-K scratch is a fixed 4 MiB array inside the library image instead of a caller buffer:
+ * nothing is allocated or freed, by this call or by anything it calls.  Every GPU that loads the
+ * library carries those 4 MiB until the process exits.
+ *   - Problems whose scratch need (b200_qmm_workspace_bytes) exceeds
+ *     b200_qmm_noalloc_max_scratch_bytes() are refused with B200_ELIMIT; nothing is launched
+ *     (e.g. 32 rows x 4608 x 3584 wants 5.6 MiB: use b200_qmm with a caller buffer for those).
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents; the call
+ *     re-zeroes the part that must start at zero.  Two calls that overlap on the GPU (different
+ *     streams, no ordering) race on it: order them.
+ */
+size_t b200_qmm_noalloc_max_scratch_bytes(void);
+int b200_qmm_noalloc(const void* x, const uint32_t* wq, const void* scales, const void* biases,
+                     const void* bias, void* y, int M, int N, int K, int group_size, int dtype, void* stream);
 
 /*
  * Streaming ("tiled") weight layout and the matmul kernel that reads it.  b200_qmm_relayout is the

@@ -49,6 +49,9 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_qmm_fused.restype = i32
     l.b200_qmm_fused.argtypes = [vp] * 10 + [i32] * 6 + [vp, sz, vp]
     f32, u64 = ctypes.c_float, ctypes.c_ulonglong
+    l.b200_qmm_noalloc_max_scratch_bytes.restype = sz
+    l.b200_qmm_noalloc.restype = i32
+    l.b200_qmm_noalloc.argtypes = [vp] * 6 + [i32] * 5 + [vp]
     l.b200_qmm_tiled_bytes.restype = sz
     l.b200_qmm_tiled_bytes.argtypes = [i32, i32]
     l.b200_qmm_relayout.restype = i32

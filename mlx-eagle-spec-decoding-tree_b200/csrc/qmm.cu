@@ -372,6 +372,36 @@ int qmm_launch(const void* x, const uint32_t* wq, const void* scales, const void
     }
 }
 
+// Scratch of the allocation-free entry point: lives in the library image, one copy per GPU that
+// loads the library, held until the process exits.
+constexpr size_t kStaticScratchBytes = 4u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};
+
+// Device address of the static scratch on the CURRENT device.  The array's name is only a host-side
+// handle; the address a kernel may use has to be asked from the runtime, once per device.
+int static_scratch_address(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        g_last_cuda_error = (int)e;
+        return B200_ECUDA;
+    }
+    if (dev < 0 || dev >= kMaxDevices) return B200_EINVAL;
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            g_last_cuda_error = (int)e;
+            return B200_ECUDA;
+        }
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return B200_OK;
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -414,6 +444,28 @@ int b200_qmm_fused(const void* x, const uint32_t* wq, const void* scales, const 
     return b200::qmm_launch(x, wq, scales, biases, wq2, scales2, biases2, bias, extra, y, M, N, K,
                             group_size, dtype, epilogue, workspace, workspace_bytes,
                             static_cast<cudaStream_t>(stream));
+}
+
+size_t b200_qmm_noalloc_max_scratch_bytes(void) { return b200::kStaticScratchBytes; }
+
+int b200_qmm_noalloc(const void* x, const uint32_t* wq, const void* scales, const void* biases,
+                     const void* bias, void* y, int M, int N, int K, int group_size, int dtype, void* stream) {
+    if (M < 1 || M > 32) return B200_EINVAL;
+    // The problem must fit the fixed scratch with the split it would normally use; no silent downgrade.
+    const size_t need = b200_qmm_workspace_bytes(M, N, K);
+    if (need > b200::kStaticScratchBytes) return B200_ELIMIT;
+    void* scratch = nullptr;
+    int rc = b200::static_scratch_address(&scratch);
+    if (rc != B200_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left; the tile counters at its head must start at zero.
+    cudaError_t e = cudaMemsetAsync(scratch, 0, b200::kCounterBytes, st);
+    if (e != cudaSuccess) {
+        b200::g_last_cuda_error = (int)e;
+        return B200_ECUDA;
+    }
+    return b200::qmm_launch(x, wq, scales, biases, nullptr, nullptr, nullptr, bias, nullptr, y, M, N, K,
+                            group_size, dtype, B200_EPI_NONE, scratch, b200::kStaticScratchBytes, st);
 }
 
 }  // extern "C"
