@@ -228,6 +228,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--roofline-only", action="store_true",
+                    help="only the quantised-matmul sweep of the target model (small profiling case)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -249,6 +251,13 @@ def main():
     warmup = max(args.warmup, 3)
     K = args.steps
 
+    if args.roofline_only:
+        base = be.Model.random_init(be.shape_preset("qwen2-7b"), seed=2000, device=dev).relayout()
+        peak, peak_src = _peaks()
+        alg, launches, qsec = qmm_roofline(be, torch, base, VERIFY + 1, reps=max(1, min(args.steps, 20)))
+        print(json.dumps({"roofline_only": True, "achieved_gbs": alg / qsec / 1e9, "peak": peak,
+                          "frac": alg / qsec / 1e9 / peak, "launches": launches, "us_per_launch": 1e6 * qsec / launches}))
+        return
     draft = be.Model.random_init(be.shape_preset("qwen2-0.5b"), seed=1000 + rank, device=dev).relayout()
     base = be.Model.random_init(be.shape_preset("qwen2-7b"), seed=2000 + rank, device=dev).relayout()
     rows = ((PROMPT + 8 * (warmup + K + DEPTH + 8) + VERIFY + 128 + 63) // 64) * 64
@@ -270,11 +279,13 @@ def main():
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.nvtx.range_push("timed_steps")
     e0.record()
     for _ in range(K):
         dec.replay()
     e1.record()
     torch.cuda.synchronize()
+    torch.cuda.nvtx.range_pop()
     if world > 1:
         dist.barrier()
     sec = e0.elapsed_time(e1) / 1e3

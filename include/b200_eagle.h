@@ -40,6 +40,10 @@ extern "C" {
 
 int b200_version(void);
 int b200_last_cuda_error(void);
+/* Kernels are launched with programmatic stream serialisation (a kernel may start while its
+ * predecessor drains and waits on the device before touching dependent data); 0 turns the launch
+ * attribute off (plain stream order).  Process-wide; default on. */
+void b200_set_pdl(int enabled);
 
 /* Bytes of scratch b200_qmm / b200_qmm_fused want for a given problem (split-K partial sums and
  * tile counters).  0 means the problem runs without scratch. */

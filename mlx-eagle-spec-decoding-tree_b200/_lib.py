@@ -35,6 +35,8 @@ def lib() -> ctypes.CDLL:
                 "There is no CPU or PyTorch fallback for this path.")
         _lib = ctypes.CDLL(LIB_PATH)
         _declare(_lib)
+        if os.environ.get("B200_PDL", "1") == "0":
+            _lib.b200_set_pdl(0)
     return _lib
 
 
@@ -42,6 +44,8 @@ def _declare(l: ctypes.CDLL) -> None:
     vp, i32, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
     l.b200_version.restype = i32
     l.b200_last_cuda_error.restype = i32
+    l.b200_set_pdl.restype = None
+    l.b200_set_pdl.argtypes = [i32]
     l.b200_qmm_workspace_bytes.restype = sz
     l.b200_qmm_workspace_bytes.argtypes = [i32, i32, i32]
     l.b200_qmm.restype = i32

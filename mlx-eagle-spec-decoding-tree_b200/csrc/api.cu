@@ -3,6 +3,7 @@
 
 namespace b200 {
 int g_last_cuda_error = 0;
+int g_use_pdl = 1;
 }
 
 extern "C" {
@@ -10,5 +11,7 @@ extern "C" {
 int b200_version(void) { return 1; }
 
 int b200_last_cuda_error(void) { return b200::g_last_cuda_error; }
+
+void b200_set_pdl(int enabled) { b200::g_use_pdl = enabled ? 1 : 0; }
 
 }  // extern "C"

@@ -45,6 +45,8 @@ struct AttnParams {
 
 template <int HD>
 __global__ void __launch_bounds__(128) tree_attention_kernel(const AttnParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
     constexpr int KS = HD + 8;                       // padded smem row (halves)
     __shared__ __align__(16) __half sk[kKeyBlock * KS];
     __shared__ __align__(16) __half sv[kKeyBlock * KS];
@@ -190,6 +192,8 @@ __global__ void __launch_bounds__(128) tree_attention_kernel(const AttnParams p)
 // order and write fp16.
 template <int HD>
 __global__ void __launch_bounds__(128) tree_attention_merge_kernel(const AttnParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int row_global = blockIdx.x * 4 + (threadIdx.x >> 5);       // m * Hq + head
     if (row_global >= p.M * p.Hq) return;
@@ -279,11 +283,11 @@ int b200_tree_attention(const void* q, int q_stride, const void* kcache, const v
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int merge_blocks = (M * Hq + 3) / 4;
     if (hd == 128) {
-        b200::tree_attention_kernel<128><<<grid, 128, 0, st>>>(p);
-        b200::tree_attention_merge_kernel<128><<<merge_blocks, 128, 0, st>>>(p);
+    b200::launch_kernel(b200::tree_attention_kernel<128>, dim3(grid), dim3(128), 0, st, p);
+    b200::launch_kernel(b200::tree_attention_merge_kernel<128>, dim3(merge_blocks), dim3(128), 0, st, p);
     } else {
-        b200::tree_attention_kernel<64><<<grid, 128, 0, st>>>(p);
-        b200::tree_attention_merge_kernel<64><<<merge_blocks, 128, 0, st>>>(p);
+    b200::launch_kernel(b200::tree_attention_kernel<64>, dim3(grid), dim3(128), 0, st, p);
+    b200::launch_kernel(b200::tree_attention_merge_kernel<64>, dim3(merge_blocks), dim3(128), 0, st, p);
     }
     return b200::check_launch();
 }

@@ -11,6 +11,8 @@ namespace {
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const uint32_t* __restrict__ wq,
                                     const __half* __restrict__ scales, const __half* __restrict__ biases,
                                     __half* __restrict__ out, int M, int H, int V) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int m = blockIdx.y;
     const int pack = blockIdx.x * blockDim.x + threadIdx.x;
     if (pack >= H / 8) return;
@@ -30,6 +32,8 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const uint32
 // One CTA per output row; `row_index` (optional, device) selects the source row of output row 0.
 __global__ void rms_norm_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
                                 __half* __restrict__ y, const int* __restrict__ row_index, int H, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float red[32];
     const int out_row = blockIdx.x;
     const int src_row = row_index ? (row_index[0] + out_row) : out_row;
@@ -70,6 +74,8 @@ __global__ void rope_kv_append_kernel(__half* __restrict__ qkv, const int* __res
                                       __half* __restrict__ kcache, __half* __restrict__ vcache,
                                       const int* __restrict__ prefix, int write_off, int Hq, int Hkv,
                                       int hd, int cap) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int m = blockIdx.y;
     const int head = blockIdx.x;              // 0..Hq-1 q, Hq..Hq+Hkv-1 k, then v
     const int i = threadIdx.x;                // 0..hd/2-1
@@ -105,6 +111,8 @@ __global__ void rope_kv_append_kernel(__half* __restrict__ qkv, const int* __res
 __global__ void rope_positions_kernel(const __half* __restrict__ in, const int* __restrict__ offsets,
                                       const float* __restrict__ inv_freq, float scaling,
                                       __half* __restrict__ out, int H, int Lq, int D) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int l = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int i = threadIdx.x;
     const size_t base = (((size_t)b * H + h) * Lq + l) * D;
@@ -128,8 +136,7 @@ int b200_embed_gather(const int* tokens, const uint32_t* wq, const void* scales,
     if (M < 1 || H < 64 || (H % 64) != 0 || V < 1) return B200_EINVAL;
     if (!b200::aligned16(out)) return B200_EALIGN;
     dim3 grid((H / 8 + 127) / 128, M);
-    b200::embed_gather_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        tokens, wq, static_cast<const __half*>(scales), static_cast<const __half*>(biases),
+    b200::launch_kernel(b200::embed_gather_kernel, dim3(grid), dim3(128), 0, static_cast<cudaStream_t>(stream), tokens, wq, static_cast<const __half*>(scales), static_cast<const __half*>(biases),
         static_cast<__half*>(out), M, H, V);
     return b200::check_launch();
 }
@@ -137,8 +144,7 @@ int b200_embed_gather(const int* tokens, const uint32_t* wq, const void* scales,
 int b200_rms_norm(const void* x, const void* w, void* y, const int* row_index, int M, int H, float eps,
                   void* stream) {
     if (!x || !w || !y || M < 1 || H < 2 || (H % 2) != 0) return B200_EINVAL;
-    b200::rms_norm_kernel<<<M, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(x), static_cast<const __half*>(w), static_cast<__half*>(y), row_index, H, eps);
+    b200::launch_kernel(b200::rms_norm_kernel, dim3(M), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __half*>(x), static_cast<const __half*>(w), static_cast<__half*>(y), row_index, H, eps);
     return b200::check_launch();
 }
 
@@ -149,8 +155,7 @@ int b200_rope_kv_append(void* qkv, const int* pos, const float* inv_freq, float 
     if (M < 1 || Hq < 1 || Hkv < 1 || hd < 2 || (hd % 2) != 0 || hd > 2048 || write_off < 0 || cache_rows < 1)
         return B200_EINVAL;
     dim3 grid(Hq + 2 * Hkv, M);
-    b200::rope_kv_append_kernel<<<grid, hd / 2, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__half*>(qkv), pos, inv_freq, scaling, static_cast<__half*>(kcache),
+    b200::launch_kernel(b200::rope_kv_append_kernel, dim3(grid), dim3(hd / 2), 0, static_cast<cudaStream_t>(stream), static_cast<__half*>(qkv), pos, inv_freq, scaling, static_cast<__half*>(kcache),
         static_cast<__half*>(vcache), prefix, write_off, Hq, Hkv, hd, cache_rows);
     return b200::check_launch();
 }
@@ -160,8 +165,7 @@ int b200_rope_positions(const void* in, const int* offsets, const float* inv_fre
     if (!in || !offsets || !inv_freqs || !out) return B200_EINVAL;
     if (B < 1 || H < 1 || L < 1 || D < 2 || (D % 2) != 0 || D > 2048 || H > 65535 || B > 65535) return B200_EINVAL;
     dim3 grid(L, H, B);
-    b200::rope_positions_kernel<<<grid, D / 2, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(in), offsets, inv_freqs, scaling_factor, static_cast<__half*>(out), H, L, D);
+    b200::launch_kernel(b200::rope_positions_kernel, dim3(grid), dim3(D / 2), 0, static_cast<cudaStream_t>(stream), static_cast<const __half*>(in), offsets, inv_freqs, scaling_factor, static_cast<__half*>(out), H, L, D);
     return b200::check_launch();
 }
 

@@ -36,6 +36,8 @@ struct Stage {
 template <int MT, int S, int WN, bool DUAL>
 __global__ void __launch_bounds__(WN * 32)
 qmm_kernel(const QmmParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
     constexpr int PF = (S == 1) ? 4 : 2;                       // weight chunks in flight per lane
     constexpr int KS = (MT == 1) ? 32 : (MT == 2 ? 16 : 8);    // chunks of x resident in smem
     constexpr int RW = DUAL ? 16 : S * 16;                      // output rows per warp
@@ -312,7 +314,7 @@ int launch_one(const QmmParams& p, const Plan& pl, cudaStream_t stream) {
         attr_set = true;
     }
     dim3 grid(pl.row_tiles, pl.splits, 1);
-    kern<<<grid, WN * 32, pl.smem_bytes, stream>>>(p);
+    launch_kernel(kern, dim3(grid), dim3(WN * 32), pl.smem_bytes, stream, p);
     return check_launch();
 }
 

@@ -117,6 +117,7 @@ __global__ void __launch_bounds__((WN + 1) * 32, 2) qmm_tiled_kernel(const Tiled
     const int nblocks = (p.N + kBlockRows - 1) / kBlockRows;
     const int nitems = p.row_tiles * p.splits;
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         s_abort = 0;
 #pragma unroll
@@ -131,7 +132,11 @@ __global__ void __launch_bounds__((WN + 1) * 32, 2) qmm_tiled_kernel(const Tiled
 
     if (warp == WN) {
         // ------------------------------------------------------------------ producer warp
+        // Weights do not depend on the kernel before this one, activations do: the first stages'
+        // weight copies are issued before the programmatic-dependency wait, so the stream starts
+        // while the previous kernel is still draining.
         uint32_t ps = 0;
+        bool dep_waited = false;
         for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
             const int row_tile = item % p.row_tiles;
             const int split = item / p.row_tiles;
@@ -144,7 +149,41 @@ __global__ void __launch_bounds__((WN + 1) * 32, 2) qmm_tiled_kernel(const Tiled
                 const int blk = min(DUAL ? row_tile : row_tile * NB + b, nblocks - 1);
                 src[b] = p.wt[DUAL ? b : 0] + ((size_t)blk * nchunks_total + c_begin) * 4 * kRec;
             }
-            for (int st = 0; st < nst; st++, ps++) {
+            const int xrows = min(p.M, MP);
+            auto issue_weights = [&](int st, uint32_t slot) {
+                const int recs = min(kCPS, n - st * kCPS);
+                const uint32_t fbar = smem_u32(full + slot);
+                if (lane == 0) {
+                    const uint32_t bytes = (uint32_t)(recs * 4 * kRec);
+                    fence_proxy_async();
+                    mbar_expect_tx(fbar, NB * bytes + (uint32_t)xrows * (uint32_t)(recs * kChunkK * 2));
+#pragma unroll
+                    for (int b = 0; b < NB; b++)
+                        bulk_copy_g2s(smem_u32(ring + slot * STAGE_BYTES + b * BLOCK_STAGE),
+                                      src[b] + (size_t)st * kCPS * 4 * kRec, bytes, fbar);
+                }
+                __syncwarp();
+            };
+            // activations of a stage's k range: one bulk copy per token row, one lane per row
+            // (rows >= M are never written: their accumulator columns are discarded)
+            auto issue_x = [&](int st, uint32_t slot) {
+                const int recs = min(kCPS, n - st * kCPS);
+                if (lane < xrows)
+                    bulk_copy_g2s(smem_u32(ring + slot * STAGE_BYTES + XOFF + lane * XPITCH),
+                                  p.x + (size_t)lane * p.K + (size_t)(c_begin + st * kCPS) * kChunkK,
+                                  (uint32_t)(recs * kChunkK * 2), smem_u32(full + slot));
+            };
+            int st0 = 0;
+            if (!dep_waited) {
+                const int pre = min((int)kNST, nst);          // ring is empty: no "empty" waits needed
+                for (int st = 0; st < pre; st++) issue_weights(st, (uint32_t)st);
+                pdl_wait();
+                dep_waited = true;
+                for (int st = 0; st < pre; st++) issue_x(st, (uint32_t)st);
+                ps = (uint32_t)pre;
+                st0 = pre;
+            }
+            for (int st = st0; st < nst; st++, ps++) {
                 const uint32_t slot = ps % kNST, use = ps / kNST;
                 bool ok = !*abort_flag;
                 if (ok && use > 0 && !mbar_wait_bounded(smem_u32(empty + slot), (use - 1) & 1u)) {
@@ -153,31 +192,15 @@ __global__ void __launch_bounds__((WN + 1) * 32, 2) qmm_tiled_kernel(const Tiled
                     if (lane == 0) atomicExch(p.counter + kErrWord, 2);
                 }
                 if (!ok) return;
-                const int recs = min(kCPS, n - st * kCPS);
-                const uint32_t fbar = smem_u32(full + slot);
-                unsigned char* stage = ring + slot * STAGE_BYTES;
-                const uint32_t xbytes = (uint32_t)(recs * kChunkK * 2);           // one activation row of this stage
-                const int xrows = min(p.M, MP);
-                if (lane == 0) {
-                    const uint32_t bytes = (uint32_t)(recs * 4 * kRec);
-                    fence_proxy_async();
-                    mbar_expect_tx(fbar, NB * bytes + (uint32_t)xrows * xbytes);
-#pragma unroll
-                    for (int b = 0; b < NB; b++)
-                        bulk_copy_g2s(smem_u32(stage + b * BLOCK_STAGE), src[b] + (size_t)st * kCPS * 4 * kRec, bytes, fbar);
-                }
-                __syncwarp();
-                // activations of this stage's k range: one bulk copy per token row, one lane per row
-                // (rows >= M are never written: their accumulator columns are discarded)
-                if (lane < xrows)
-                    bulk_copy_g2s(smem_u32(stage + XOFF + lane * XPITCH),
-                                  p.x + (size_t)lane * p.K + (size_t)(c_begin + st * kCPS) * kChunkK, xbytes, fbar);
+                issue_weights(st, slot);
+                issue_x(st, slot);
             }
         }
         return;
     }
 
     // ---------------------------------------------------------------------- consumers
+    pdl_wait();
     uint32_t cs = 0;
     int rec_off[S];
 #pragma unroll
@@ -365,6 +388,7 @@ __global__ void relayout_kernel(const uint32_t* __restrict__ wq, const __half* _
     const int blk = bc / nchunks, c = bc - blk * nchunks;
     const int t16 = blk * 4 + tib;
     const int i = threadIdx.x;                  // 0..287: u32 index inside the record
+    pdl_wait();
     uint32_t v = 0;
     if (i < 256) {
         const int hh = i >> 7, lane = (i >> 2) & 31, j = i & 3;
@@ -456,7 +480,7 @@ int launch_t(const TiledParams& p, const TPlan& pl, cudaStream_t stream) {
             return check_launch();
         attr_set = true;
     }
-    kern<<<pl.grid, (WN + 1) * 32, pl.smem_bytes, stream>>>(p);
+    launch_kernel(kern, dim3(pl.grid), dim3((WN + 1) * 32), pl.smem_bytes, stream, p);
     return check_launch();
 }
 
@@ -489,8 +513,9 @@ int b200_qmm_relayout(const uint32_t* wq, const void* scales, const void* biases
     if (!wq || !scales || !biases || !out || N < 1 || K < b200::kChunkK || (K % b200::kChunkK) != 0) return B200_EINVAL;
     if (!b200::aligned16(out)) return B200_EALIGN;
     const int recs = ((N + b200::kBlockRows - 1) / b200::kBlockRows) * (K / b200::kChunkK) * 4;
-    b200::relayout_kernel<<<recs, b200::kRec / 4, 0, static_cast<cudaStream_t>(stream)>>>(
-        wq, static_cast<const __half*>(scales), static_cast<const __half*>(biases), static_cast<uint32_t*>(out), N, K);
+    b200::launch_kernel(b200::relayout_kernel, dim3(recs), dim3(b200::kRec / 4), 0, static_cast<cudaStream_t>(stream),
+                        wq, static_cast<const __half*>(scales), static_cast<const __half*>(biases),
+                        static_cast<uint32_t*>(out), N, K);
     return b200::check_launch();
 }
 

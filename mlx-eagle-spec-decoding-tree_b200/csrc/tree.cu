@@ -94,6 +94,8 @@ __device__ __forceinline__ float score_of(float logit, double lse) {
 
 // ---------------------------------------------------------------- row kernels over logits [R, V]
 __global__ void row_max_kernel(const __half* __restrict__ logits, int V, uint32_t* __restrict__ row_max) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.y;
     const int begin = blockIdx.x * kTopkChunk, end = min(V, begin + kTopkChunk);
     const __half* row = logits + (size_t)r * V;
@@ -106,6 +108,8 @@ __global__ void row_max_kernel(const __half* __restrict__ logits, int V, uint32_
 
 __global__ void row_sumexp_kernel(const __half* __restrict__ logits, int V, const uint32_t* __restrict__ row_max,
                                   unsigned long long* __restrict__ row_sum) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.y;
     const int begin = blockIdx.x * kTopkChunk, end = min(V, begin + kTopkChunk);
     const __half* row = logits + (size_t)r * V;
@@ -124,6 +128,8 @@ __global__ void __launch_bounds__(256) row_topk_kernel(const __half* __restrict_
                                                        const uint32_t* __restrict__ row_max,
                                                        const unsigned long long* __restrict__ row_sum,
                                                        int by_score, unsigned long long* __restrict__ cand) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ unsigned long long keys[kTopkChunk];
     __shared__ unsigned long long wbest[8];
     const int r = blockIdx.y;
@@ -158,6 +164,8 @@ __global__ void __launch_bounds__(256) row_topk_kernel(const __half* __restrict_
 }
 
 __global__ void row_argmax_kernel(const __half* __restrict__ logits, int V, unsigned long long* __restrict__ best_key) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.y;
     const int begin = blockIdx.x * kTopkChunk, end = min(V, begin + kTopkChunk);
     const __half* row = logits + (size_t)r * V;
@@ -191,6 +199,8 @@ struct ExpandParams {
 };
 
 __global__ void __launch_bounds__(256) tree_expand_kernel(const ExpandParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float s_val[kK][kK];      // per-row top-8 log-probabilities
     __shared__ int s_idx[kK][kK];        // per-row top-8 token ids
     __shared__ float s_cu[kK * kK];
@@ -290,6 +300,8 @@ __global__ void __launch_bounds__(256) tree_expand_kernel(const ExpandParams p) 
 // with zeros to 8 rows (mlx_eagle.py:400-408); logits of row `accept_len` are the ones used.
 __global__ void prep_catchup_kernel(const int* __restrict__ ctl, const int* __restrict__ y, int* fwd_tokens,
                                     int* fwd_pos, unsigned long long* fwd_mask, int* fwd_prefix, int* sel_row) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int m = threadIdx.x;
     if (m >= kK) return;
     const int dl = ctl[CTL_DRAFT_LEN], a = ctl[CTL_ACCEPT];
@@ -322,6 +334,8 @@ struct FinalizeParams {
 };
 
 __global__ void __launch_bounds__(512) tree_finalize_kernel(const FinalizeParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ unsigned long long s_key[kMaxPool];
     __shared__ unsigned char s_sel[kMaxPool];
     __shared__ int s_selidx[32];
@@ -428,6 +442,8 @@ struct AcceptParams {
 };
 
 __global__ void tree_accept_kernel(const AcceptParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
     constexpr int RW = kMaxDepth + 2;
     const int lane = threadIdx.x;
     const int T = p.T;
@@ -489,6 +505,8 @@ __global__ void tree_accept_kernel(const AcceptParams p) {
 __global__ void kv_compact_kernel(__half* __restrict__ cache, size_t layer_stride, size_t kv_stride,
                                   int cap, int hd, const int* __restrict__ accept_rows,
                                   const int* __restrict__ ctl) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half* buf = reinterpret_cast<__half*>(smem_raw);
     const int a = accept_rows[0];
@@ -523,8 +541,8 @@ int b200_logits_rowstats(const void* logits, int R, int V, uint32_t* row_max, un
     if (!logits || !row_max || !row_sum || R < 1 || R > 32 || V < 1) return B200_EINVAL;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid(b200::nblk_for(V), R);
-    b200::row_max_kernel<<<grid, 256, 0, st>>>(static_cast<const __half*>(logits), V, row_max);
-    b200::row_sumexp_kernel<<<grid, 256, 0, st>>>(static_cast<const __half*>(logits), V, row_max, row_sum);
+    b200::launch_kernel(b200::row_max_kernel, dim3(grid), dim3(256), 0, st, static_cast<const __half*>(logits), V, row_max);
+    b200::launch_kernel(b200::row_sumexp_kernel, dim3(grid), dim3(256), 0, st, static_cast<const __half*>(logits), V, row_max, row_sum);
     return b200::check_launch();
 }
 
@@ -534,8 +552,7 @@ int b200_logits_topk_candidates(const void* logits, int R, int V, const uint32_t
                                 unsigned long long* cand, void* stream) {
     if (!logits || !row_max || !row_sum || !cand || R < 1 || R > 32 || V < 1) return B200_EINVAL;
     dim3 grid(b200::nblk_for(V), R);
-    b200::row_topk_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(logits), V, row_max, row_sum, by_score, cand);
+    b200::launch_kernel(b200::row_topk_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __half*>(logits), V, row_max, row_sum, by_score, cand);
     return b200::check_launch();
 }
 
@@ -556,14 +573,14 @@ int b200_tree_expand(const void* logits, int V, int level, const unsigned long l
     p.pool_scores = pool_scores; p.pool_tokens = pool_tokens; p.pool_parents = pool_parents;
     p.cur_scores = cur_scores; p.topk_cs_index = topk_cs_index;
     p.fwd_tokens = fwd_tokens; p.fwd_pos = fwd_pos; p.fwd_mask = fwd_mask; p.fwd_prefix = fwd_prefix;
-    b200::tree_expand_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    b200::launch_kernel(b200::tree_expand_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
     return b200::check_launch();
 }
 
 int b200_prep_catchup(const int* ctl, const int* y, int* fwd_tokens, int* fwd_pos, unsigned long long* fwd_mask,
                       int* fwd_prefix, int* sel_row, void* stream) {
     if (!ctl || !y || !fwd_tokens || !fwd_pos || !fwd_mask || !fwd_prefix || !sel_row) return B200_EINVAL;
-    b200::prep_catchup_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ctl, y, fwd_tokens, fwd_pos,
+    b200::launch_kernel(b200::prep_catchup_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), ctl, y, fwd_tokens, fwd_pos,
                                                                                fwd_mask, fwd_prefix, sel_row);
     return b200::check_launch();
 }
@@ -582,7 +599,7 @@ int b200_tree_finalize(int depth, int T, const float* pool_scores, const int* po
     p.pool_parents = pool_parents; p.ctl = ctl; p.y = y; p.fwd_tokens = fwd_tokens; p.fwd_pos = fwd_pos;
     p.fwd_mask = fwd_mask; p.fwd_prefix = fwd_prefix; p.tree_position_ids = tree_position_ids;
     p.mask_index = mask_index; p.draft_tokens = draft_tokens; p.retrieve = retrieve; p.tree_info = tree_info;
-    b200::tree_finalize_kernel<<<1, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    b200::launch_kernel(b200::tree_finalize_kernel, dim3(1), dim3(512), 0, static_cast<cudaStream_t>(stream), p);
     return b200::check_launch();
 }
 
@@ -591,8 +608,7 @@ int b200_tree_finalize(int depth, int T, const float* pool_scores, const int* po
 int b200_logits_argmax(const void* logits, int R, int V, unsigned long long* best_key, void* stream) {
     if (!logits || !best_key || R < 1 || R > 32 || V < 1) return B200_EINVAL;
     dim3 grid(b200::nblk_for(V), R);
-    b200::row_argmax_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(logits), V, best_key);
+    b200::launch_kernel(b200::row_argmax_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __half*>(logits), V, best_key);
     return b200::check_launch();
 }
 
@@ -607,7 +623,7 @@ int b200_tree_accept(int T, unsigned long long* argmax_key, const int* draft_tok
     p.T = T; p.argmax_key = argmax_key; p.draft_tokens = draft_tokens; p.retrieve = retrieve;
     p.tree_info = tree_info; p.ctl = ctl; p.y = y; p.accept_rows = accept_rows; p.out_tokens = out_tokens;
     p.step_log = step_log;
-    b200::tree_accept_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    b200::launch_kernel(b200::tree_accept_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), p);
     return b200::check_launch();
 }
 
@@ -617,8 +633,7 @@ int b200_kv_compact(void* cache, int layers, int Hkv, int cache_rows, int hd, co
     if (!cache || !accept_rows || !ctl || layers < 1 || Hkv < 1 || cache_rows < 1 || hd < 1) return B200_EINVAL;
     const size_t kv_stride = (size_t)Hkv * cache_rows * hd;
     dim3 grid(Hkv, layers, 2);
-    b200::kv_compact_kernel<<<grid, 128, (size_t)b200::kK * hd * sizeof(__half), static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__half*>(cache), 2 * kv_stride, kv_stride, cache_rows, hd, accept_rows, ctl);
+    b200::launch_kernel(b200::kv_compact_kernel, dim3(grid), dim3(128), (size_t)b200::kK * hd * sizeof(__half), static_cast<cudaStream_t>(stream), static_cast<__half*>(cache), 2 * kv_stride, kv_stride, cache_rows, hd, accept_rows, ctl);
     return b200::check_launch();
 }
 
