@@ -168,6 +168,68 @@ int b200_tree_attention(const void* q, int q_stride, const void* kcache, const v
                         void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Whole forward pass as one persistent cooperative kernel.
+ * Replaces one call of Model.__call__ (mlx_llama.py:298-313: embed_tokens, every TransformerBlock
+ * :231-249 with Attention :121-196 and MLP :199-215, the final norm and lm_head / as_linear) for
+ * M <= 32 tokens whose ids, rotary positions, tail masks and committed length are in device memory
+ * (same meaning as in b200_rope_kv_append / b200_tree_attention).  All linear weights are in the
+ * streaming layout of b200_qmm_relayout; the embedding stays in the MLX row-major layout.
+ *
+ * The descriptor itself is HOST memory (read during the call only); every pointer in it is a device
+ * pointer.  layer_table is a device array of n_layers entries of 8 pointers each:
+ *   { qkv weights (q|k|v rows concatenated), qkv bias [NQKV] fp16 or NULL, o_proj, gate_proj, up_proj,
+ *     down_proj weights, input_layernorm weight [hidden] fp16, post_attention_layernorm weight }.
+ * Buffers: h, hw [32][hidden]; qkv [32][(n_heads+2*n_kv_heads)*head_dim]; attn [32][n_heads*head_dim];
+ * act [32][intermediate]; logits [rows_out][vocab] (all fp16).  kv_cache is
+ * [n_layers][2][n_kv_heads][cache_rows][head_dim] fp16; the K/V rows of the M new tokens are written
+ * to cache row prefix[0]+write_off+m.  Output row r of logits belongs to token row_index[0]+r
+ * (row_index may be NULL = 0).  RMSNorm is folded into the adjacent matmuls (h*w is rounded to fp16,
+ * the per-token 1/rms multiplies the fp32 accumulator), which differs from the per-op kernels by
+ * input-rounding noise only.
+ *
+ * workspace: b200_forward_workspace_bytes bytes, the first 4352 bytes zero before the first use (the
+ * kernel restores that state).  Int word 2 of the workspace is an error flag: non-zero after a launch
+ * means a bounded wait inside the kernel gave up; zero the first 4352 bytes before reusing it.
+ * The launch is cooperative (one CTA per SM, all co-resident); launches sharing a workspace must be
+ * stream-ordered.  hidden, intermediate and n_heads*head_dim must be multiples of 128, hidden <= 8192,
+ * head_dim 64 or 128, tail <= 64, write_off + M <= tail.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct b200_forward_desc {
+    int M, rows_out;
+    int hidden, intermediate, n_heads, n_kv_heads, head_dim, vocab, n_layers;
+    int cache_rows, write_off, tail;
+    float rms_eps, rope_scaling, attn_scale;
+    int reserved;
+    const int* tokens;
+    const int* pos;
+    const unsigned long long* mask;
+    const int* prefix;
+    const int* row_index;
+    const float* inv_freq;
+    const uint32_t* embed_wq;
+    const void* embed_scales;
+    const void* embed_biases;
+    const void* final_norm;
+    const void* lm_head_tiled;
+    const void* layer_table;
+    void* h;
+    void* hw;
+    void* qkv;
+    void* attn;
+    void* act;
+    void* logits;
+    void* kv_cache;
+    void* workspace;
+    size_t workspace_bytes;
+    void* timeline;         /* optional profiling hook, NULL = off: int64 [SMs][timeline_pitch][2]; CTA b  */
+    int timeline_pitch;     /* stores the nanosecond timer when it arrives at / leaves device barrier i   */
+    int reserved2;          /* (i = 0 after the embedding, then 6 per layer) and, arrive only, at its end */
+} b200_forward_desc;
+
+size_t b200_forward_workspace_bytes(const b200_forward_desc* desc);
+int b200_forward(const b200_forward_desc* desc, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Draft tree, acceptance and compaction.  One request; k = 8 children per node.
  * ctl is int32[16]: [0] committed length of the target cache, [1] of the draft cache, [2] accept
  * length of the previous step, [3] tokens generated, [4] step, [5] draft cache length after the

@@ -92,8 +92,27 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_logits_argmax.argtypes = [vp, i32, i32, vp, vp]
     l.b200_tree_accept.restype = i32
     l.b200_tree_accept.argtypes = [i32] + [vp] * 10
+    l.b200_forward_workspace_bytes.restype = sz
+    l.b200_forward_workspace_bytes.argtypes = [ctypes.POINTER(ForwardDesc)]
+    l.b200_forward.restype = i32
+    l.b200_forward.argtypes = [ctypes.POINTER(ForwardDesc), vp]
     l.b200_kv_compact.restype = i32
     l.b200_kv_compact.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp]
+
+
+class ForwardDesc(ctypes.Structure):
+    """Mirror of ``b200_forward_desc`` (include/b200_eagle.h): host struct of sizes and device pointers."""
+    _fields_ = ([(n, ctypes.c_int) for n in (
+        "M", "rows_out", "hidden", "intermediate", "n_heads", "n_kv_heads", "head_dim", "vocab", "n_layers",
+        "cache_rows", "write_off", "tail")]
+        + [(n, ctypes.c_float) for n in ("rms_eps", "rope_scaling", "attn_scale")]
+        + [("reserved", ctypes.c_int)]
+        + [(n, ctypes.c_void_p) for n in (
+            "tokens", "pos", "mask", "prefix", "row_index", "inv_freq", "embed_wq", "embed_scales", "embed_biases",
+            "final_norm", "lm_head_tiled", "layer_table", "h", "hw", "qkv", "attn", "act", "logits", "kv_cache",
+            "workspace")]
+        + [("workspace_bytes", ctypes.c_size_t), ("timeline", ctypes.c_void_p), ("timeline_pitch", ctypes.c_int),
+           ("reserved2", ctypes.c_int)])
 
 
 def check(rc: int, what: str) -> None:

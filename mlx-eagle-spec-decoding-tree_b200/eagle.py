@@ -227,6 +227,8 @@ class SpecDecoder:
                     break
         torch.cuda.synchronize(self.device)
         total = time.perf_counter() - tic
+        self.base.check_fused_error()
+        self.draft.check_fused_error()
         steps_run = i
         log = self.step_log[: 2 * steps_run].cpu().tolist()
         produced = sum(1 + log[2 * s] for s in range(steps_run))

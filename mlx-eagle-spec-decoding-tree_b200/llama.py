@@ -4,7 +4,9 @@
 (``mlx_llama.py:298-313``): explicit additive mask, integer or per-token array
 positions, ``flat_rope`` giving every token of the call the same position.  All
 linear layers are 4-bit / group-64 quantised and run through ``libb200eagle.so``;
-q/k/v are stored as one fused matrix, so one layer is nine kernel launches:
+q/k/v are stored as one fused matrix.  Once the weights are in the streaming layout
+(``Model.relayout``) a whole pass is ONE persistent kernel (``b200_forward``); before that, or
+with ``model.fused = False``, one layer is nine kernel launches:
 
     rms_norm -> qmm(+bias) -> rope_kv_append -> tree_attention (+ merge) -> qmm(+residual)
     -> rms_norm -> qmm(SiLU(gate)*up) -> qmm(+residual)
@@ -15,7 +17,9 @@ device memory, so that a whole speculative step can be replayed as a CUDA graph.
 """
 from __future__ import annotations
 
+import ctypes
 import math
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Union
 
@@ -175,8 +179,13 @@ class Model:
         self.logits = torch.zeros(MAX_ROWS, args.vocab_size, **f16)
         self._attn_ws = None
         self._attn_ws_rows = 0
+        self.hw = torch.zeros(MAX_ROWS, H, **f16)        # h * norm weight (fused forward)
+        self.fused = True                                # one persistent kernel per pass when possible
+        self._fwd_ws = None
+        self._fwd_ws_key = None
+        self._layer_table = None
+        self.timeline = None
         self.fwd = FwdInputs(self.device)
-        self.launches_per_forward = 9 * args.num_hidden_layers + 3      # attention = 2 kernels
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -262,6 +271,84 @@ class Model:
                                   lin.in_features, 64, 0, epilogue, p(ws), ws.numel(), st)
             _lib.check(rc, "b200_qmm_fused")
 
+    @property
+    def launches_per_forward(self) -> int:
+        """Kernel launches of one pass: 1 (persistent kernel) or 9 per layer + embedding, final norm, head."""
+        return 1 if self.can_fuse() else 9 * self.args.num_hidden_layers + 3
+
+    # ------------------------------------------------------------------ fused forward (one kernel)
+    def can_fuse(self) -> bool:
+        """True when the pass can run as the single persistent kernel ``b200_forward``: every linear
+        layer in the streaming layout, the embedding still row-major, sizes in multiples of 128."""
+        if not self.fused or os.environ.get("B200_FUSED_FORWARD", "1") == "0":
+            return False
+        a = self.args
+        if any(lw[k].tiled is None for lw in self.layers for k in ("qkv", "o", "gate", "up", "down")):
+            return False
+        if self.lm_head.tiled is None or self.embed.weight is None:
+            return False
+        return (a.hidden_size % 128 == 0 and a.hidden_size <= 8192 and a.intermediate_size % 128 == 0
+                and self.nq % 128 == 0 and a.head_dim in (64, 128) and a.vocab_size % 8 == 0)
+
+    def _fused_desc(self, M, cache, write_off, tail, fwd, rows, row_index):
+        a = self.args
+        p = lambda t: None if t is None else t.data_ptr()
+        if self._layer_table is None:
+            rows_ = []
+            for lw in self.layers:
+                rows_.append([lw["qkv"].tiled.data_ptr(), p(lw["qkv"].bias) or 0, lw["o"].tiled.data_ptr(),
+                              lw["gate"].tiled.data_ptr(), lw["up"].tiled.data_ptr(), lw["down"].tiled.data_ptr(),
+                              lw["input_norm"].data_ptr(), lw["post_norm"].data_ptr()])
+            self._layer_table = torch.tensor(rows_, dtype=torch.int64).to(self.device)
+        d = _lib.ForwardDesc()
+        d.M, d.rows_out = M, rows
+        d.hidden, d.intermediate, d.n_heads, d.n_kv_heads = a.hidden_size, a.intermediate_size, \
+            a.num_attention_heads, a.num_key_value_heads
+        d.head_dim, d.vocab, d.n_layers = a.head_dim, a.vocab_size, a.num_hidden_layers
+        d.cache_rows, d.write_off, d.tail = cache.rows, write_off, tail
+        d.rms_eps, d.rope_scaling, d.attn_scale = float(a.rms_norm_eps), self.rope_scaling_factor, self.scale
+        d.tokens, d.pos, d.mask, d.prefix = p(fwd.tokens), p(fwd.pos), p(fwd.mask), p(fwd.prefix)
+        d.row_index = p(row_index)
+        d.inv_freq = p(self.inv_freqs)
+        d.embed_wq, d.embed_scales, d.embed_biases = p(self.embed.weight), p(self.embed.scales), p(self.embed.biases)
+        d.final_norm, d.lm_head_tiled, d.layer_table = p(self.norm), p(self.lm_head.tiled), p(self._layer_table)
+        d.h, d.hw, d.qkv, d.attn, d.act, d.logits = p(self.h), p(self.hw), p(self.qkv), p(self.attn), p(self.act), \
+            p(self.logits)
+        d.kv_cache = p(cache.data)
+        key = (cache.rows,)
+        if self._fwd_ws is None or self._fwd_ws_key != key:
+            d32 = _lib.ForwardDesc.from_buffer_copy(d)
+            d32.M, d32.rows_out, d32.write_off, d32.tail = MAX_ROWS, MAX_ROWS, 0, MAX_TAIL
+            nbytes = _lib.lib().b200_forward_workspace_bytes(ctypes.byref(d32))
+            if nbytes == 0:
+                raise _lib.B200Error("b200_forward_workspace_bytes rejected the model shape")
+            self._fwd_ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+            self._fwd_ws_key = key
+        d.workspace, d.workspace_bytes = p(self._fwd_ws), self._fwd_ws.numel()
+        if self.timeline is not None:
+            d.timeline, d.timeline_pitch = p(self.timeline), self.timeline.shape[1]
+        return d
+
+    def enable_timeline(self, on: bool = True):
+        """Profiling hook of the persistent kernel: per SM, the device timer (ns) at arrival at and
+        departure from every device-wide barrier of the next pass (``self.timeline`` int64
+        ``[SMs, barriers + 1, 2]``; the last entry holds the end of the kernel)."""
+        if on:
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            self.timeline = torch.zeros(sms, 6 * self.args.num_hidden_layers + 2, 2, dtype=torch.int64,
+                                        device=self.device)
+        else:
+            self.timeline = None
+
+    def check_fused_error(self):
+        """Raise if a bounded wait inside the persistent forward kernel ever gave up (synchronises)."""
+        if self._fwd_ws is None:
+            return
+        code = int(self._fwd_ws[:16].view(torch.int32)[2])
+        if code != 0:
+            self._fwd_ws[:4352].zero_()
+            raise _lib.B200Error(f"b200_forward: a bounded wait gave up inside the kernel (code {code})")
+
     # ------------------------------------------------------------------ device-side forward
     def _attention_workspace(self, cache: KVCache):
         if self._attn_ws is None or self._attn_ws_rows < cache.rows:
@@ -282,6 +369,11 @@ class Model:
         if not (1 <= M <= MAX_ROWS and 1 <= tail <= MAX_TAIL and write_off + M <= tail):
             raise _lib.B200Error("forward_device: need 1 <= M <= 32, tail <= 64, write_off + M <= tail")
         fwd = fwd or self.fwd
+        if self.can_fuse():
+            rows = M if logits_rows is None else logits_rows
+            desc = self._fused_desc(M, cache, write_off, tail, fwd, rows, row_index)
+            _lib.check(_lib.lib().b200_forward(ctypes.byref(desc), _lib.stream_ptr(self.device)), "b200_forward")
+            return self.logits[:rows]
         a, L, lib = self.args, _lib.lib(), _lib.lib()
         st, p = _lib.stream_ptr(self.device), _lib.ptr
         ws = qk.workspace(self.device)

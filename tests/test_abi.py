@@ -49,3 +49,18 @@ def test_missing_library_fails_loudly(be, monkeypatch):
     monkeypatch.setattr(be._lib, "LIB_PATH", "/nonexistent/libb200eagle.so")
     with pytest.raises(be._lib.B200Error):
         be._lib.lib()
+
+
+def test_forward_descriptor_validation_without_gpu(be):
+    lib = be._lib.lib()
+    d = be._lib.ForwardDesc()
+    d.M, d.rows_out = 16, 16
+    d.hidden, d.intermediate, d.n_heads, d.n_kv_heads, d.head_dim = 3584, 18944, 28, 4, 128
+    d.vocab, d.n_layers, d.cache_rows, d.write_off, d.tail = 152064, 28, 1024, 0, 16
+    assert lib.b200_forward_workspace_bytes(ctypes.byref(d)) > 4352
+    assert lib.b200_forward(ctypes.byref(d), None) == -1          # null pointers: refused before any CUDA call
+    d.hidden = 3500                                               # not a multiple of 128
+    assert lib.b200_forward_workspace_bytes(ctypes.byref(d)) == 0
+    d.hidden, d.head_dim = 3584, 96
+    assert lib.b200_forward(ctypes.byref(d), None) == -1
+    assert ctypes.sizeof(be._lib.ForwardDesc) == 64 + 20 * 8 + 8 + 16  # layout of b200_forward_desc in the header

@@ -1,0 +1,138 @@
+"""The whole-pass persistent kernel (b200_forward) against the CPU oracle and against the per-op kernels."""
+import dataclasses
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import eagle_ref, model_ref
+
+pytestmark = pytest.mark.gpu
+f64 = np.float64
+
+
+def _close(got, want, rel, abs_):
+    got, want = np.asarray(got).astype(f64), np.asarray(want).astype(f64)
+    err = np.abs(got - want)
+    assert np.all(err <= rel * np.abs(want) + abs_), f"max err {err.max()} (want scale {np.abs(want).max()})"
+
+
+@pytest.fixture(scope="module", params=["tiny-qwen2", "tiny-llama"])
+def pair(request, be, cuda):
+    args = be.shape_preset(request.param)
+    m = be.Model.random_init(args, seed=5, device=cuda, gen_device="cpu")
+    om = model_ref.OracleModel(args, m.state_numpy())
+    m.relayout()
+    assert m.can_fuse() and m.launches_per_forward == 1
+    return args, m, om
+
+
+def test_causal_prompt_matches_oracle_logits_and_cache(pair):
+    args, m, om = pair
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, args.vocab_size, 45)          # passes of 32 and 13 rows
+    cache = m.make_cache(128)
+    logits = m(torch.from_numpy(prompt)[None], cache=cache)[0].cpu().numpy()
+    m.check_fused_error()
+    oc = model_ref.make_prompt_cache(om, 128)
+    want = om(prompt, oc)
+    _close(logits, want, 2.0 ** -6, 2e-2)                  # stated tolerance: |d| <= 2^-6 |want| + 2e-2
+    assert np.mean(logits.argmax(-1) == want.argmax(-1)) >= 0.9
+    for li, c in enumerate(oc):
+        _close(cache.data[li, 0, :, :45].cpu().numpy(), c.keys[0, :, :45], 2.0 ** -6, 2e-2)
+        _close(cache.data[li, 1, :, :45].cpu().numpy(), c.values[0, :, :45], 2.0 ** -6, 2e-2)
+
+
+def test_tree_pass_with_golden_mask_matches_oracle(be, pair):
+    args, m, om = pair
+    rng = np.random.default_rng(2)
+    prompt = rng.integers(0, args.vocab_size, 70)          # prefix longer than one key block
+    tokens = rng.integers(0, args.vocab_size, 8)
+    mask_index = np.array([0, 1, 2, 2, 3, 4, 5])           # mlx_eagle_tests.py:80
+    tm = np.eye(8, dtype=bool)
+    for i in range(7):
+        tm[i + 1] |= tm[mask_index[i]]
+    pos = tm.sum(1) - 1
+    cache = m.make_cache(192)
+    m(torch.from_numpy(prompt)[None], cache=cache, logits_last_only=True)
+    got = be.eagle.tree_decoding(torch.from_numpy(tokens)[None], torch.from_numpy(tm), torch.from_numpy(pos), m, cache)
+    m.check_fused_error()
+    oc = model_ref.make_prompt_cache(om, 192)
+    om(prompt, oc)
+    want = eagle_ref.tree_decoding(tokens[None], tm, pos, om, oc)
+    _close(got[0].cpu().numpy(), want, 2.0 ** -6, 2e-2)
+
+
+def test_row_results_do_not_depend_on_the_row_count(pair):
+    """One token alone and the same token as row 0 of a 16-row pass give bit-equal logits (the property
+    that makes speculative greedy output equal plain greedy decoding)."""
+    args, m, _ = pair
+    rng = np.random.default_rng(4)
+    prompt = torch.from_numpy(rng.integers(0, args.vocab_size, 40))
+    c1, c2 = m.make_cache(128), m.make_cache(128)
+    m(prompt[None], cache=c1, logits_last_only=True)
+    m(prompt[None], cache=c2, logits_last_only=True)
+    toks = torch.from_numpy(rng.integers(0, args.vocab_size, 16))
+    one = m(toks[None, :1], cache=c1)[0, 0].clone()
+    many = m(toks[None], cache=c2)[0, 0].clone()
+    assert torch.equal(one, many)
+
+
+SHAPES = [
+    ("qwen2-0.5b", 3),      # hidden 896 (7 k-chunks), 14/2 heads of 64, tied head
+    ("qwen2-7b", 2),        # hidden 3584, 28/4 heads of 128, MLP 18944
+    ("llama3.2-1b", 2),     # 32/8 heads of 64
+]
+
+
+@pytest.mark.parametrize("name,layers", SHAPES)
+def test_fused_pass_equals_per_op_kernels_at_benchmark_shapes(be, cuda, name, layers):
+    """Full-width layers of the benchmark shapes (few of them): the persistent kernel against the nine
+    launches per layer, same weights, same inputs; prompt passes of 32 rows, then a 16-row tree pass
+    over a 300-row prefix, then a one-row pass."""
+    args = dataclasses.replace(be.shape_preset(name), num_hidden_layers=layers)
+    m = be.Model.random_init(args, seed=21, device=cuda).relayout()
+    assert m.can_fuse()
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, args.vocab_size, (300,), generator=g)
+    tree = torch.randint(0, args.vocab_size, (16,), generator=g)
+    tm = torch.tril(torch.ones(16, 16, dtype=torch.bool))
+    tm[9:, 5:9] = False                                    # a branching tree: rows 9.. skip nodes 5..8
+    tm |= torch.eye(16, dtype=torch.bool)
+    pos = tm.sum(1) - 1
+    outs = {}
+    for fused in (True, False):
+        m.fused = fused
+        cache = m.make_cache(512)
+        last = m(prompt[None], cache=cache, logits_last_only=True)[0, 0].float().cpu()
+        t = be.eagle.tree_decoding(tree[None], tm, pos, m, cache)[0].float().cpu()
+        cache.offset = 300
+        one = m(tree[None, :1], cache=cache)[0, 0].float().cpu()
+        outs[fused] = (last, t, one, cache.data[:, :, :, :316].float().cpu())
+    m.fused = True
+    m.check_fused_error()
+    for a, b in zip(outs[True], outs[False]):
+        assert torch.isfinite(a).all()
+        _close(a.numpy(), b.numpy(), 2.0 ** -6, 2e-2)
+    # the row-0 logits of the tree pass and the one-row pass agree bit for bit inside each path
+    assert torch.equal(outs[True][1][0], outs[True][2])
+
+
+def test_forward_rejects_bad_descriptors(be, pair):
+    import ctypes
+    args, m, _ = pair
+    cache = m.make_cache(64)
+    d = m._fused_desc(8, cache, 0, 8, m.fwd, 8, None)
+    lib = be._lib.lib()
+    bad = be._lib.ForwardDesc.from_buffer_copy(d)
+    bad.M = 33
+    assert lib.b200_forward(ctypes.byref(bad), None) == -1
+    bad = be._lib.ForwardDesc.from_buffer_copy(d)
+    bad.tail = 4                                            # write_off + M > tail
+    assert lib.b200_forward(ctypes.byref(bad), None) == -1
+    bad = be._lib.ForwardDesc.from_buffer_copy(d)
+    bad.workspace_bytes = 1024
+    assert lib.b200_forward(ctypes.byref(bad), None) == -4
+    bad = be._lib.ForwardDesc.from_buffer_copy(d)
+    bad.h = d.h + 2
+    assert lib.b200_forward(ctypes.byref(bad), None) == -2
