@@ -179,8 +179,9 @@ int b200_tree_attention(const void* q, int q_stride, const void* kcache, const v
  * pointer.  layer_table is a device array of n_layers entries of 8 pointers each:
  *   { qkv weights (q|k|v rows concatenated), qkv bias [NQKV] fp16 or NULL, o_proj, gate_proj, up_proj,
  *     down_proj weights, input_layernorm weight [hidden] fp16, post_attention_layernorm weight }.
- * Buffers: h, hw [32][hidden]; qkv [32][(n_heads+2*n_kv_heads)*head_dim]; attn [32][n_heads*head_dim];
- * act [32][intermediate]; logits [rows_out][vocab] (all fp16).  kv_cache is
+ * Buffers (all fp16): h [32][hidden]; qkv [32][(n_heads+2*n_kv_heads)*head_dim]; logits [rows_out][vocab];
+ * hw, attn, act are scratch the kernel keeps in its own chunk-major padded layout and need
+ * (width/128)*32*160 halves each, width = hidden, n_heads*head_dim, intermediate.  kv_cache is
  * [n_layers][2][n_kv_heads][cache_rows][head_dim] fp16; the K/V rows of the M new tokens are written
  * to cache row prefix[0]+write_off+m.  Output row r of logits belongs to token row_index[0]+r
  * (row_index may be NULL = 0).  RMSNorm is folded into the adjacent matmuls (h*w is rounded to fp16,
@@ -199,7 +200,9 @@ typedef struct b200_forward_desc {
     int hidden, intermediate, n_heads, n_kv_heads, head_dim, vocab, n_layers;
     int cache_rows, write_off, tail;
     float rms_eps, rope_scaling, attn_scale;
-    int reserved;
+    int attn_split_blocks;  /* 0 = default (9): from this many 64-key blocks of cache on, attention splits the   */
+                            /* keys across CTAs and merges in a second phase; below, one CTA per kv head walks */
+                            /* all blocks.  < 0 = always split                                                  */
     const int* tokens;
     const int* pos;
     const unsigned long long* mask;
@@ -221,9 +224,12 @@ typedef struct b200_forward_desc {
     void* kv_cache;
     void* workspace;
     size_t workspace_bytes;
-    void* timeline;         /* optional profiling hook, NULL = off: int64 [SMs][timeline_pitch][2]; CTA b  */
+    void* timeline;         /* optional profiling hook, NULL = off: int64 [SMs][timeline_pitch][8]; CTA b  */
     int timeline_pitch;     /* stores the nanosecond timer when it arrives at / leaves device barrier i   */
-    int reserved2;          /* (i = 0 after the embedding, then 6 per layer) and, arrive only, at its end */
+    int phase_mask;         /* (i = 0 after the embedding, then 6 per layer) and, arrive only, at its end */
+                            /* phase_mask: profiling only, 0 = run everything; else bit k set = run phase  */
+                            /* kind k (0 embedding, 1 qkv, 2 attention, 3 merge, 4 o_proj, 5 gate/up,      */
+                            /* 6 down_proj, 7 vocabulary projection); results are then meaningless         */
 } b200_forward_desc;
 
 size_t b200_forward_workspace_bytes(const b200_forward_desc* desc);

@@ -106,13 +106,13 @@ class ForwardDesc(ctypes.Structure):
         "M", "rows_out", "hidden", "intermediate", "n_heads", "n_kv_heads", "head_dim", "vocab", "n_layers",
         "cache_rows", "write_off", "tail")]
         + [(n, ctypes.c_float) for n in ("rms_eps", "rope_scaling", "attn_scale")]
-        + [("reserved", ctypes.c_int)]
+        + [("attn_split_blocks", ctypes.c_int)]
         + [(n, ctypes.c_void_p) for n in (
             "tokens", "pos", "mask", "prefix", "row_index", "inv_freq", "embed_wq", "embed_scales", "embed_biases",
             "final_norm", "lm_head_tiled", "layer_table", "h", "hw", "qkv", "attn", "act", "logits", "kv_cache",
             "workspace")]
         + [("workspace_bytes", ctypes.c_size_t), ("timeline", ctypes.c_void_p), ("timeline_pitch", ctypes.c_int),
-           ("reserved2", ctypes.c_int)])
+           ("phase_mask", ctypes.c_int)])
 
 
 def check(rc: int, what: str) -> None:

@@ -29,6 +29,8 @@
 // raises the error word of the workspace, stops waiting and runs to the end, so the kernel always
 // terminates.  The kernel must be launched cooperatively (all CTAs co-resident).  No load here uses
 // cluster multicast.
+#include <cuda.h>
+
 #include "pipeline.cuh"
 #include "qmm_common.cuh"
 
@@ -40,18 +42,28 @@ constexpr int kNCons = kWN * 32;
 constexpr int kFwdThreads = kNCons + 32;      // + one producer warp
 constexpr int kRec = 1152;                    // bytes per 16-row x 128-k weight record
 constexpr int kWArea = 8 * 4 * kRec;          // weight bytes of a ring stage: 8 (block, chunk) cells of 4 records
-constexpr int kXPitch = 4 * kChunkK * 2 + 64; // activation row pitch in a stage (up to 4 chunks)
+// Matmul inputs that a phase of this kernel writes for a later phase (h*w, attention output, MLP
+// activations) live in a chunk-major, padded layout: [k chunk of 128][token row (MP of them)][160
+// halves], so that the activations of a stage's K range are ONE contiguous run (one bulk copy; a
+// copy costs 60-150 cycles to issue whatever its size) whose rows are already padded for
+// conflict-free fragment loads (320-byte pitch).
+constexpr int kXRowH = 160;                   // halves per padded row of one chunk
+constexpr int kXRow = kXRowH * 2;             // bytes
+constexpr int kMaxLayers = 128;               // layer pointer table kept in shared memory (64 bytes per layer)
+constexpr int kLtabBytes = kMaxLayers * 64;
+constexpr int kScratch = 36864;               // shared scratch for the K-part reduction of a tile
 constexpr int kKeyBlock = 64;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr uint32_t kGridWaitLimit = 1u << 22;
 constexpr int kSsqPitch = 32;                 // ssq[part][token]
-constexpr int kMaxSsqParts = 64;
+constexpr int kMaxSsqParts = 512;             // one part per 16 columns of h: hidden <= 8192
 constexpr int kCsPitch = 64;                  // cos/sin table: cs[token][i], i < head_dim/2 <= 64
 
 // sync words (ints) at the head of the workspace
 constexpr int kSyncBar = 0, kSyncExit = 1, kSyncErr = 2;
 
 enum { EPI_QKV = 0, EPI_SILU = 1, EPI_RESID = 2, EPI_HEAD = 3 };
+enum { K_EMBED = 0, K_A = 1, K_B1 = 2, K_B2 = 3, K_C = 4, K_D = 5, K_E = 6, K_HEAD = 7 };
 enum { PLAN_A = 0, PLAN_C = 1, PLAN_D = 2, PLAN_E = 3, PLAN_HEAD = 4 };
 
 struct LayerPtrs {                 // one entry per layer, in device memory (8 pointers = 64 bytes)
@@ -66,11 +78,12 @@ struct LayerPtrs {                 // one entry per layer, in device memory (8 p
 };
 
 struct PhasePlan {
-    int row_tiles, splits, chunks_per_split;
+    int row_items, splits, chunks_per_split;   // items along N, split-K ways across CTAs
+    int kw, U;                                 // K-parts per tile inside a CTA (8/kw tiles per item), records per warp and stage
 };
 
 struct FwdParams {
-    int M, rows_out, H, I, Hq, Hkv, HD, V, L, NQKV;
+    int M, mp, rows_out, H, I, Hq, Hkv, HD, V, L, NQKV;   // mp: M rounded up to 8 (row count of the padded layout)
     float eps, rope_scale, scale_log2;
     const int* tokens;
     const int* pos;
@@ -97,16 +110,21 @@ struct FwdParams {
     float* partial;
     int nkb, qrp;
     PhasePlan plan[5];
-    long long* timeline;           // optional [CTAs][timeline_pitch][2] globaltimer stamps (arrive, leave) per barrier
+    int attn_fused_max;            // single-phase attention while the cache spans at most this many key blocks
+    unsigned phase_mask;           // bit per phase kind (K_*): kinds to run; all ones normally
+    alignas(64) CUtensorMap kvmap; // the whole KV cache as a 2-D fp16 tensor [rows][head_dim], 64 x 64 boxes, 128-byte swizzle
+    long long* timeline;           // optional [CTAs][timeline_pitch][8] timer stamps per barrier: arrive, leave, then
+                                   // six stamps inside the matmul phase that ends at that barrier
     int timeline_pitch;
 };
 
 template <int MT>
 struct Geo {
     static constexpr int MP = MT * 8;
-    static constexpr int STAGE = kWArea + MP * kXPitch;
-    static constexpr int NST = MT <= 2 ? 4 : 3;
-    static constexpr int SMEM = NST * STAGE + 128;
+    static constexpr int CPS_MAX = MT == 1 ? 8 : (MT == 2 ? 4 : 2);    // chunks of activations a stage can hold
+    static constexpr int STAGE = kWArea + CPS_MAX * MP * kXRow;
+    static constexpr int NST = 3;
+    static constexpr int SMEM = NST * STAGE + 128 + kScratch + kLtabBytes;
 };
 
 struct QDesc {
@@ -118,28 +136,33 @@ struct QDesc {
     __half* y;
     int N, K;
     PhasePlan pl;
-    int xrows;
-    int rstd_off;               // token row of x row 0 (selects the ssq column)
-    int ssq_parts;
+    int xrows;                  // token rows of the pass
+    int row_lo, row_cnt;        // token rows [row_lo, row_lo+row_cnt) are stored, as output rows 0.. (vocabulary projection)
+    bool y_tiled;               // output goes to the chunk-major padded layout (it is a later phase's matmul input)
 };
 
 struct Ctx {
     unsigned char* ring;
     uint64_t* full;
     uint64_t* empty;
-    uint64_t* rstd_bar;
+    unsigned char* scratch;
+    const LayerPtrs* ltab;        // the layer pointer table, copied to shared memory at kernel start
     volatile int* abort_flag;
+    volatile uint32_t* s_epoch;   // grid barriers this CTA has seen complete (written by thread 0)
     int* is_last;
     float* s_rstd;
     uint32_t pos;       // ring stages produced (producer warp) / consumed (consumer warps)
     uint32_t epoch;     // grid barriers before the current phase
-    uint32_t rstd_n;    // rstd hand-overs consumed
     int lane, warp;
 };
 
 // Ring waits of this kernel: up to 2^20 polls of <= 1 us each (about a second) before giving up.
 __device__ __forceinline__ bool fwd_wait(uint32_t bar, uint32_t parity) {
     return mbar_wait_timed(bar, parity, 1u << 20, 1000u);
+}
+
+__device__ __forceinline__ size_t xt_index(int tok, int n, int mp) {
+    return ((size_t)(n >> 7) * mp + tok) * kXRowH + (n & 127);
 }
 
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;\n" ::: "memory"); }
@@ -154,6 +177,12 @@ __device__ __forceinline__ long long global_ns() {
     long long t;
     asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
     return t;
+}
+
+// Profiling stamp k (2..7) of the phase in progress (thread 0 of the CTA, timeline enabled only).
+__device__ __forceinline__ void stamp(const FwdParams& p, const Ctx& c, int k) {
+    if (p.timeline != nullptr && threadIdx.x == 0 && (int)c.epoch < p.timeline_pitch)
+        p.timeline[((size_t)blockIdx.x * p.timeline_pitch + c.epoch) * 8 + k] = clock64();   // SM cycles
 }
 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_ptr) {
@@ -177,7 +206,7 @@ __device__ void grid_barrier(const FwdParams& p, Ctx& c) {
     if (threadIdx.x == 0 && !*c.abort_flag) {
         long long* tl = nullptr;
         if (p.timeline != nullptr && (int)c.epoch <= p.timeline_pitch) {
-            tl = p.timeline + ((size_t)blockIdx.x * p.timeline_pitch + (c.epoch - 1)) * 2;
+            tl = p.timeline + ((size_t)blockIdx.x * p.timeline_pitch + (c.epoch - 1)) * 8;
             tl[0] = global_ns();
         }
         __threadfence();               // cumulative: covers the CTA's writes ordered before the bar.sync
@@ -185,12 +214,17 @@ __device__ void grid_barrier(const FwdParams& p, Ctx& c) {
         atomicAdd(p.sync + kSyncBar, 1);
         const int target = (int)(c.epoch * gridDim.x);
         bool ok = false;
+        const volatile int* bar = p.sync + kSyncBar;
         for (uint32_t i = 0; i < kGridWaitLimit; i++) {
-            if (ld_acquire(p.sync + kSyncBar) >= target) { ok = true; break; }
+            if (*bar >= target) { ok = true; break; }
         }
         if (!ok) raise_error(p, c, 10);
         __threadfence();
-        if (tl != nullptr) tl[1] = global_ns();
+        *c.s_epoch = c.epoch;          // the producer warp watches this word instead of the global counter
+        if (tl != nullptr) {
+            tl[1] = global_ns();
+            tl[7] = clock64();         // same instant in SM cycles, the origin of the next phase's stamps
+        }
     }
     consumer_sync(kNCons);
 }
@@ -201,43 +235,51 @@ __device__ bool producer_grid_wait(const FwdParams& p, Ctx& c, uint32_t need_epo
     int ok = 1;
     if (need_epoch > 0 && c.lane == 0) {
         ok = 0;
-        const int target = (int)(need_epoch * gridDim.x);
-        for (uint32_t i = 0; i < kGridWaitLimit && !*c.abort_flag; i++) {
-            if (ld_acquire(p.sync + kSyncBar) >= target) { ok = 1; break; }
+        for (uint32_t i = 0; i < (kGridWaitLimit << 4) && !*c.abort_flag; i++) {
+            if (*c.s_epoch >= need_epoch) { ok = 1; break; }
         }
         if (!ok && !*c.abort_flag) raise_error(p, c, 11);
+        __threadfence();
     }
     ok = __shfl_sync(0xffffffffu, ok, 0);
     fence_proxy_async_all();       // activations were written through the generic proxy by other CTAs
     return ok != 0;
 }
 
-// ================================================================================ QMM, producer
-// Streams the weight records (and activation rows) of this CTA's items of one matmul phase into the
-// ring.  `need_epoch`: grid barriers that must have completed before the activations may be read.
-template <int MT, bool DUAL>
-__device__ void qmm_produce(const FwdParams& p, Ctx& c, const QDesc& d, uint32_t need_epoch, bool need_rstd) {
+// ================================================================================ QMM phases
+// Item = (group of TPI = 8/kw 16-row tiles [tile pairs gate/up in dual mode], K range).  The eight
+// consumer warps are arranged as TPI tiles x kw K-parts: warp (j, i) owns tile j of the item and, in
+// every ring stage, the chunks i, i+kw, ... of that stage.  The K-parts of a tile are added in
+// shared memory in part order, so small matrices need no split-K through global memory.  A stage
+// holds CPS = kw*U chunks: for every chunk the TPI records of the item's tiles (contiguous in the
+// streaming layout for TPI <= 4), then the same for up_proj in dual mode, then the activations of
+// the stage's K range (one bulk copy per token row).
+
+// Streams the weight records (and activation rows) of this CTA's items into the ring.
+// `need_epoch`: grid barriers that must have completed before the activations may be read.
+template <int MT>
+__device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QDesc& d, uint32_t need_epoch,
+                                            const bool dual) {
     using G = Geo<MT>;
-    constexpr int NB = DUAL ? 4 : 2;            // 64-row block cells per stage
-    constexpr int CPS = 8 / NB;                 // chunks per stage
-    constexpr int CELL = CPS * 4 * kRec;        // bytes of one block cell
-    constexpr int R = 128;
     const int lane = c.lane;
+    const int kw = d.pl.kw, U = d.pl.U;
+    const int TPI = kWN / kw, CPS = kw * U;
+    const int chunk_bytes = TPI * kRec;
+    const int up_off = CPS * chunk_bytes;
     const int nchunks_total = d.K / kChunkK;
     const int nblocks = (d.N + 63) / 64;
-    const int nitems = d.pl.row_tiles * d.pl.splits;
+    const int nitems = d.pl.row_items * d.pl.splits;
     if ((int)blockIdx.x >= nitems) return;
-    (void)R;
 
     bool ready = false;
     int npend = 0;
     uint32_t pend_slot[G::NST];
     int pend_k0[G::NST], pend_recs[G::NST];
 
-    auto issue_x = [&](uint32_t slot, int k0, int recs) {
-        if (lane < d.xrows)
-            bulk_copy_g2s(smem_u32(c.ring + slot * G::STAGE + kWArea + lane * kXPitch),
-                          d.x + (size_t)lane * d.K + k0, (uint32_t)(recs * kChunkK * 2), smem_u32(c.full + slot));
+    auto issue_x = [&](uint32_t slot, int k0, int recs) {       // one run: `recs` chunks x MP padded rows
+        if (lane == 0)
+            bulk_copy_g2s(smem_u32(c.ring + slot * G::STAGE + kWArea), d.x + (size_t)(k0 >> 7) * G::MP * kXRowH,
+                          (uint32_t)(recs * G::MP * kXRow), smem_u32(c.full + slot));
     };
     auto flush = [&]() -> bool {
         if (!producer_grid_wait(p, c, need_epoch)) return false;
@@ -246,34 +288,18 @@ __device__ void qmm_produce(const FwdParams& p, Ctx& c, const QDesc& d, uint32_t
             if (i < npend) issue_x(pend_slot[i], pend_k0[i], pend_recs[i]);
         npend = 0;
         ready = true;
-        if (need_rstd) {
-            float ss = 0.f;
-            if (lane < d.xrows) {
-#pragma unroll 8
-                for (int part = 0; part < d.ssq_parts; part++)
-                    ss += __ldcg(p.ssq + part * kSsqPitch + d.rstd_off + lane);
-            }
-            c.s_rstd[lane] = (lane < d.xrows) ? rsqrtf(ss / (float)p.H + p.eps) : 0.f;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(c.rstd_bar));
-        }
         return true;
     };
 
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-        const int row_tile = item % d.pl.row_tiles;
-        const int split = item / d.pl.row_tiles;
+        const int row_item = item % d.pl.row_items;
+        const int split = item / d.pl.row_items;
         const int c_begin = split * d.pl.chunks_per_split;
         const int n = min(d.pl.chunks_per_split, nchunks_total - c_begin);
         const int nst = (n + CPS - 1) / CPS;
         const bool last_item = item + (int)gridDim.x >= nitems;
-        const unsigned char* src[NB];
-#pragma unroll
-        for (int b = 0; b < NB; b++) {
-            const int blk = min(row_tile * 2 + (b & 1), nblocks - 1);
-            const unsigned char* base = (DUAL && b >= 2) ? d.w1 : d.w0;
-            src[b] = base + ((size_t)blk * nchunks_total + c_begin) * 4 * kRec;
-        }
+        const int t0 = row_item * TPI;                     // first 16-row tile of the item
+        const int blk0 = min(t0 >> 2, nblocks - 1), blk1 = min((t0 >> 2) + 1, nblocks - 1);
         for (int st = 0; st < nst; st++, c.pos++) {
             const uint32_t slot = c.pos % G::NST, use = c.pos / G::NST;
             if (*c.abort_flag) return;
@@ -282,16 +308,34 @@ __device__ void qmm_produce(const FwdParams& p, Ctx& c, const QDesc& d, uint32_t
                 return;
             }
             const int recs = min(CPS, n - st * CPS);
+            const uint32_t fbar = smem_u32(c.full + slot);
+            const int nmat = dual ? 2 : 1;
             if (lane == 0) {
-                const uint32_t fbar = smem_u32(c.full + slot);
-                const uint32_t bytes = (uint32_t)(recs * 4 * kRec);
                 fence_proxy_async();
-                mbar_expect_tx(fbar, NB * bytes + (uint32_t)d.xrows * (uint32_t)(recs * kChunkK * 2));
-#pragma unroll
-                for (int b = 0; b < NB; b++)
-                    bulk_copy_g2s(smem_u32(c.ring + slot * G::STAGE + b * CELL), src[b] + (size_t)st * CELL, bytes, fbar);
+                mbar_expect_tx(fbar, (uint32_t)(nmat * recs * chunk_bytes) + (uint32_t)(recs * G::MP * kXRow));
             }
             __syncwarp();
+            unsigned char* stage = c.ring + slot * G::STAGE;
+            const size_t ch0 = (size_t)(c_begin + st * CPS);
+            if (TPI >= 4) {
+                // whole 64-row blocks: the stage's chunks of a block are one contiguous run
+                const int nb = TPI / 4;
+                if (lane < nb * nmat) {
+                    const int mtx = lane / nb, b = lane - mtx * nb;
+                    const unsigned char* wbase = mtx ? d.w1 : d.w0;
+                    bulk_copy_g2s(smem_u32(stage + mtx * up_off + b * CPS * 4 * kRec),
+                                  wbase + ((size_t)(b ? blk1 : blk0) * nchunks_total + ch0) * 4 * kRec,
+                                  (uint32_t)(recs * 4 * kRec), fbar);
+                }
+            } else {
+                for (int idx = lane; idx < recs * nmat; idx += 32) {     // part of a block: one copy per chunk
+                    const int mtx = idx / recs, cc = idx - mtx * recs;
+                    const unsigned char* wbase = mtx ? d.w1 : d.w0;
+                    bulk_copy_g2s(smem_u32(stage + mtx * up_off + cc * chunk_bytes),
+                                  wbase + (((size_t)blk0 * nchunks_total + ch0 + cc) * 4 + (t0 & 3)) * kRec,
+                                  (uint32_t)chunk_bytes, fbar);
+                }
+            }
             const int k0 = (c_begin + st * CPS) * kChunkK;
             if (ready) {
                 issue_x(slot, k0, recs);
@@ -308,31 +352,57 @@ __device__ void qmm_produce(const FwdParams& p, Ctx& c, const QDesc& d, uint32_t
     }
 }
 
-// ================================================================================ QMM, consumers
-template <int MT, bool DUAL, int EPI>
-__device__ void qmm_consume(const FwdParams& p, Ctx& c, const QDesc& d) {
+// rstd[m] = rsqrt(mean(h[m]^2) + eps) from the per-tile sums of squares the producer of h left in
+// p.ssq; all consumer threads, right after the grid barrier (overlaps the wait for the activations).
+__device__ __forceinline__ void compute_rstd(const FwdParams& p, Ctx& c, int rows) {
+    const int parts = p.H / 16;
+    const int l16 = threadIdx.x & 15;
+    for (int m0 = 0; m0 < rows; m0 += 16) {
+        const int m = m0 + (threadIdx.x >> 4);
+        float ss = 0.f;
+        for (int base = 0; base < parts; base += 256) {
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) {                 // sixteen independent loads in flight per thread
+                const int part = base + i * 16 + l16;
+                v[i] = (m < rows && part < parts) ? __ldcg(p.ssq + part * kSsqPitch + m) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; i++) ss += v[i];
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (l16 == 0 && m < rows) c.s_rstd[m] = rsqrtf(ss / (float)p.H + p.eps);
+    }
+    consumer_sync(kNCons);
+}
+
+template <int MT, bool DUAL>
+__device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QDesc& d, const int EPI) {
     using G = Geo<MT>;
-    constexpr int NB = DUAL ? 4 : 2;
-    constexpr int CPS = 8 / NB;
-    constexpr int CELL = CPS * 4 * kRec;
     constexpr int S = DUAL ? 2 : 1;
-    constexpr int R = 128;                       // output rows (of each matrix) per item
     constexpr int MP = MT * 8;
-    constexpr int TW = DUAL ? 2 * R : R;
-    constexpr bool NEED_RSTD = (EPI != EPI_RESID);
     const int lane = c.lane, warp = c.warp;
     const int g = lane >> 2, t = lane & 3;
+    const int kw = d.pl.kw, U = d.pl.U;
+    const int TPI = kWN / kw, CPS = kw * U;
+    const int R = TPI * 16;                      // output rows (of each matrix) per item
+    const int TW = S * R;
+    const int chunk_bytes = TPI * kRec;
+    const int up_off = CPS * chunk_bytes;
+    const int tj = warp / kw, ki = warp - tj * kw;    // tile of the item, K-part
+    // record of (chunk cc of the stage, tile tj): whole blocks arrive as [block][chunk][4 tiles], parts of a block as [chunk][tiles]
+    const int rec_base = (TPI >= 4) ? ((tj >> 2) * CPS * 4 * kRec + (tj & 3) * kRec) : tj * kRec;
+    const int rec_cstride = (TPI >= 4) ? 4 * kRec : chunk_bytes;
     const int nchunks_total = d.K / kChunkK;
-    const int nitems = d.pl.row_tiles * d.pl.splits;
-    bool rstd_ready = false;
-
-    int rec_off[S];
-#pragma unroll
-    for (int s = 0; s < S; s++) rec_off[s] = ((DUAL ? 2 * s : 0) + warp / 4) * CELL + (warp % 4) * kRec;
+    const int nitems = d.pl.row_items * d.pl.splits;
+    const bool need_rstd = (EPI != EPI_RESID);
+    bool rstd_done = !need_rstd;
+    stamp(p, c, 2);
 
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-        const int row_tile = item % d.pl.row_tiles;
-        const int split = item / d.pl.row_tiles;
+        const int row_item = item % d.pl.row_items;
+        const int split = item / d.pl.row_items;
         const int c_begin = split * d.pl.chunks_per_split;
         const int n = min(d.pl.chunks_per_split, nchunks_total - c_begin);
         const int nst = (n + CPS - 1) / CPS;
@@ -353,40 +423,39 @@ __device__ void qmm_consume(const FwdParams& p, Ctx& c, const QDesc& d) {
                 if (lane == 0) raise_error(p, c, 1);
             }
             ok = __all_sync(0xffffffffu, ok);      // warp-uniform: the MMA path below needs all lanes
+            if (st == 0 && item == (int)blockIdx.x) stamp(p, c, 4);
             if (ok) {
                 const unsigned char* stage = c.ring + slot * G::STAGE;
+                const int nrec = min(CPS, n - st * CPS);
+                for (int cc = ki; cc < nrec; cc += kw) {
+                    const unsigned char* xrow = stage + kWArea + (cc * MP + g) * kXRow + t * 16;
+                    uint4 w[S][2];
+                    uint2 sb[S][2];
 #pragma unroll
-                for (int cc = 0; cc < CPS; cc++) {
-                    if (st * CPS + cc < n) {
-                        const unsigned char* xrow = stage + kWArea + g * kXPitch + cc * (kChunkK * 2) + t * 16;
-                        uint4 w[S][2];
-                        uint2 sb[S][2];
+                    for (int s = 0; s < S; s++) {
+                        const unsigned char* rec = stage + s * up_off + cc * rec_cstride + rec_base;
+                        w[s][0] = *reinterpret_cast<const uint4*>(rec + lane * 16);
+                        w[s][1] = *reinterpret_cast<const uint4*>(rec + 512 + lane * 16);
+                        sb[s][0] = *reinterpret_cast<const uint2*>(rec + 1024 + g * 8);
+                        sb[s][1] = *reinterpret_cast<const uint2*>(rec + 1024 + (8 + g) * 8);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        uint4 xb[MT];
+#pragma unroll
+                        for (int mt = 0; mt < MT; mt++)
+                            xb[mt] = *reinterpret_cast<const uint4*>(xrow + mt * 8 * kXRow + j * 64);
 #pragma unroll
                         for (int s = 0; s < S; s++) {
-                            const unsigned char* rec = stage + rec_off[s] + cc * 4 * kRec;
-                            w[s][0] = *reinterpret_cast<const uint4*>(rec + lane * 16);
-                            w[s][1] = *reinterpret_cast<const uint4*>(rec + 512 + lane * 16);
-                            sb[s][0] = *reinterpret_cast<const uint2*>(rec + 1024 + g * 8);
-                            sb[s][1] = *reinterpret_cast<const uint2*>(rec + 1024 + (8 + g) * 8);
-                        }
+                            const __half2 p0 = u32_as_h2((j < 2) ? sb[s][0].x : sb[s][0].y);   // {scale, bias}
+                            const __half2 p1 = u32_as_h2((j < 2) ? sb[s][1].x : sb[s][1].y);
+                            uint32_t d0[4], d1[4];
+                            dequant_pack(comp(w[s][0], j), __low2half2(p0), __high2half2(p0), d0);
+                            dequant_pack(comp(w[s][1], j), __low2half2(p1), __high2half2(p1), d1);
 #pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            uint4 xb[MT];
-#pragma unroll
-                            for (int mt = 0; mt < MT; mt++)
-                                xb[mt] = *reinterpret_cast<const uint4*>(xrow + mt * 8 * kXPitch + j * 64);
-#pragma unroll
-                            for (int s = 0; s < S; s++) {
-                                const __half2 p0 = u32_as_h2((j < 2) ? sb[s][0].x : sb[s][0].y);   // {scale, bias}
-                                const __half2 p1 = u32_as_h2((j < 2) ? sb[s][1].x : sb[s][1].y);
-                                uint32_t d0[4], d1[4];
-                                dequant_pack(comp(w[s][0], j), __low2half2(p0), __high2half2(p0), d0);
-                                dequant_pack(comp(w[s][1], j), __low2half2(p1), __high2half2(p1), d1);
-#pragma unroll
-                                for (int mt = 0; mt < MT; mt++) {
-                                    mma_m16n8k16(acc[s][mt], d0[0], d1[0], d0[1], d1[1], xb[mt].x, xb[mt].y);
-                                    mma_m16n8k16(acc[s][mt], d0[2], d1[2], d0[3], d1[3], xb[mt].z, xb[mt].w);
-                                }
+                            for (int mt = 0; mt < MT; mt++) {
+                                mma_m16n8k16(acc[s][mt], d0[0], d1[0], d0[1], d1[1], xb[mt].x, xb[mt].y);
+                                mma_m16n8k16(acc[s][mt], d0[2], d1[2], d0[3], d1[3], xb[mt].z, xb[mt].w);
                             }
                         }
                     }
@@ -396,56 +465,84 @@ __device__ void qmm_consume(const FwdParams& p, Ctx& c, const QDesc& d) {
             if (lane == 0) mbar_arrive(smem_u32(c.empty + slot));
         }
 
-        if (NEED_RSTD && !rstd_ready) {
-            if (!*c.abort_flag && !fwd_wait(smem_u32(c.rstd_bar), c.rstd_n & 1u)) {
-                if (lane == 0) raise_error(p, c, 3);
-            }
-            c.rstd_n++;
-            rstd_ready = true;
+        stamp(p, c, 5);
+        if (!rstd_done) {             // the per-token 1/rms of the input, needed by the epilogue only
+            compute_rstd(p, c, d.xrows);
+            rstd_done = true;
         }
-
-        // lane (g,t) holds, per sub-tile and token tile: rows g / g+8 x tokens 2t / 2t+1
-        const bool via_partials = (EPI == EPI_RESID) || d.pl.splits > 1;
-        if (via_partials) {
-            float* mine = p.partial + ((size_t)split * d.pl.row_tiles + row_tile) * MP * TW;
+        stamp(p, c, 3);
+        // ---- K-parts of a tile -> its first warp, through shared memory, in part order
+        if (kw > 1) {
+            float4* sc = reinterpret_cast<float4*>(c.scratch);
+            if (ki != 0) {
 #pragma unroll
-            for (int s = 0; s < S; s++) {
-                const int ri = s * R + warp * 16;
+                for (int s = 0; s < S; s++)
 #pragma unroll
-                for (int mt = 0; mt < MT; mt++) {
-                    const int tok = mt * 8 + 2 * t;
-                    mine[(size_t)tok * TW + ri + g] = acc[s][mt][0];
-                    mine[(size_t)(tok + 1) * TW + ri + g] = acc[s][mt][1];
-                    mine[(size_t)tok * TW + ri + g + 8] = acc[s][mt][2];
-                    mine[(size_t)(tok + 1) * TW + ri + g + 8] = acc[s][mt][3];
+                    for (int mt = 0; mt < MT; mt++)
+                        sc[((warp * S + s) * MT + mt) * 32 + lane] =
+                            make_float4(acc[s][mt][0], acc[s][mt][1], acc[s][mt][2], acc[s][mt][3]);
+            }
+            consumer_sync(kNCons);
+            if (ki == 0) {
+                for (int i = 1; i < kw; i++) {
+#pragma unroll
+                    for (int s = 0; s < S; s++)
+#pragma unroll
+                        for (int mt = 0; mt < MT; mt++) {
+                            const float4 v = sc[(((warp + i) * S + s) * MT + mt) * 32 + lane];
+                            acc[s][mt][0] += v.x; acc[s][mt][1] += v.y; acc[s][mt][2] += v.z; acc[s][mt][3] += v.w;
+                        }
                 }
             }
-            __threadfence();
+            consumer_sync(kNCons);         // scratch is rewritten by the next item
+        }
+        const bool leader = (ki == 0);
+        stamp(p, c, 6);
+
+        // lane (g,t) of a tile's first warp holds, per matrix and token tile: rows g / g+8 x tokens 2t / 2t+1
+        const int tile_global = row_item * TPI + tj;
+        if (d.pl.splits > 1) {
+            // ---- split-K across CTAs: partial sums through global memory, last CTA of the row item reduces
+            float* mine = p.partial + ((size_t)split * d.pl.row_items + row_item) * MP * TW;
+            if (leader) {
+#pragma unroll
+                for (int s = 0; s < S; s++) {
+                    const int ri = s * R + tj * 16;
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++) {
+                        const int tok = mt * 8 + 2 * t;
+                        mine[(size_t)tok * TW + ri + g] = acc[s][mt][0];
+                        mine[(size_t)(tok + 1) * TW + ri + g] = acc[s][mt][1];
+                        mine[(size_t)tok * TW + ri + g + 8] = acc[s][mt][2];
+                        mine[(size_t)(tok + 1) * TW + ri + g + 8] = acc[s][mt][3];
+                    }
+                }
+            }
             consumer_sync(kNCons);
             if (threadIdx.x == 0) {
-                const int old = atomicAdd(p.counter + row_tile, 1);
+                __threadfence();
+                const int old = atomicAdd(p.counter + row_item, 1);
                 const int last = (old == d.pl.splits - 1);
                 *c.is_last = last;
-                if (last) p.counter[row_tile] = 0;
+                if (last) p.counter[row_item] = 0;
+                __threadfence();
             }
             consumer_sync(kNCons);
             if (*c.is_last) {
-                __threadfence();
-                // last CTA of the row tile: add the splits in split order, 8 outputs per thread step
-                constexpr int UPT = R / 8;           // 16 threads per token row
+                const int UPT = R / 8;               // threads per token row
                 const int units = d.xrows * UPT;
                 const int units32 = (units + 31) & ~31;
                 for (int i = threadIdx.x; i < units32; i += kNCons) {
                     const int tok = i / UPT;
                     const int c0 = (i - tok * UPT) * 8;
-                    const int n0 = row_tile * R + c0;
+                    const int n0 = row_item * R + c0;
                     const bool valid = i < units && n0 < d.N;
                     float a0[8], a1[8];
 #pragma unroll
                     for (int e = 0; e < 8; e++) a0[e] = a1[e] = 0.f;
                     if (valid) {
                         for (int sp = 0; sp < d.pl.splits; sp++) {
-                            const float* src = p.partial + ((size_t)sp * d.pl.row_tiles + row_tile) * MP * TW + (size_t)tok * TW + c0;
+                            const float* src = p.partial + ((size_t)sp * d.pl.row_items + row_item) * MP * TW + (size_t)tok * TW + c0;
                             const float4 u0 = __ldcg(reinterpret_cast<const float4*>(src));
                             const float4 u1 = __ldcg(reinterpret_cast<const float4*>(src) + 1);
                             a0[0] += u0.x; a0[1] += u0.y; a0[2] += u0.z; a0[3] += u0.w;
@@ -475,11 +572,10 @@ __device__ void qmm_consume(const FwdParams& p, Ctx& c, const QDesc& d) {
                                 hw[e] = __hmul(out[e], wh[e]);
                             }
                             *reinterpret_cast<uint4*>(p.h + (size_t)tok * d.N + n0) = *reinterpret_cast<const uint4*>(out);
-                            *reinterpret_cast<uint4*>(p.hw + (size_t)tok * d.N + n0) = *reinterpret_cast<const uint4*>(hw);
+                            *reinterpret_cast<uint4*>(p.hw + xt_index(tok, n0, MP)) = *reinterpret_cast<const uint4*>(hw);
                         }
-#pragma unroll
-                        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                        if (valid && (lane & 15) == 0) p.ssq[row_tile * kSsqPitch + tok] = ss;
+                        ss += __shfl_xor_sync(0xffffffffu, ss, 1);          // the two 8-column halves of a 16-row tile
+                        if (valid && (lane & 1) == 0) p.ssq[(n0 >> 4) * kSsqPitch + tok] = ss;
                     } else if (valid) {
                         const float rs = c.s_rstd[tok];
                         if (DUAL) {
@@ -495,30 +591,78 @@ __device__ void qmm_consume(const FwdParams& p, Ctx& c, const QDesc& d) {
                                 for (int e = 0; e < 8; e++) out[e] = __hadd(out[e], bh[e]);
                             }
                         }
-                        *reinterpret_cast<uint4*>(d.y + (size_t)tok * d.N + n0) = *reinterpret_cast<const uint4*>(out);
+                        if (d.y_tiled) {
+                            *reinterpret_cast<uint4*>(d.y + xt_index(tok, n0, MP)) = *reinterpret_cast<const uint4*>(out);
+                        } else if (tok >= d.row_lo && tok < d.row_lo + d.row_cnt) {
+                            *reinterpret_cast<uint4*>(d.y + (size_t)(tok - d.row_lo) * d.N + n0) = *reinterpret_cast<const uint4*>(out);
+                        }
                     }
                 }
             }
             consumer_sync(kNCons);     // is_last is rewritten by the next item
-        } else {
-            // direct epilogue from registers (QKV / SILU / HEAD without split-K)
-            const int nbase = row_tile * R + warp * 16 + g;
+        } else if (leader) {
+            // ---- direct epilogue from the registers of the tile's first warp
+            const int nbase = tile_global * 16 + g;
+            if (EPI == EPI_RESID) {
+                // residuals and norm weights first, all loads in flight together (h is read and written here)
+                unsigned short res[MT][4];
 #pragma unroll
-            for (int mt = 0; mt < MT; mt++) {
+                for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int tok = mt * 8 + 2 * t + (i & 1);
-                    const int nn = nbase + ((i >> 1) ? 8 : 0);
-                    if (tok >= d.xrows || nn >= d.N) continue;
-                    const float rs = c.s_rstd[tok];
-                    __half o;
-                    if (DUAL) {
-                        o = __float2half_rn(silu_mul_f16(acc[0][mt][i] * rs, acc[S - 1][mt][i] * rs));
-                    } else {
-                        o = __float2half_rn(acc[0][mt][i] * rs);
-                        if (d.bias != nullptr) o = __hadd(o, d.bias[nn]);
+                    for (int i = 0; i < 4; i++) {
+                        const int tok = mt * 8 + 2 * t + (i & 1);
+                        const int nn = nbase + ((i >> 1) ? 8 : 0);
+                        res[mt][i] = (tok < d.xrows && nn < d.N)
+                                         ? __ldcg(reinterpret_cast<const unsigned short*>(p.h) + (size_t)tok * d.N + nn) : (unsigned short)0;
                     }
-                    d.y[(size_t)tok * d.N + nn] = o;
+                const __half wn0 = nbase < d.N ? d.wn[nbase] : __ushort_as_half(0);
+                const __half wn8 = nbase + 8 < d.N ? d.wn[nbase + 8] : __ushort_as_half(0);
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    float ss0 = 0.f, ss1 = 0.f;            // tokens 2t, 2t+1 of this token tile
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int tok = mt * 8 + 2 * t + (i & 1);
+                        const int nn = nbase + ((i >> 1) ? 8 : 0);
+                        if (tok < d.xrows && nn < d.N) {
+                            const __half r = __ushort_as_half(res[mt][i]);
+                            const __half o = __hadd(r, __float2half_rn(acc[0][mt][i]));
+                            const float f = __half2float(o);
+                            if (i & 1) ss1 += f * f; else ss0 += f * f;
+                            p.h[(size_t)tok * d.N + nn] = o;
+                            p.hw[xt_index(tok, nn, MP)] = __hmul(o, (i >> 1) ? wn8 : wn0);
+                        }
+                    }
+#pragma unroll
+                    for (int o = 4; o < 32; o <<= 1) {
+                        ss0 += __shfl_xor_sync(0xffffffffu, ss0, o);
+                        ss1 += __shfl_xor_sync(0xffffffffu, ss1, o);
+                    }
+                    if (g == 0 && tile_global * 16 < d.N) {
+                        const int tok = mt * 8 + 2 * t;
+                        if (tok < d.xrows) p.ssq[tile_global * kSsqPitch + tok] = ss0;
+                        if (tok + 1 < d.xrows) p.ssq[tile_global * kSsqPitch + tok + 1] = ss1;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int tok = mt * 8 + 2 * t + (i & 1);
+                        const int nn = nbase + ((i >> 1) ? 8 : 0);
+                        if (tok >= d.xrows || nn >= d.N) continue;
+                        const float rs = c.s_rstd[tok];
+                        __half o;
+                        if (DUAL) {
+                            o = __float2half_rn(silu_mul_f16(acc[0][mt][i] * rs, acc[S - 1][mt][i] * rs));
+                        } else {
+                            o = __float2half_rn(acc[0][mt][i] * rs);
+                            if (d.bias != nullptr) o = __hadd(o, d.bias[nn]);
+                        }
+                        if (d.y_tiled) d.y[xt_index(tok, nn, MP)] = o;
+                        else if (tok >= d.row_lo && tok < d.row_lo + d.row_cnt) d.y[(size_t)(tok - d.row_lo) * d.N + nn] = o;
+                    }
                 }
             }
         }
@@ -526,12 +670,12 @@ __device__ void qmm_consume(const FwdParams& p, Ctx& c, const QDesc& d) {
 }
 
 // ================================================================================ phase 0
-__device__ void embed_phase(const FwdParams& p, Ctx& c) {
+__device__ __forceinline__ void embed_phase(const FwdParams& p, Ctx& c) {
     const int lane = c.lane;
     const int NP = p.H / 128;
     const int units = p.M * NP;                         // (token, 128-column part), one half-warp each
     const int pairs = (units + 1) / 2;
-    const __half* wn = p.layers[0].norm_in;
+    const __half* wn = c.ltab[0].norm_in;
     for (int pr = blockIdx.x * kWN + c.warp; pr < pairs; pr += gridDim.x * kWN) {
         const int u = pr * 2 + (lane >> 4);
         const bool valid = u < units;
@@ -556,13 +700,12 @@ __device__ void embed_phase(const FwdParams& p, Ctx& c) {
         }
         if (valid) {
             *reinterpret_cast<uint4*>(p.h + (size_t)m * p.H + pack * 8) = *reinterpret_cast<const uint4*>(o);
-            *reinterpret_cast<uint4*>(p.hw + (size_t)m * p.H + pack * 8) = *reinterpret_cast<const uint4*>(ow);
+            *reinterpret_cast<uint4*>(p.hw + xt_index(m, pack * 8, p.mp)) = *reinterpret_cast<const uint4*>(ow);
         } else {
             ss = 0.f;
         }
-#pragma unroll
-        for (int o2 = 8; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
-        if (valid && (lane & 15) == 0) p.ssq[part * kSsqPitch + m] = ss;
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);          // two packs = one 16-column part
+        if (valid && (lane & 1) == 0) p.ssq[(pack >> 1) * kSsqPitch + m] = ss;
     }
     // RoPE table: cs[m][i] = (cos, sin) of (scaling * inv_freq[i]) * pos[m]; one CTA per token, from the far end
     for (int m = (int)gridDim.x - 1 - (int)blockIdx.x; m < p.M; m += (int)gridDim.x) {
@@ -583,8 +726,38 @@ struct ADesc {
     int prefix, total, nact;
 };
 
+// 16-byte asynchronous copy global -> shared; bytes beyond src_bytes are written as zero.
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// Makes `bar` wait for every cp.async this thread has issued so far (pending count +1 now, -1 on completion).
+__device__ __forceinline__ void cp_async_track(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+
+// One 64-key block of K and V, cache rows -> padded shared rows, by one warp: each lane owns one
+// 16-byte column of the row and walks the rows (no divisions, two copies per step).
+template <int HD>
+__device__ __forceinline__ void kv_block_copy(uint32_t sk, uint32_t sv, const __half* kbase, const __half* vbase,
+                                              int rows, int lane) {
+    constexpr int KS = HD + 8;
+    constexpr int VPR = HD / 8;                 // 16-byte vectors per row: 8 or 16
+    constexpr int RPS = 32 / VPR;               // rows per step of the warp: 4 or 2
+    const int cv = lane % VPR, r0 = lane / VPR;
+    const __half* kp = kbase + cv * 8;
+    const __half* vp = vbase + cv * 8;
+    const uint32_t dk = sk + cv * 16, dv = sv + cv * 16;
+#pragma unroll 4
+    for (int r = r0; r < kKeyBlock; r += RPS) {
+        const uint32_t nb = r < rows ? 16u : 0u;
+        const int rs = r < rows ? r : 0;
+        cp_async16_zfill(dk + r * (KS * 2), kp + (size_t)rs * HD, nb);
+        cp_async16_zfill(dv + r * (KS * 2), vp + (size_t)rs * HD, nb);
+    }
+}
+
 template <int MT, int HD>
-__device__ void attn_produce(const FwdParams& p, Ctx& c, const ADesc& a) {
+__device__ __forceinline__ void attn_produce(const FwdParams& p, Ctx& c, const ADesc& a) {
     using G = Geo<MT>;
     constexpr int KS = HD + 8;
     static_assert(2 * kKeyBlock * KS * 2 <= kWArea, "K/V block must fit the weight area of a stage");
@@ -601,23 +774,18 @@ __device__ void attn_produce(const FwdParams& p, Ctx& c, const ADesc& a) {
             return;
         }
         const uint32_t fbar = smem_u32(c.full + slot);
-        if (lane == 0) {
-            fence_proxy_async();
-            mbar_expect_tx(fbar, (uint32_t)rows * HD * 2 * 2);
-        }
-        __syncwarp();
-        unsigned char* stage = c.ring + slot * G::STAGE;
+        const uint32_t sk = smem_u32(c.ring + slot * G::STAGE);
         const __half* kbase = a.kc + ((size_t)hk * p.cap + key0) * HD;
         const __half* vbase = a.vc + ((size_t)hk * p.cap + key0) * HD;
-        for (int r = lane; r < rows; r += 32) {
-            bulk_copy_g2s(smem_u32(stage + r * KS * 2), kbase + (size_t)r * HD, HD * 2, fbar);
-            bulk_copy_g2s(smem_u32(stage + (kKeyBlock + r) * KS * 2), vbase + (size_t)r * HD, HD * 2, fbar);
-        }
+        kv_block_copy<HD>(sk, sk + kKeyBlock * KS * 2, kbase, vbase, rows, lane);     // rows past the end become zero
+        cp_async_track(fbar);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(fbar);
     }
 }
 
 template <int MT, int HD>
-__device__ void attn_consume(const FwdParams& p, Ctx& c, const ADesc& a) {
+__device__ __forceinline__ void attn_consume(const FwdParams& p, Ctx& c, const ADesc& a) {
     using G = Geo<MT>;
     constexpr int KS = HD + 8;
     constexpr int VPR = HD / 8;
@@ -647,11 +815,7 @@ __device__ void attn_consume(const FwdParams& p, Ctx& c, const ADesc& a) {
             for (int idx = threadIdx.x; idx < kKeyBlock * VPR; idx += kNCons) {
                 const int r = idx / VPR, cv = idx - r * VPR;
                 const int key = key0 + r;
-                if (key >= a.total) {
-                    *reinterpret_cast<uint4*>(sk + r * KS + cv * 8) = make_uint4(0, 0, 0, 0);
-                    *reinterpret_cast<uint4*>(sv + r * KS + cv * 8) = make_uint4(0, 0, 0, 0);
-                    continue;
-                }
+                if (key >= a.total) continue;                  // zero-filled by the producer
                 const int m = key - new0;
                 if (m < 0 || m >= p.M) continue;
                 const __half* src = p.qkv + (size_t)m * p.NQKV;
@@ -809,9 +973,327 @@ __device__ void attn_consume(const FwdParams& p, Ctx& c, const ADesc& a) {
     }
 }
 
+// ---- single-phase attention for short contexts -----------------------------------------------------
+// When the cache is at most attn_fused_max key blocks long, splitting the keys across CTAs costs more
+// in barriers than it saves: one item is then (kv head, group of up to four 16-row query tiles, one per
+// warp and scheduler), the producer streams all key blocks of the head through the ring, every busy
+// warp keeps the running softmax state (max, sum, fp32 output) of its tile in registers and the
+// normalised output goes straight to `attn`; the merge phase and its barrier disappear.
+// K/V blocks arrive as TMA tiles (cp.async.bulk.tensor, 64 rows x 64 halves per box, 128-byte swizzle):
+// two to four copies per block, and the swizzle makes the fragment loads conflict-free without padding.
+constexpr int kAttnTG = 4;                    // query tiles (warps) per item
+constexpr int kBox = 64 * 128;                // bytes of one 64-row x 128-byte TMA box
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans_u(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+// 2-D tiled TMA load: box at (x = column in halves, y = row) of the tensor map -> shared memory.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// Byte offset of 16-byte vector v (of HD/8) of row r inside a swizzled K or V block (boxes of 8 vectors side by side).
+__device__ __forceinline__ uint32_t swz(int r, int v) {
+    return (uint32_t)((v >> 3) * kBox + r * 128 + (((v & 7) ^ (r & 7)) << 4));
+}
+
+template <int MT, int HD>
+__device__ __forceinline__ void attn_fused_produce(const FwdParams& p, Ctx& c, const ADesc& a, int layer) {
+    using G = Geo<MT>;
+    constexpr int NBX = HD / 64;                  // boxes per K (and per V) block
+    const int lane = c.lane;
+    const int Gq = p.Hq / p.Hkv;
+    const int ntiles = (p.M * Gq + 15) / 16;
+    const int ngroups = (ntiles + kAttnTG - 1) / kAttnTG;
+    const int nitems = p.Hkv * ngroups;
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+        const int hk = item / ngroups;
+        const int krow0 = ((layer * 2 + 0) * p.Hkv + hk) * p.cap;       // row of the cache viewed as [rows][HD]
+        const int vrow0 = ((layer * 2 + 1) * p.Hkv + hk) * p.cap;
+        for (int kb = 0; kb < a.nact; kb++, c.pos++) {
+            const uint32_t slot = c.pos % G::NST, use = c.pos / G::NST;
+            if (*c.abort_flag) return;
+            if (use > 0 && !__all_sync(0xffffffffu, fwd_wait(smem_u32(c.empty + slot), (use - 1) & 1u))) {
+                if (lane == 0) raise_error(p, c, 6);
+                return;
+            }
+            const uint32_t fbar = smem_u32(c.full + slot);
+            const uint32_t sk = smem_u32(c.ring + slot * G::STAGE);
+            if (lane == 0) {
+                fence_proxy_async();
+                mbar_expect_tx(fbar, 2 * NBX * kBox);
+            }
+            __syncwarp();
+            if (lane < 2 * NBX) {                  // K boxes, then V boxes
+                const int isv = lane / NBX, bx = lane - isv * NBX;
+                tma_load_2d(sk + lane * kBox, &p.kvmap, bx * 64, (isv ? vrow0 : krow0) + kb * kKeyBlock, fbar);
+            }
+        }
+    }
+}
+
+template <int MT, int HD>
+__device__ __forceinline__ void attn_fused_consume(const FwdParams& p, Ctx& c, const ADesc& a) {
+    using G = Geo<MT>;
+    constexpr int KS = HD + 8;                    // padded pitch of the query tile
+    constexpr int VPR = HD / 8;
+    constexpr int NBX = HD / 64;
+    static_assert(kWN * 16 * KS * 2 <= kScratch, "query tiles of all warps must fit the scratch area");
+    static_assert(2 * NBX * kBox <= kWArea, "a K/V block must fit the weight area of a stage");
+    const int lane = c.lane, warp = c.warp;
+    const int g = lane >> 2, t = lane & 3;
+    const int Gq = p.Hq / p.Hkv;
+    const int QR = p.M * Gq;
+    const int ntiles = (QR + 15) / 16;
+    const int ngroups = (ntiles + kAttnTG - 1) / kAttnTG;
+    const int nitems = p.Hkv * ngroups;
+    const int prefix = a.prefix;
+    const int new0 = prefix + p.write_off;
+
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+        const int hk = item / ngroups, tg = item - hk * ngroups;
+        const int rt = tg * kAttnTG + warp;
+        const bool has_tile = warp < kAttnTG && rt < ntiles;
+        const int r0 = rt * 16 + g, r1 = r0 + 8;
+        const bool v0 = has_tile && r0 < QR, v1 = has_tile && r1 < QR;
+        const int m0 = v0 ? r0 / Gq : 0, m1 = v1 ? r1 / Gq : 0;
+        const int h0 = hk * Gq + (v0 ? r0 - m0 * Gq : 0), h1 = hk * Gq + (v1 ? r1 - m1 * Gq : 0);
+        const unsigned long long mk0 = v0 ? p.mask[m0] : 0ull, mk1 = v1 ? p.mask[m1] : 0ull;
+
+        stamp(p, c, 2);
+        // rotated queries of this warp's tile -> its private padded tile in shared memory (A fragments are
+        // re-read per key block: that keeps 32 registers free for the output accumulators)
+        __half* sq = reinterpret_cast<__half*>(c.scratch) + warp * 16 * KS;
+        if (has_tile) {
+            constexpr int HV = VPR / 2;                       // vector pairs (i, i + HD/2) per row
+            for (int pi = lane; pi < 16 * HV; pi += 32) {
+                const int row = pi / HV, cv = pi - row * HV;
+                const int r = rt * 16 + row;
+                uint4 o1 = make_uint4(0, 0, 0, 0), o2 = make_uint4(0, 0, 0, 0);
+                if (r < QR) {
+                    const int m = r / Gq, hh = hk * Gq + (r - m * Gq);
+                    const __half* q = p.qkv + (size_t)m * p.NQKV + (size_t)hh * HD + cv * 8;
+                    const uint4 x1v = __ldcg(reinterpret_cast<const uint4*>(q));
+                    const uint4 x2v = __ldcg(reinterpret_cast<const uint4*>(q + HD / 2));
+                    const float4* csp = reinterpret_cast<const float4*>(p.cs + m * kCsPitch + cv * 8);
+                    float4 cs4[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) cs4[e] = __ldcg(csp + e);
+                    const __half* x1 = reinterpret_cast<const __half*>(&x1v);
+                    const __half* x2 = reinterpret_cast<const __half*>(&x2v);
+                    __half* q1 = reinterpret_cast<__half*>(&o1);
+                    __half* q2 = reinterpret_cast<__half*>(&o2);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const float co = (e & 1) ? cs4[e >> 1].z : cs4[e >> 1].x;
+                        const float si = (e & 1) ? cs4[e >> 1].w : cs4[e >> 1].y;
+                        const float a1 = __half2float(x1[e]), a2 = __half2float(x2[e]);
+                        q1[e] = __float2half_rn(a1 * co - a2 * si);
+                        q2[e] = __float2half_rn(a1 * si + a2 * co);
+                    }
+                }
+                *reinterpret_cast<uint4*>(sq + row * KS + cv * 8) = o1;
+                *reinterpret_cast<uint4*>(sq + row * KS + HD / 2 + cv * 8) = o2;
+            }
+        }
+        __syncwarp();
+        stamp(p, c, 3);
+        const uint32_t sq_frag = smem_u32(sq + ((lane & 7) + ((lane >> 3) & 1) * 8) * KS + (lane >> 4) * 8);
+
+        float mrun0 = -INFINITY, mrun1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+        float o[HD / 8][4];
+#pragma unroll
+        for (int nd = 0; nd < HD / 8; nd++) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.f;
+
+        for (int kb = 0; kb < a.nact; kb++, c.pos++) {
+            const int key0 = kb * kKeyBlock;
+            const uint32_t slot = c.pos % G::NST;
+            bool ok = !*c.abort_flag;
+            if (ok && !fwd_wait(smem_u32(c.full + slot), (c.pos / G::NST) & 1u)) {
+                ok = false;
+                if (lane == 0) raise_error(p, c, 7);
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (kb == 0) stamp(p, c, 4);
+            unsigned char* skp = c.ring + slot * G::STAGE;
+            const uint32_t sk = smem_u32(skp), sv = sk + NBX * kBox;
+            // the block that holds this pass's own rows: take them from the qkv buffer (k rotated) and append them to the cache
+            const bool patch = key0 + kKeyBlock > new0 && key0 < new0 + p.M;
+            if (patch) {
+                if (ok) {
+                    for (int idx = threadIdx.x; idx < p.M * VPR; idx += kNCons) {
+                        const int m = idx / VPR, cv = idx - m * VPR;
+                        const int key = new0 + m;
+                        const int r = key - key0;
+                        if (r < 0 || r >= kKeyBlock) continue;
+                        const bool writer = (tg == 0);             // one item per kv head appends to the cache
+                        const __half* src = p.qkv + (size_t)m * p.NQKV;
+                        const uint4 vv = __ldcg(reinterpret_cast<const uint4*>(src + (size_t)(p.Hq + p.Hkv) * HD + (size_t)hk * HD + cv * 8));
+                        *reinterpret_cast<uint4*>(skp + NBX * kBox + swz(r, cv)) = vv;
+                        if (writer && key < p.cap) *reinterpret_cast<uint4*>(a.vc + ((size_t)hk * p.cap + key) * HD + cv * 8) = vv;
+                        if (cv < VPR / 2) {
+                            const __half* ksrc = src + (size_t)p.Hq * HD + (size_t)hk * HD;
+                            const uint4 x1v = __ldcg(reinterpret_cast<const uint4*>(ksrc + cv * 8));
+                            const uint4 x2v = __ldcg(reinterpret_cast<const uint4*>(ksrc + HD / 2 + cv * 8));
+                            const float4* csp = reinterpret_cast<const float4*>(p.cs + m * kCsPitch + cv * 8);
+                            float4 cs4[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++) cs4[e] = __ldcg(csp + e);
+                            const __half* x1 = reinterpret_cast<const __half*>(&x1v);
+                            const __half* x2 = reinterpret_cast<const __half*>(&x2v);
+                            __align__(16) __half k1[8], k2[8];
+#pragma unroll
+                            for (int e = 0; e < 8; e++) {
+                                const float co = (e & 1) ? cs4[e >> 1].z : cs4[e >> 1].x;
+                                const float si = (e & 1) ? cs4[e >> 1].w : cs4[e >> 1].y;
+                                const float a1 = __half2float(x1[e]), a2 = __half2float(x2[e]);
+                                k1[e] = __float2half_rn(a1 * co - a2 * si);
+                                k2[e] = __float2half_rn(a1 * si + a2 * co);
+                            }
+                            *reinterpret_cast<uint4*>(skp + swz(r, cv)) = *reinterpret_cast<const uint4*>(k1);
+                            *reinterpret_cast<uint4*>(skp + swz(r, cv + VPR / 2)) = *reinterpret_cast<const uint4*>(k2);
+                            if (writer && key < p.cap) {
+                                __half* kd = a.kc + ((size_t)hk * p.cap + key) * HD;
+                                *reinterpret_cast<uint4*>(kd + cv * 8) = *reinterpret_cast<const uint4*>(k1);
+                                *reinterpret_cast<uint4*>(kd + HD / 2 + cv * 8) = *reinterpret_cast<const uint4*>(k2);
+                            }
+                        }
+                    }
+                    fence_proxy_async();       // the slot is refilled through the async proxy later
+                }
+                consumer_sync(kNCons);
+            }
+
+            if (ok && has_tile) {
+                const bool all_visible = key0 + kKeyBlock <= prefix;      // committed rows: no mask needed
+#pragma unroll
+                for (int half = 0; half < 2; half++) {         // 32 keys at a time keeps the scores in 16 registers
+                    float s[4][4];
+#pragma unroll
+                    for (int nt = 0; nt < 4; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+                    for (int ks = 0; ks < HD / 16; ks += 2) {
+                        uint32_t qa0[4], qa1[4];
+                        ldmatrix_x4(qa0, sq_frag + ks * 32);
+                        ldmatrix_x4(qa1, sq_frag + ks * 32 + 32);
+#pragma unroll
+                        for (int nt = 0; nt < 4; nt++) {
+                            uint32_t kf[4];
+                            // matrices: (keys, hd ks*16..+8), (keys, +8), (keys, (ks+1)*16..+8), (keys, +8)
+                            ldmatrix_x4(kf, sk + swz(half * 32 + nt * 8 + (lane & 7), ks * 2 + (lane >> 3)));
+                            mma_m16n8k16(s[nt], qa0[0], qa0[1], qa0[2], qa0[3], kf[0], kf[1]);
+                            mma_m16n8k16(s[nt], qa1[0], qa1[1], qa1[2], qa1[3], kf[2], kf[3]);
+                        }
+                    }
+                    float mx0 = mrun0, mx1 = mrun1;
+                    if (all_visible) {
+#pragma unroll
+                        for (int nt = 0; nt < 4; nt++) {
+#pragma unroll
+                            for (int e = 0; e < 2; e++) {
+                                s[nt][e] = v0 ? s[nt][e] * p.scale_log2 : -INFINITY;
+                                s[nt][2 + e] = v1 ? s[nt][2 + e] * p.scale_log2 : -INFINITY;
+                                mx0 = fmaxf(mx0, s[nt][e]);
+                                mx1 = fmaxf(mx1, s[nt][2 + e]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int nt = 0; nt < 4; nt++) {
+#pragma unroll
+                            for (int e = 0; e < 2; e++) {
+                                const int key = key0 + half * 32 + nt * 8 + 2 * t + e;
+                                const int j = key - prefix;
+                                const bool in_prefix = key < prefix;
+                                const bool in_tail = j >= 0 && j < p.tail;
+                                const int js = in_tail ? j : 0;
+                                const bool vis0 = v0 && (in_prefix || (in_tail && ((mk0 >> js) & 1ull)));
+                                const bool vis1 = v1 && (in_prefix || (in_tail && ((mk1 >> js) & 1ull)));
+                                s[nt][e] = vis0 ? s[nt][e] * p.scale_log2 : -INFINITY;
+                                s[nt][2 + e] = vis1 ? s[nt][2 + e] * p.scale_log2 : -INFINITY;
+                                mx0 = fmaxf(mx0, s[nt][e]);
+                                mx1 = fmaxf(mx1, s[nt][2 + e]);
+                            }
+                        }
+                    }
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                    const float base0 = (mx0 == -INFINITY) ? 0.f : mx0;
+                    const float base1 = (mx1 == -INFINITY) ? 0.f : mx1;
+                    if (mx0 != mrun0 || mx1 != mrun1) {        // the running maximum moved: rescale sums and outputs
+                        const float al0 = (mrun0 == -INFINITY) ? 0.f : exp2f(mrun0 - base0);
+                        const float al1 = (mrun1 == -INFINITY) ? 0.f : exp2f(mrun1 - base1);
+                        mrun0 = mx0;
+                        mrun1 = mx1;
+                        l0 *= al0;
+                        l1 *= al1;
+#pragma unroll
+                        for (int nd = 0; nd < HD / 8; nd++) {
+                            o[nd][0] *= al0; o[nd][1] *= al0; o[nd][2] *= al1; o[nd][3] *= al1;
+                        }
+                    }
+                    uint32_t pa[4][2];
+#pragma unroll
+                    for (int nt = 0; nt < 4; nt++) {
+                        const float p00 = exp2f(s[nt][0] - base0), p01 = exp2f(s[nt][1] - base0);
+                        const float p10 = exp2f(s[nt][2] - base1), p11 = exp2f(s[nt][3] - base1);
+                        const __half2 hh0 = __floats2half2_rn(p00, p01), hh1 = __floats2half2_rn(p10, p11);
+                        // the sum uses the rounded probabilities so that numerator and denominator agree
+                        l0 += __low2float(hh0) + __high2float(hh0);
+                        l1 += __low2float(hh1) + __high2float(hh1);
+                        pa[nt][0] = h2_as_u32(hh0);
+                        pa[nt][1] = h2_as_u32(hh1);
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < 2; kk++) {
+#pragma unroll
+                        for (int nd = 0; nd < HD / 8; nd += 2) {
+                            uint32_t vb[4];
+                            ldmatrix_x4_trans_u(vb, sv + swz(half * 32 + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), nd + (lane >> 4)));
+                            mma_m16n8k16(o[nd], pa[2 * kk][0], pa[2 * kk][1], pa[2 * kk + 1][0], pa[2 * kk + 1][1], vb[0], vb[1]);
+                            mma_m16n8k16(o[nd + 1], pa[2 * kk][0], pa[2 * kk][1], pa[2 * kk + 1][0], pa[2 * kk + 1][1], vb[2], vb[3]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(c.empty + slot));
+        }
+
+        stamp(p, c, 5);
+        // normalise and store: lane (g,t) holds rows r0 / r1, columns nd*8 + 2t, +1
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+        if (v0) {
+            __half* orow = p.attn + xt_index(m0, h0 * HD, p.mp) + 2 * t;      // a head's columns stay inside one 128-chunk
+#pragma unroll
+            for (int nd = 0; nd < HD / 8; nd++)
+                *reinterpret_cast<__half2*>(orow + nd * 8) = __floats2half2_rn(o[nd][0] * inv0, o[nd][1] * inv0);
+        }
+        if (v1) {
+            __half* orow = p.attn + xt_index(m1, h1 * HD, p.mp) + 2 * t;
+#pragma unroll
+            for (int nd = 0; nd < HD / 8; nd++)
+                *reinterpret_cast<__half2*>(orow + nd * 8) = __floats2half2_rn(o[nd][2] * inv1, o[nd][3] * inv1);
+        }
+    }
+}
+
 // Merge of the key blocks: one warp per (token, query head), blocks added in block order.
 template <int HD>
-__device__ void attn_merge(const FwdParams& p, Ctx& c, const ADesc& a) {
+__device__ __forceinline__ void attn_merge(const FwdParams& p, Ctx& c, const ADesc& a) {
     const int lane = c.lane;
     const int Gq = p.Hq / p.Hkv;
     const int nrows = p.M * p.Hq;
@@ -848,7 +1330,7 @@ __device__ void attn_merge(const FwdParams& p, Ctx& c, const ADesc& a) {
             }
         }
         const float inv = denom > 0.f ? 1.f / denom : 0.f;
-        __half* orow = p.attn + (size_t)m * p.Hq * HD + (size_t)head * HD;
+        __half* orow = p.attn + xt_index(m, head * HD, p.mp);
 #pragma unroll
         for (int cc = 0; cc < CPT; cc++) orow[lane + 32 * cc] = __float2half_rn(acc[cc] * inv);
     }
@@ -858,31 +1340,39 @@ __device__ void attn_merge(const FwdParams& p, Ctx& c, const ADesc& a) {
 template <int MT, int HD>
 __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_constant__ FwdParams p) {
     using G = Geo<MT>;
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];      // swizzled TMA boxes want 1024-byte aligned stages
     __shared__ int s_abort, s_is_last;
+    __shared__ uint32_t s_epoch;
     __shared__ float s_rstd[32];
     Ctx c;
     c.ring = smem;
     c.full = reinterpret_cast<uint64_t*>(smem + G::NST * G::STAGE);
     c.empty = c.full + G::NST;
-    c.rstd_bar = c.empty + G::NST;
+    c.scratch = smem + G::NST * G::STAGE + 128;
+    {
+        // every phase needs its layer's pointers the moment a barrier opens: keep the table on chip
+        uint4* dst = reinterpret_cast<uint4*>(c.scratch + kScratch);
+        const uint4* src = reinterpret_cast<const uint4*>(p.layers);
+        for (int i = threadIdx.x; i < p.L * 4; i += kFwdThreads) dst[i] = src[i];
+        c.ltab = reinterpret_cast<const LayerPtrs*>(dst);
+    }
     c.abort_flag = &s_abort;
+    c.s_epoch = &s_epoch;
     c.is_last = &s_is_last;
     c.s_rstd = s_rstd;
     c.pos = 0;
     c.epoch = 0;
-    c.rstd_n = 0;
     c.lane = threadIdx.x & 31;
     c.warp = threadIdx.x >> 5;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
+        s_epoch = 0;
 #pragma unroll
         for (int s = 0; s < G::NST; s++) {
             mbar_init(smem_u32(c.full + s), 1);
             mbar_init(smem_u32(c.empty + s), kWN);
         }
-        mbar_init(smem_u32(c.rstd_bar), 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
@@ -894,67 +1384,79 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
     ad.prefix = prefix;
     ad.total = prefix + p.tail;
     ad.nact = min((ad.total + kKeyBlock - 1) / kKeyBlock, p.nkb);
-    const int ssq_parts = p.H / 128;
+    ad.kc = ad.vc = nullptr;
+    const bool attn_fused = ad.nact <= p.attn_fused_max;
 
-    // ---- phase 0
-    if (!producer) {
-        embed_phase(p, c);
-        grid_barrier(p, c);
-    } else {
-        c.epoch++;
-    }
-
-    for (int l = 0; l < p.L; l++) {
-        const LayerPtrs lp = p.layers[l];
-        ad.kc = p.kv + (size_t)l * p.kv_layer_stride;
-        ad.vc = ad.kc + p.kv_half_stride;
-        QDesc d;
-        d.xrows = p.M;
-        d.rstd_off = 0;
-        d.ssq_parts = ssq_parts;
-        // ---- A: q|k|v
-        d.x = p.hw; d.w0 = lp.qkv_w; d.w1 = nullptr; d.bias = lp.qkv_bias; d.wn = nullptr; d.y = p.qkv;
-        d.N = p.NQKV; d.K = p.H; d.pl = p.plan[PLAN_A];
-        if (producer) { qmm_produce<MT, false>(p, c, d, c.epoch, true); c.epoch++; }
-        else { qmm_consume<MT, false, EPI_QKV>(p, c, d); grid_barrier(p, c); }
-        // ---- B1: attention partials (K/V blocks do not depend on this pass: no barrier for the producer)
-        if (producer) { attn_produce<MT, HD>(p, c, ad); c.epoch++; }
-        else { attn_consume<MT, HD>(p, c, ad); grid_barrier(p, c); }
-        // ---- B2: merge
-        if (producer) { c.epoch++; }
-        else { attn_merge<HD>(p, c, ad); grid_barrier(p, c); }
-        // ---- C: h += attn . Wo^T
-        d.x = p.attn; d.w0 = lp.o_w; d.bias = nullptr; d.wn = lp.norm_post; d.y = p.h;
-        d.N = p.H; d.K = p.Hq * p.HD; d.pl = p.plan[PLAN_C];
-        if (producer) { qmm_produce<MT, false>(p, c, d, c.epoch, false); c.epoch++; }
-        else { qmm_consume<MT, false, EPI_RESID>(p, c, d); grid_barrier(p, c); }
-        // ---- D: act = silu(gate) * up
-        d.x = p.hw; d.w0 = lp.gate_w; d.w1 = lp.up_w; d.wn = nullptr; d.y = p.act;
-        d.N = p.I; d.K = p.H; d.pl = p.plan[PLAN_D];
-        if (producer) { qmm_produce<MT, true>(p, c, d, c.epoch, true); c.epoch++; }
-        else { qmm_consume<MT, true, EPI_SILU>(p, c, d); grid_barrier(p, c); }
-        // ---- E: h += act . Wdown^T
-        d.x = p.act; d.w0 = lp.down_w; d.w1 = nullptr;
-        d.wn = (l + 1 < p.L) ? p.layers[l + 1].norm_in : p.final_norm; d.y = p.h;
-        d.N = p.H; d.K = p.I; d.pl = p.plan[PLAN_E];
-        if (producer) { qmm_produce<MT, false>(p, c, d, c.epoch, false); c.epoch++; }
-        else { qmm_consume<MT, false, EPI_RESID>(p, c, d); grid_barrier(p, c); }
-    }
-
-    // ---- vocabulary projection on the selected rows
-    {
-        QDesc d;
-        d.xrows = p.rows_out;
-        d.rstd_off = row_off;
-        d.ssq_parts = ssq_parts;
-        d.x = p.hw + (size_t)row_off * p.H; d.w0 = p.head_w; d.w1 = nullptr; d.bias = nullptr; d.wn = nullptr;
-        d.y = p.logits; d.N = p.V; d.K = p.H; d.pl = p.plan[PLAN_HEAD];
-        if (producer) qmm_produce<MT, false>(p, c, d, c.epoch, true);
-        else qmm_consume<MT, false, EPI_HEAD>(p, c, d);
+    // Phases in order: 0 = embedding, then per layer A, B1, B2, C, D, E, last = vocabulary projection.
+    // One code path per kind (the four single-matrix products share one), a device-wide barrier after
+    // every executed phase but the last.  phase_mask (one bit per kind) selects kinds for profiling.
+    const int nph = 6 * p.L + 2;
+    for (int ph = 0; ph < nph; ph++) {
+        int kind = K_HEAD, l = 0;
+        if (ph == 0) {
+            kind = K_EMBED;
+        } else if (ph < nph - 1) {
+            l = (ph - 1) / 6;
+            kind = K_A + (ph - 1) - 6 * l;
+        }
+        if (!((p.phase_mask >> kind) & 1u)) continue;
+        if (kind == K_EMBED) {
+            if (!producer) embed_phase(p, c);
+        } else if (kind == K_B1) {
+            ad.kc = p.kv + (size_t)l * p.kv_layer_stride;
+            ad.vc = ad.kc + p.kv_half_stride;
+            if (attn_fused) {
+                if (producer) attn_fused_produce<MT, HD>(p, c, ad, l);
+                else attn_fused_consume<MT, HD>(p, c, ad);
+            } else {
+                if (producer) attn_produce<MT, HD>(p, c, ad);
+                else attn_consume<MT, HD>(p, c, ad);
+            }
+        } else if (kind == K_B2) {
+            if (attn_fused) continue;                      // no merge phase and no barrier in single-phase mode
+            if (!producer) attn_merge<HD>(p, c, ad);
+        } else {
+            const LayerPtrs lp = c.ltab[l];
+            QDesc d;
+            d.xrows = p.M;
+            d.row_lo = 0; d.row_cnt = p.M;
+            d.y_tiled = false;
+            d.w1 = nullptr; d.bias = nullptr; d.wn = nullptr;
+            int epi = EPI_RESID;
+            if (kind == K_A) {
+                d.x = p.hw; d.w0 = lp.qkv_w; d.bias = lp.qkv_bias; d.y = p.qkv;
+                d.N = p.NQKV; d.K = p.H; d.pl = p.plan[PLAN_A]; epi = EPI_QKV;
+            } else if (kind == K_C) {
+                d.x = p.attn; d.w0 = lp.o_w; d.wn = lp.norm_post; d.y = p.h;
+                d.N = p.H; d.K = p.Hq * p.HD; d.pl = p.plan[PLAN_C];
+            } else if (kind == K_D) {
+                d.x = p.hw; d.w0 = lp.gate_w; d.w1 = lp.up_w; d.y = p.act; d.y_tiled = true;
+                d.N = p.I; d.K = p.H; d.pl = p.plan[PLAN_D]; epi = EPI_SILU;
+            } else if (kind == K_E) {
+                d.x = p.act; d.w0 = lp.down_w;
+                d.wn = (l + 1 < p.L) ? c.ltab[l + 1].norm_in : p.final_norm; d.y = p.h;
+                d.N = p.H; d.K = p.I; d.pl = p.plan[PLAN_E];
+            } else {                                   // K_HEAD, on the selected rows
+                d.row_lo = row_off; d.row_cnt = p.rows_out;       // all rows are multiplied, the selected ones stored
+                d.x = p.hw; d.w0 = p.head_w; d.y = p.logits;
+                d.N = p.V; d.K = p.H; d.pl = p.plan[PLAN_HEAD]; epi = EPI_HEAD;
+            }
+            if (producer) {
+                qmm_produce<MT>(p, c, d, c.epoch, kind == K_D);
+            } else if (kind == K_D) {
+                qmm_consume<MT, true>(p, c, d, EPI_SILU);
+            } else {
+                qmm_consume<MT, false>(p, c, d, epi);
+            }
+        }
+        if (kind != K_HEAD) {
+            if (producer) c.epoch++;
+            else grid_barrier(p, c);
+        }
     }
 
     if (threadIdx.x == 0 && p.timeline != nullptr && (int)c.epoch < p.timeline_pitch)
-        p.timeline[((size_t)blockIdx.x * p.timeline_pitch + c.epoch) * 2] = global_ns();
+        p.timeline[((size_t)blockIdx.x * p.timeline_pitch + c.epoch) * 8] = global_ns();
     // ---- leave: the last CTA out resets the barrier words for the next launch (not after an error)
     __syncthreads();
     if (threadIdx.x == 0 && !s_abort) {
@@ -967,25 +1469,51 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
     }
 }
 
-PhasePlan make_plan(int N, int K, int grid, bool allow_split) {
-    PhasePlan pl{};
-    pl.row_tiles = (N + 127) / 128;
+// Chooses, for one matmul phase, how the eight consumer warps split an item (kw K-parts x 8/kw
+// tiles) and whether K is also split across CTAs, with a small cost model in microseconds: a warp
+// spends about half a microsecond per record while all warps of an SM stream, a shared-memory
+// K reduction costs a few tenths, a split through global memory about three (partial sums out,
+// ticket, partial sums back in).
+PhasePlan make_plan(int N, int K, int grid, int mt, bool dual) {
     const int nchunks = K / kChunkK;
-    int splits = 1;
-    if (allow_split && pl.row_tiles < grid && pl.row_tiles < kMaxCounters) {
-        splits = grid / pl.row_tiles;
-        const int max_splits = (nchunks + 3) / 4;
-        if (splits > max_splits) splits = max_splits;
-        if (splits < 1) splits = 1;
+    const int tiles = (N + 15) / 16;
+    const int cps_max = mt == 1 ? 8 : (mt == 2 ? 4 : 2);
+    const int umax = dual ? 2 : 4;                      // weight area: 32 records = 16 pairs per stage
+    PhasePlan best{};
+    double best_cost = 1e30;
+    for (int kw = 1; kw <= 8; kw *= 2) {
+        if (kw > cps_max || kw > nchunks) continue;
+        if (dual && mt >= 3 && kw > 1) continue;        // the K-part scratch holds 8 warps x 2 matrices x 2 token tiles
+        const int tpi = kWN / kw;
+        const int row_items = (tiles + tpi - 1) / tpi;
+        int U = cps_max / kw;
+        if (U > umax) U = umax;
+        const int max_splits = row_items < kMaxCounters ? (nchunks + 3) / 4 : 1;
+        for (int splits = 1; splits <= max_splits; splits++) {
+            const int cps = (nchunks + splits - 1) / splits;
+            const int eff = (nchunks + cps - 1) / cps;
+            if (eff != splits) continue;
+            const long long items = (long long)row_items * splits;
+            const long long rounds = (items + grid - 1) / grid;
+            const int rec_per_warp = ((cps + kw - 1) / kw) * (dual ? 2 : 1);
+            // bulk copies cost ~0.06 us each to issue: whole blocks come as one run per stage, parts of a block chunk by chunk
+            const int stages = (cps + kw * U - 1) / (kw * U);
+            const int ops_per_stage = 1 + (dual ? 2 : 1) * (tpi >= 4 ? tpi / 4 : kw * U);
+            const double cost = rounds * (0.5 * rec_per_warp + 0.06 * stages * ops_per_stage + (kw > 1 ? 0.3 : 0.0) +
+                                          (splits > 1 ? 3.0 : 0.0) + 1.0);
+            if (cost < best_cost - 1e-9) {
+                best_cost = cost;
+                best.row_items = row_items; best.splits = splits; best.chunks_per_split = cps; best.kw = kw; best.U = U;
+            }
+            if (items >= 4LL * grid) break;             // more splits cannot help any more
+        }
     }
-    pl.chunks_per_split = (nchunks + splits - 1) / splits;
-    pl.splits = (nchunks + pl.chunks_per_split - 1) / pl.chunks_per_split;
-    return pl;
+    return best;
 }
 
-size_t partial_bytes(const PhasePlan& pl, int mp, bool dual, bool always) {
-    if (pl.splits <= 1 && !always) return 0;
-    return (size_t)pl.splits * pl.row_tiles * mp * (dual ? 256 : 128) * sizeof(float);
+size_t partial_bytes(const PhasePlan& pl, int mp, bool dual) {
+    if (pl.splits <= 1) return 0;
+    return (size_t)pl.splits * pl.row_items * mp * (dual ? 2 : 1) * (kWN / pl.kw) * 16 * sizeof(float);
 }
 
 struct WsLayout {
@@ -1009,12 +1537,12 @@ int fwd_grid() {
 bool fwd_shape_ok(const b200_forward_desc* d) {
     if (!d) return false;
     if (d->M < 1 || d->M > 32 || d->rows_out < 1 || d->rows_out > d->M) return false;
-    if (d->hidden < 128 || (d->hidden % 128) != 0 || d->hidden / 128 > kMaxSsqParts) return false;
+    if (d->hidden < 128 || (d->hidden % 128) != 0 || d->hidden / 16 > kMaxSsqParts) return false;
     if (d->intermediate < 128 || (d->intermediate % 128) != 0) return false;
     if (d->head_dim != 64 && d->head_dim != 128) return false;
     if (d->n_heads < 1 || d->n_kv_heads < 1 || (d->n_heads % d->n_kv_heads) != 0) return false;
     if (((d->n_heads * d->head_dim) % 128) != 0) return false;
-    if (d->vocab < 8 || (d->vocab % 8) != 0 || d->n_layers < 1) return false;
+    if (d->vocab < 8 || (d->vocab % 8) != 0 || d->n_layers < 1 || d->n_layers > kMaxLayers) return false;
     if (d->tail < 1 || d->tail > 64 || d->write_off < 0 || d->write_off + d->M > d->tail) return false;
     if (d->cache_rows < d->tail) return false;
     return true;
@@ -1024,20 +1552,25 @@ WsLayout fwd_layout(const b200_forward_desc* d, PhasePlan (&plan)[5]) {
     const int grid = fwd_grid();
     const int mp = ((d->M + 7) / 8) * 8;
     const int nqkv = (d->n_heads + 2 * d->n_kv_heads) * d->head_dim;
-    plan[PLAN_A] = make_plan(nqkv, d->hidden, grid, true);
-    plan[PLAN_C] = make_plan(d->hidden, d->n_heads * d->head_dim, grid, true);
-    plan[PLAN_D] = make_plan(d->intermediate, d->hidden, grid, true);
-    plan[PLAN_E] = make_plan(d->hidden, d->intermediate, grid, true);
-    plan[PLAN_HEAD] = make_plan(d->vocab, d->hidden, grid, true);
+    const int mt = mp / 8;
+    plan[PLAN_A] = make_plan(nqkv, d->hidden, grid, mt, false);
+    plan[PLAN_C] = make_plan(d->hidden, d->n_heads * d->head_dim, grid, mt, false);
+    plan[PLAN_D] = make_plan(d->intermediate, d->hidden, grid, mt, true);
+    plan[PLAN_E] = make_plan(d->hidden, d->intermediate, grid, mt, false);
+    plan[PLAN_HEAD] = make_plan(d->vocab, d->hidden, grid, mt, false);
+    // split-K scratch: sized for any row count up to 32, so one workspace serves every pass shape
     size_t pb = 0;
-    pb = std::max(pb, partial_bytes(plan[PLAN_A], mp, false, false));
-    pb = std::max(pb, partial_bytes(plan[PLAN_C], mp, false, true));
-    pb = std::max(pb, partial_bytes(plan[PLAN_D], mp, true, false));
-    pb = std::max(pb, partial_bytes(plan[PLAN_E], mp, false, true));
-    pb = std::max(pb, partial_bytes(plan[PLAN_HEAD], mp, false, false));
+    for (int m = 1; m <= 4; m++) {
+        PhasePlan q[5] = {make_plan(nqkv, d->hidden, grid, m, false),
+                          make_plan(d->hidden, d->n_heads * d->head_dim, grid, m, false),
+                          make_plan(d->intermediate, d->hidden, grid, m, true),
+                          make_plan(d->hidden, d->intermediate, grid, m, false),
+                          make_plan(d->vocab, d->hidden, grid, m, false)};
+        for (int i = 0; i < 5; i++) pb = std::max(pb, partial_bytes(q[i], m * 8, i == PLAN_D));
+    }
     WsLayout w{};
     const int G = d->n_heads / d->n_kv_heads;
-    w.qrp = ((d->M * G + 15) / 16) * 16;
+    w.qrp = ((32 * G + 15) / 16) * 16;
     w.nkb = (d->cache_rows + kKeyBlock - 1) / kKeyBlock;
     size_t off = 0;
     w.sync = off; off += 256;
@@ -1051,6 +1584,34 @@ WsLayout fwd_layout(const b200_forward_desc* d, PhasePlan (&plan)[5]) {
     w.partial = off; off += pb;
     w.total = off;
     return w;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+
+int make_kv_map(CUtensorMap* map, void* cache, int layers, int hkv, int cap, int hd) {
+    if (g_encode_tiled == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || fn == nullptr)
+            return check_launch() == B200_OK ? B200_ECUDA : B200_ECUDA;
+        g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)layers * 2 * hkv * cap};
+    const cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    const cuuint32_t box[2] = {64, 64};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, cache, dims, strides, box, estr,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = (int)r;
+        return B200_ECUDA;
+    }
+    return B200_OK;
 }
 
 template <int MT, int HD>
@@ -1108,7 +1669,7 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
     FwdParams p{};
     const WsLayout w = fwd_layout(d, p.plan);
     if (d->workspace_bytes < w.total) return B200_EWORKSPACE;
-    p.M = d->M; p.rows_out = d->rows_out; p.H = d->hidden; p.I = d->intermediate; p.Hq = d->n_heads;
+    p.M = d->M; p.mp = ((d->M + 7) / 8) * 8; p.rows_out = d->rows_out; p.H = d->hidden; p.I = d->intermediate; p.Hq = d->n_heads;
     p.Hkv = d->n_kv_heads; p.HD = d->head_dim; p.V = d->vocab; p.L = d->n_layers;
     p.NQKV = (d->n_heads + 2 * d->n_kv_heads) * d->head_dim;
     p.eps = d->rms_eps; p.rope_scale = d->rope_scaling; p.scale_log2 = d->attn_scale * kLog2e;
@@ -1136,6 +1697,12 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
     p.part_o = reinterpret_cast<float*>(ws + w.part_o);
     p.partial = reinterpret_cast<float*>(ws + w.partial);
     p.nkb = w.nkb; p.qrp = w.qrp;
+    {
+        const int rc = make_kv_map(&p.kvmap, d->kv_cache, d->n_layers, d->n_kv_heads, d->cache_rows, d->head_dim);
+        if (rc != B200_OK) return rc;
+    }
+    p.phase_mask = d->phase_mask ? (unsigned)d->phase_mask : 0xffu;
+    p.attn_fused_max = d->attn_split_blocks > 0 ? d->attn_split_blocks - 1 : (d->attn_split_blocks < 0 ? 0 : 8);
     p.timeline = static_cast<long long*>(d->timeline);
     p.timeline_pitch = d->timeline ? d->timeline_pitch : 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);

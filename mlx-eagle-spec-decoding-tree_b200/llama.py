@@ -179,12 +179,18 @@ class Model:
         self.logits = torch.zeros(MAX_ROWS, args.vocab_size, **f16)
         self._attn_ws = None
         self._attn_ws_rows = 0
-        self.hw = torch.zeros(MAX_ROWS, H, **f16)        # h * norm weight (fused forward)
+        # matmul inputs of the fused forward, chunk-major padded: [width/128][rows <= 32][160]
+        self.hw = torch.zeros(H // 128 * MAX_ROWS * 160 if H % 128 == 0 else 0, **f16)      # h * norm weight
+        self.xt_attn = torch.zeros(self.nq // 128 * MAX_ROWS * 160 if self.nq % 128 == 0 else 0, **f16)
+        self.xt_act = torch.zeros(args.intermediate_size // 128 * MAX_ROWS * 160
+                                  if args.intermediate_size % 128 == 0 else 0, **f16)
         self.fused = True                                # one persistent kernel per pass when possible
         self._fwd_ws = None
         self._fwd_ws_key = None
         self._layer_table = None
         self.timeline = None
+        self.attn_split_blocks = 0                       # 0 = library default; < 0 = always split the keys across CTAs
+        self.phase_mask = 0                              # profiling: run only some phase kinds (0 = all)
         self.fwd = FwdInputs(self.device)
 
     # ------------------------------------------------------------------ construction
@@ -312,8 +318,8 @@ class Model:
         d.inv_freq = p(self.inv_freqs)
         d.embed_wq, d.embed_scales, d.embed_biases = p(self.embed.weight), p(self.embed.scales), p(self.embed.biases)
         d.final_norm, d.lm_head_tiled, d.layer_table = p(self.norm), p(self.lm_head.tiled), p(self._layer_table)
-        d.h, d.hw, d.qkv, d.attn, d.act, d.logits = p(self.h), p(self.hw), p(self.qkv), p(self.attn), p(self.act), \
-            p(self.logits)
+        d.h, d.hw, d.qkv, d.attn, d.act, d.logits = p(self.h), p(self.hw), p(self.qkv), p(self.xt_attn), \
+            p(self.xt_act), p(self.logits)
         d.kv_cache = p(cache.data)
         key = (cache.rows,)
         if self._fwd_ws is None or self._fwd_ws_key != key:
@@ -325,17 +331,20 @@ class Model:
             self._fwd_ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
             self._fwd_ws_key = key
         d.workspace, d.workspace_bytes = p(self._fwd_ws), self._fwd_ws.numel()
+        d.phase_mask = self.phase_mask
+        d.attn_split_blocks = self.attn_split_blocks
         if self.timeline is not None:
             d.timeline, d.timeline_pitch = p(self.timeline), self.timeline.shape[1]
         return d
 
     def enable_timeline(self, on: bool = True):
         """Profiling hook of the persistent kernel: per SM, the device timer (ns) at arrival at and
-        departure from every device-wide barrier of the next pass (``self.timeline`` int64
-        ``[SMs, barriers + 1, 2]``; the last entry holds the end of the kernel)."""
+        departure from every device-wide barrier of the next pass, plus six stamps inside the matmul phase
+        that ends at the barrier: entry, rstd done, first stage landed, stages done, K-parts reduced, end
+        (``self.timeline`` int64 ``[SMs, barriers + 1, 8]``; the last entry holds the end of the kernel)."""
         if on:
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-            self.timeline = torch.zeros(sms, 6 * self.args.num_hidden_layers + 2, 2, dtype=torch.int64,
+            self.timeline = torch.zeros(sms, 6 * self.args.num_hidden_layers + 2, 8, dtype=torch.int64,
                                         device=self.device)
         else:
             self.timeline = None
