@@ -200,9 +200,9 @@ typedef struct b200_forward_desc {
     int hidden, intermediate, n_heads, n_kv_heads, head_dim, vocab, n_layers;
     int cache_rows, write_off, tail;
     float rms_eps, rope_scaling, attn_scale;
-    int attn_split_blocks;  /* 0 = default (9): from this many 64-key blocks of cache on, attention splits the   */
-                            /* keys across CTAs and merges in a second phase; below, one CTA per kv head walks */
-                            /* all blocks.  < 0 = always split                                                  */
+    int attn_split_blocks;  /* 0 = default (33): from this many 64-key blocks of cache on, attention splits the  */
+                            /* keys across CTAs and merges in a second phase; below, one CTA per (kv head,      */
+                            /* query tile) scores the key blocks on its warps side by side.  < 0 = always split  */
     const int* tokens;
     const int* pos;
     const unsigned long long* mask;

@@ -124,7 +124,7 @@ struct Geo {
     static constexpr int CPS_MAX = MT == 1 ? 8 : (MT == 2 ? 4 : 2);    // chunks of activations a stage can hold
     static constexpr int STAGE = kWArea + CPS_MAX * MP * kXRow;
     static constexpr int NST = 3;
-    static constexpr int SMEM = NST * STAGE + 128 + kScratch + kLtabBytes;
+    static constexpr int SMEM = NST * STAGE + 256 + kScratch + kLtabBytes;
 };
 
 struct QDesc {
@@ -145,6 +145,8 @@ struct Ctx {
     unsigned char* ring;
     uint64_t* full;
     uint64_t* empty;
+    uint64_t* afull;              // attention geometry: one barrier pair per key-block slot
+    uint64_t* aempty;
     unsigned char* scratch;
     const LayerPtrs* ltab;        // the layer pointer table, copied to shared memory at kernel start
     volatile int* abort_flag;
@@ -152,6 +154,9 @@ struct Ctx {
     int* is_last;
     float* s_rstd;
     uint32_t pos;       // ring stages produced (producer warp) / consumed (consumer warps)
+    uint32_t apos;      // attention key blocks produced / assigned so far
+    uint32_t ause;      // key blocks this consumer warp has taken from its slot so far
+    int ans;            // number of key-block slots (attention geometry)
     uint32_t epoch;     // grid barriers before the current phase
     int lane, warp;
 };
@@ -246,6 +251,29 @@ __device__ bool producer_grid_wait(const FwdParams& p, Ctx& c, uint32_t need_epo
     return ok != 0;
 }
 
+// The ring memory has two geometries: NST matmul stages, or `ans` slots of one 64-key K/V block each
+// (attention).  Producer side of a geometry switch: wait until the consumers have released
+// everything issued so far in the other geometry.
+template <int MT>
+__device__ __forceinline__ bool drain_stages(const FwdParams& p, Ctx& c) {
+    using G = Geo<MT>;
+    bool ok = true;
+    for (uint32_t s = c.pos > (uint32_t)G::NST ? c.pos - G::NST : 0; s < c.pos; s++)
+        ok = ok && fwd_wait(smem_u32(c.empty + s % G::NST), (s / G::NST) & 1u);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok && c.lane == 0) raise_error(p, c, 8);
+    return ok;
+}
+__device__ __forceinline__ bool drain_blocks(const FwdParams& p, Ctx& c) {
+    const uint32_t ns = (uint32_t)c.ans;
+    bool ok = true;
+    for (uint32_t n = c.apos > ns ? c.apos - ns : 0; n < c.apos; n++)
+        ok = ok && fwd_wait(smem_u32(c.aempty + n % ns), (n / ns) & 1u);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok && c.lane == 0) raise_error(p, c, 9);
+    return ok;
+}
+
 // ================================================================================ QMM phases
 // Item = (group of TPI = 8/kw 16-row tiles [tile pairs gate/up in dual mode], K range).  The eight
 // consumer warps are arranged as TPI tiles x kw K-parts: warp (j, i) owns tile j of the item and, in
@@ -270,7 +298,9 @@ __device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QD
     const int nblocks = (d.N + 63) / 64;
     const int nitems = d.pl.row_items * d.pl.splits;
     if ((int)blockIdx.x >= nitems) return;
+    if (c.apos > 0 && !drain_blocks(p, c)) return;        // key-block slots overlay the stages
 
+    const uint64_t wpolicy = make_evict_first_policy();   // weights are read once per pass: do not let them crowd L2
     bool ready = false;
     int npend = 0;
     uint32_t pend_slot[G::NST];
@@ -300,6 +330,15 @@ __device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QD
         const bool last_item = item + (int)gridDim.x >= nitems;
         const int t0 = row_item * TPI;                     // first 16-row tile of the item
         const int blk0 = min(t0 >> 2, nblocks - 1), blk1 = min((t0 >> 2) + 1, nblocks - 1);
+        // the epilogue's per-column vectors (bias, next norm weight) are first touched there: pull them into L2 now
+        if (lane < 2) {
+            const __half* vec = lane == 0 ? d.bias : d.wn;
+            const int col = t0 * 16 + 0;
+            if (vec != nullptr && col < d.N) {
+                asm volatile("prefetch.global.L2 [%0];\n" ::"l"(vec + col));
+                if (TPI * 16 > 64 && col + 64 < d.N) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(vec + col + 64));
+            }
+        }
         for (int st = 0; st < nst; st++, c.pos++) {
             const uint32_t slot = c.pos % G::NST, use = c.pos / G::NST;
             if (*c.abort_flag) return;
@@ -323,17 +362,17 @@ __device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QD
                 if (lane < nb * nmat) {
                     const int mtx = lane / nb, b = lane - mtx * nb;
                     const unsigned char* wbase = mtx ? d.w1 : d.w0;
-                    bulk_copy_g2s(smem_u32(stage + mtx * up_off + b * CPS * 4 * kRec),
-                                  wbase + ((size_t)(b ? blk1 : blk0) * nchunks_total + ch0) * 4 * kRec,
-                                  (uint32_t)(recs * 4 * kRec), fbar);
+                    bulk_copy_g2s_hint(smem_u32(stage + mtx * up_off + b * CPS * 4 * kRec),
+                                       wbase + ((size_t)(b ? blk1 : blk0) * nchunks_total + ch0) * 4 * kRec,
+                                       (uint32_t)(recs * 4 * kRec), fbar, wpolicy);
                 }
             } else {
                 for (int idx = lane; idx < recs * nmat; idx += 32) {     // part of a block: one copy per chunk
                     const int mtx = idx / recs, cc = idx - mtx * recs;
                     const unsigned char* wbase = mtx ? d.w1 : d.w0;
-                    bulk_copy_g2s(smem_u32(stage + mtx * up_off + cc * chunk_bytes),
-                                  wbase + (((size_t)blk0 * nchunks_total + ch0 + cc) * 4 + (t0 & 3)) * kRec,
-                                  (uint32_t)chunk_bytes, fbar);
+                    bulk_copy_g2s_hint(smem_u32(stage + mtx * up_off + cc * chunk_bytes),
+                                       wbase + (((size_t)blk0 * nchunks_total + ch0 + cc) * 4 + (t0 & 3)) * kRec,
+                                       (uint32_t)chunk_bytes, fbar, wpolicy);
                 }
             }
             const int k0 = (c_begin + st * CPS) * kChunkK;
@@ -763,6 +802,7 @@ __device__ __forceinline__ void attn_produce(const FwdParams& p, Ctx& c, const A
     static_assert(2 * kKeyBlock * KS * 2 <= kWArea, "K/V block must fit the weight area of a stage");
     const int lane = c.lane;
     const int nitems = p.Hkv * a.nact;
+    if ((int)blockIdx.x < nitems && c.apos > 0 && !drain_blocks(p, c)) return;
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, c.pos++) {
         const int hk = item / a.nact, kb = item - hk * a.nact;
         const int key0 = kb * kKeyBlock;
@@ -973,15 +1013,15 @@ __device__ __forceinline__ void attn_consume(const FwdParams& p, Ctx& c, const A
     }
 }
 
-// ---- single-phase attention for short contexts -----------------------------------------------------
-// When the cache is at most attn_fused_max key blocks long, splitting the keys across CTAs costs more
-// in barriers than it saves: one item is then (kv head, group of up to four 16-row query tiles, one per
-// warp and scheduler), the producer streams all key blocks of the head through the ring, every busy
-// warp keeps the running softmax state (max, sum, fp32 output) of its tile in registers and the
-// normalised output goes straight to `attn`; the merge phase and its barrier disappear.
-// K/V blocks arrive as TMA tiles (cp.async.bulk.tensor, 64 rows x 64 halves per box, 128-byte swizzle):
-// two to four copies per block, and the swizzle makes the fragment loads conflict-free without padding.
-constexpr int kAttnTG = 4;                    // query tiles (warps) per item
+// ---- block-parallel attention (the default) ---------------------------------------------------------
+// One item is (kv head, 16-row query tile).  The ring memory is re-used as NS slots of one 64-key K/V
+// block each (TMA tiles, 64 x 64 boxes, 128-byte swizzle: conflict-free fragment loads without
+// padding); block n of the phase goes to slot n % NS and is scored by warp n % NS, so the key blocks
+// of a tile are processed side by side, each warp keeping the running softmax state of its blocks
+// in registers.  The warps then leave (max, sum, fp32 output) in their slots and all threads merge
+// them in key-block order, normalise and store.  No partial sums in global memory, no merge phase.
+// The slots overlay the matmul stages: the producer drains one geometry before it fills the other.
+constexpr int kASlotsMax = 8;
 constexpr int kBox = 64 * 128;                // bytes of one 64-row x 128-byte TMA box
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -1005,34 +1045,44 @@ __device__ __forceinline__ uint32_t swz(int r, int v) {
 }
 
 template <int MT, int HD>
-__device__ __forceinline__ void attn_fused_produce(const FwdParams& p, Ctx& c, const ADesc& a, int layer) {
-    using G = Geo<MT>;
-    constexpr int NBX = HD / 64;                  // boxes per K (and per V) block
+struct AGeo {
+    static constexpr int NBX = HD / 64;                      // boxes per K (and per V) block
+    static constexpr int SLOT = 2 * NBX * kBox;              // 16 or 32 KB
+    static constexpr int FIT = Geo<MT>::NST * Geo<MT>::STAGE / SLOT;
+    static constexpr int NS = FIT < kASlotsMax ? FIT : kASlotsMax;
+    static constexpr int OP = HD + 8;                        // pitch (floats) of a warp's partial output tile
+    static_assert(16 * OP * 4 + 16 * 8 <= SLOT, "a warp's partial state must fit its slot");
+};
+
+template <int MT, int HD>
+__device__ __forceinline__ void attn_bp_produce(const FwdParams& p, Ctx& c, const ADesc& a, int layer) {
+    using A = AGeo<MT, HD>;
     const int lane = c.lane;
     const int Gq = p.Hq / p.Hkv;
     const int ntiles = (p.M * Gq + 15) / 16;
-    const int ngroups = (ntiles + kAttnTG - 1) / kAttnTG;
-    const int nitems = p.Hkv * ngroups;
+    const int nitems = p.Hkv * ntiles;
+    if ((int)blockIdx.x >= nitems) return;
+    if (*c.abort_flag || !drain_stages<MT>(p, c)) return;
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-        const int hk = item / ngroups;
+        const int hk = item / ntiles;
         const int krow0 = ((layer * 2 + 0) * p.Hkv + hk) * p.cap;       // row of the cache viewed as [rows][HD]
         const int vrow0 = ((layer * 2 + 1) * p.Hkv + hk) * p.cap;
-        for (int kb = 0; kb < a.nact; kb++, c.pos++) {
-            const uint32_t slot = c.pos % G::NST, use = c.pos / G::NST;
+        for (int kb = 0; kb < a.nact; kb++, c.apos++) {
+            const uint32_t slot = c.apos % A::NS, use = c.apos / A::NS;
             if (*c.abort_flag) return;
-            if (use > 0 && !__all_sync(0xffffffffu, fwd_wait(smem_u32(c.empty + slot), (use - 1) & 1u))) {
+            if (use > 0 && !__all_sync(0xffffffffu, fwd_wait(smem_u32(c.aempty + slot), (use - 1) & 1u))) {
                 if (lane == 0) raise_error(p, c, 6);
                 return;
             }
-            const uint32_t fbar = smem_u32(c.full + slot);
-            const uint32_t sk = smem_u32(c.ring + slot * G::STAGE);
+            const uint32_t fbar = smem_u32(c.afull + slot);
+            const uint32_t sk = smem_u32(c.ring + slot * A::SLOT);
             if (lane == 0) {
                 fence_proxy_async();
-                mbar_expect_tx(fbar, 2 * NBX * kBox);
+                mbar_expect_tx(fbar, A::SLOT);
             }
             __syncwarp();
-            if (lane < 2 * NBX) {                  // K boxes, then V boxes
-                const int isv = lane / NBX, bx = lane - isv * NBX;
+            if (lane < 2 * A::NBX) {                  // K boxes, then V boxes
+                const int isv = lane / A::NBX, bx = lane - isv * A::NBX;
                 tma_load_2d(sk + lane * kBox, &p.kvmap, bx * 64, (isv ? vrow0 : krow0) + kb * kKeyBlock, fbar);
             }
         }
@@ -1040,40 +1090,34 @@ __device__ __forceinline__ void attn_fused_produce(const FwdParams& p, Ctx& c, c
 }
 
 template <int MT, int HD>
-__device__ __forceinline__ void attn_fused_consume(const FwdParams& p, Ctx& c, const ADesc& a) {
-    using G = Geo<MT>;
+__device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, const ADesc& a) {
+    using A = AGeo<MT, HD>;
+    constexpr int NS = A::NS, NBX = A::NBX, OP = A::OP;
     constexpr int KS = HD + 8;                    // padded pitch of the query tile
     constexpr int VPR = HD / 8;
-    constexpr int NBX = HD / 64;
-    static_assert(kWN * 16 * KS * 2 <= kScratch, "query tiles of all warps must fit the scratch area");
-    static_assert(2 * NBX * kBox <= kWArea, "a K/V block must fit the weight area of a stage");
+    static_assert(16 * KS * 2 <= kScratch, "the query tile must fit the scratch area");
     const int lane = c.lane, warp = c.warp;
     const int g = lane >> 2, t = lane & 3;
     const int Gq = p.Hq / p.Hkv;
     const int QR = p.M * Gq;
     const int ntiles = (QR + 15) / 16;
-    const int ngroups = (ntiles + kAttnTG - 1) / kAttnTG;
-    const int nitems = p.Hkv * ngroups;
+    const int nitems = p.Hkv * ntiles;
     const int prefix = a.prefix;
     const int new0 = prefix + p.write_off;
+    __half* sq = reinterpret_cast<__half*>(c.scratch);
+    __half* nkv = sq + 16 * KS;                    // [2][M][HD]: rotated k rows, then v rows, of this pass
+    static_assert(16 * KS * 2 + 2 * 32 * HD * 2 <= kScratch, "query tile and new K/V rows must fit the scratch area");
+    unsigned char* myslot = c.ring + (warp < NS ? warp : 0) * A::SLOT;
 
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-        const int hk = item / ngroups, tg = item - hk * ngroups;
-        const int rt = tg * kAttnTG + warp;
-        const bool has_tile = warp < kAttnTG && rt < ntiles;
-        const int r0 = rt * 16 + g, r1 = r0 + 8;
-        const bool v0 = has_tile && r0 < QR, v1 = has_tile && r1 < QR;
-        const int m0 = v0 ? r0 / Gq : 0, m1 = v1 ? r1 / Gq : 0;
-        const int h0 = hk * Gq + (v0 ? r0 - m0 * Gq : 0), h1 = hk * Gq + (v1 ? r1 - m1 * Gq : 0);
-        const unsigned long long mk0 = v0 ? p.mask[m0] : 0ull, mk1 = v1 ? p.mask[m1] : 0ull;
-
+        const int hk = item / ntiles, rt = item - hk * ntiles;
+        const uint32_t n0 = c.apos;                        // first block of this item in the phase's block sequence
+        c.apos += a.nact;
         stamp(p, c, 2);
-        // rotated queries of this warp's tile -> its private padded tile in shared memory (A fragments are
-        // re-read per key block: that keeps 32 registers free for the output accumulators)
-        __half* sq = reinterpret_cast<__half*>(c.scratch) + warp * 16 * KS;
-        if (has_tile) {
+        // ---- rotated queries of the tile -> padded tile in shared memory, by all threads
+        {
             constexpr int HV = VPR / 2;                       // vector pairs (i, i + HD/2) per row
-            for (int pi = lane; pi < 16 * HV; pi += 32) {
+            for (int pi = threadIdx.x; pi < 16 * HV; pi += kNCons) {
                 const int row = pi / HV, cv = pi - row * HV;
                 const int r = rt * 16 + row;
                 uint4 o1 = make_uint4(0, 0, 0, 0), o2 = make_uint4(0, 0, 0, 0);
@@ -1103,75 +1147,92 @@ __device__ __forceinline__ void attn_fused_consume(const FwdParams& p, Ctx& c, c
                 *reinterpret_cast<uint4*>(sq + row * KS + HD / 2 + cv * 8) = o2;
             }
         }
-        __syncwarp();
+        // ---- this pass's own K (rotated) and V rows of the head -> shared memory, by all threads; the first
+        //      tile's item of each kv head also appends them to the cache
+        {
+            const bool writer = (rt == 0);
+            for (int idx = threadIdx.x; idx < p.M * VPR; idx += kNCons) {
+                const int m = idx / VPR, cv = idx - m * VPR;
+                const int key = new0 + m;
+                const __half* src = p.qkv + (size_t)m * p.NQKV;
+                const uint4 vv = __ldcg(reinterpret_cast<const uint4*>(src + (size_t)(p.Hq + p.Hkv) * HD + (size_t)hk * HD + cv * 8));
+                *reinterpret_cast<uint4*>(nkv + (p.M + m) * HD + cv * 8) = vv;
+                if (writer && key < p.cap) *reinterpret_cast<uint4*>(a.vc + ((size_t)hk * p.cap + key) * HD + cv * 8) = vv;
+                if (cv < VPR / 2) {
+                    const __half* ksrc = src + (size_t)p.Hq * HD + (size_t)hk * HD;
+                    const uint4 x1v = __ldcg(reinterpret_cast<const uint4*>(ksrc + cv * 8));
+                    const uint4 x2v = __ldcg(reinterpret_cast<const uint4*>(ksrc + HD / 2 + cv * 8));
+                    const float4* csp = reinterpret_cast<const float4*>(p.cs + m * kCsPitch + cv * 8);
+                    float4 cs4[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) cs4[e] = __ldcg(csp + e);
+                    const __half* x1 = reinterpret_cast<const __half*>(&x1v);
+                    const __half* x2 = reinterpret_cast<const __half*>(&x2v);
+                    __align__(16) __half k1[8], k2[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const float co = (e & 1) ? cs4[e >> 1].z : cs4[e >> 1].x;
+                        const float si = (e & 1) ? cs4[e >> 1].w : cs4[e >> 1].y;
+                        const float a1 = __half2float(x1[e]), a2 = __half2float(x2[e]);
+                        k1[e] = __float2half_rn(a1 * co - a2 * si);
+                        k2[e] = __float2half_rn(a1 * si + a2 * co);
+                    }
+                    *reinterpret_cast<uint4*>(nkv + m * HD + cv * 8) = *reinterpret_cast<const uint4*>(k1);
+                    *reinterpret_cast<uint4*>(nkv + m * HD + HD / 2 + cv * 8) = *reinterpret_cast<const uint4*>(k2);
+                    if (writer && key < p.cap) {
+                        __half* kd = a.kc + ((size_t)hk * p.cap + key) * HD;
+                        *reinterpret_cast<uint4*>(kd + cv * 8) = *reinterpret_cast<const uint4*>(k1);
+                        *reinterpret_cast<uint4*>(kd + HD / 2 + cv * 8) = *reinterpret_cast<const uint4*>(k2);
+                    }
+                }
+            }
+        }
+        consumer_sync(kNCons);
         stamp(p, c, 3);
         const uint32_t sq_frag = smem_u32(sq + ((lane & 7) + ((lane >> 3) & 1) * 8) * KS + (lane >> 4) * 8);
+
+        const int r0 = rt * 16 + g, r1 = r0 + 8;
+        const bool v0 = r0 < QR, v1 = r1 < QR;
+        const int m0 = v0 ? r0 / Gq : 0, m1 = v1 ? r1 / Gq : 0;
+        const unsigned long long mk0 = v0 ? p.mask[m0] : 0ull, mk1 = v1 ? p.mask[m1] : 0ull;
 
         float mrun0 = -INFINITY, mrun1 = -INFINITY, l0 = 0.f, l1 = 0.f;
         float o[HD / 8][4];
 #pragma unroll
         for (int nd = 0; nd < HD / 8; nd++) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.f;
 
-        for (int kb = 0; kb < a.nact; kb++, c.pos++) {
-            const int key0 = kb * kKeyBlock;
-            const uint32_t slot = c.pos % G::NST;
-            bool ok = !*c.abort_flag;
-            if (ok && !fwd_wait(smem_u32(c.full + slot), (c.pos / G::NST) & 1u)) {
-                ok = false;
-                if (lane == 0) raise_error(p, c, 7);
-            }
-            ok = __all_sync(0xffffffffu, ok);
-            if (kb == 0) stamp(p, c, 4);
-            unsigned char* skp = c.ring + slot * G::STAGE;
-            const uint32_t sk = smem_u32(skp), sv = sk + NBX * kBox;
-            // the block that holds this pass's own rows: take them from the qkv buffer (k rotated) and append them to the cache
-            const bool patch = key0 + kKeyBlock > new0 && key0 < new0 + p.M;
-            if (patch) {
-                if (ok) {
-                    for (int idx = threadIdx.x; idx < p.M * VPR; idx += kNCons) {
-                        const int m = idx / VPR, cv = idx - m * VPR;
-                        const int key = new0 + m;
-                        const int r = key - key0;
-                        if (r < 0 || r >= kKeyBlock) continue;
-                        const bool writer = (tg == 0);             // one item per kv head appends to the cache
-                        const __half* src = p.qkv + (size_t)m * p.NQKV;
-                        const uint4 vv = __ldcg(reinterpret_cast<const uint4*>(src + (size_t)(p.Hq + p.Hkv) * HD + (size_t)hk * HD + cv * 8));
-                        *reinterpret_cast<uint4*>(skp + NBX * kBox + swz(r, cv)) = vv;
-                        if (writer && key < p.cap) *reinterpret_cast<uint4*>(a.vc + ((size_t)hk * p.cap + key) * HD + cv * 8) = vv;
-                        if (cv < VPR / 2) {
-                            const __half* ksrc = src + (size_t)p.Hq * HD + (size_t)hk * HD;
-                            const uint4 x1v = __ldcg(reinterpret_cast<const uint4*>(ksrc + cv * 8));
-                            const uint4 x2v = __ldcg(reinterpret_cast<const uint4*>(ksrc + HD / 2 + cv * 8));
-                            const float4* csp = reinterpret_cast<const float4*>(p.cs + m * kCsPitch + cv * 8);
-                            float4 cs4[4];
-#pragma unroll
-                            for (int e = 0; e < 4; e++) cs4[e] = __ldcg(csp + e);
-                            const __half* x1 = reinterpret_cast<const __half*>(&x1v);
-                            const __half* x2 = reinterpret_cast<const __half*>(&x2v);
-                            __align__(16) __half k1[8], k2[8];
-#pragma unroll
-                            for (int e = 0; e < 8; e++) {
-                                const float co = (e & 1) ? cs4[e >> 1].z : cs4[e >> 1].x;
-                                const float si = (e & 1) ? cs4[e >> 1].w : cs4[e >> 1].y;
-                                const float a1 = __half2float(x1[e]), a2 = __half2float(x2[e]);
-                                k1[e] = __float2half_rn(a1 * co - a2 * si);
-                                k2[e] = __float2half_rn(a1 * si + a2 * co);
-                            }
-                            *reinterpret_cast<uint4*>(skp + swz(r, cv)) = *reinterpret_cast<const uint4*>(k1);
-                            *reinterpret_cast<uint4*>(skp + swz(r, cv + VPR / 2)) = *reinterpret_cast<const uint4*>(k2);
-                            if (writer && key < p.cap) {
-                                __half* kd = a.kc + ((size_t)hk * p.cap + key) * HD;
-                                *reinterpret_cast<uint4*>(kd + cv * 8) = *reinterpret_cast<const uint4*>(k1);
-                                *reinterpret_cast<uint4*>(kd + HD / 2 + cv * 8) = *reinterpret_cast<const uint4*>(k2);
-                            }
-                        }
-                    }
-                    fence_proxy_async();       // the slot is refilled through the async proxy later
+        // ---- this warp's key blocks: those whose sequence number is congruent to the warp index
+        bool ok = true;
+        int nmine = 0;
+        if (warp < NS) {
+            const int kb_first = (int)((warp + NS - n0 % NS) % NS);
+            for (int kb = kb_first; kb < a.nact; kb += NS, c.ause++, nmine++) {
+                const int key0 = kb * kKeyBlock;
+                if (nmine > 0) {                           // the previous block of this warp is done: give its slot back
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(c.aempty + warp));
                 }
-                consumer_sync(kNCons);
-            }
-
-            if (ok && has_tile) {
+                ok = ok && !*c.abort_flag;
+                if (ok && !fwd_wait(smem_u32(c.afull + warp), c.ause & 1u)) {
+                    ok = false;
+                    if (lane == 0) raise_error(p, c, 7);
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (kb == kb_first) stamp(p, c, 4);
+                if (!ok) continue;
+                const uint32_t sk = smem_u32(myslot), sv = sk + NBX * kBox;
+                // this pass's own rows inside the block come from the rows prepared above
+                if (key0 + kKeyBlock > new0 && key0 < new0 + p.M) {
+                    for (int idx = lane; idx < p.M * VPR; idx += 32) {
+                        const int m = idx / VPR, cv = idx - m * VPR;
+                        const int r = new0 + m - key0;
+                        if (r < 0 || r >= kKeyBlock) continue;
+                        *reinterpret_cast<uint4*>(myslot + swz(r, cv)) = *reinterpret_cast<const uint4*>(nkv + m * HD + cv * 8);
+                        *reinterpret_cast<uint4*>(myslot + NBX * kBox + swz(r, cv)) =
+                            *reinterpret_cast<const uint4*>(nkv + (p.M + m) * HD + cv * 8);
+                    }
+                    __syncwarp();
+                }
                 const bool all_visible = key0 + kKeyBlock <= prefix;      // committed rows: no mask needed
 #pragma unroll
                 for (int half = 0; half < 2; half++) {         // 32 keys at a time keeps the scores in 16 registers
@@ -1265,29 +1326,70 @@ __device__ __forceinline__ void attn_fused_consume(const FwdParams& p, Ctx& c, c
                     }
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(c.empty + slot));
+            // ---- leave the partial state in this warp's slot (its K/V block is no longer needed)
+            if (nmine > 0) {
+                l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+                l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+                l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+                l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+                __syncwarp();
+                float* po = reinterpret_cast<float*>(myslot);
+                float* pml = po + 16 * OP;
+#pragma unroll
+                for (int nd = 0; nd < HD / 8; nd++) {
+                    *reinterpret_cast<float2*>(po + g * OP + nd * 8 + 2 * t) = make_float2(o[nd][0], o[nd][1]);
+                    *reinterpret_cast<float2*>(po + (g + 8) * OP + nd * 8 + 2 * t) = make_float2(o[nd][2], o[nd][3]);
+                }
+                if (t == 0) {
+                    *reinterpret_cast<float2*>(pml + g * 2) = make_float2(mrun0, l0);
+                    *reinterpret_cast<float2*>(pml + (g + 8) * 2) = make_float2(mrun1, l1);
+                }
+            }
         }
-
+        consumer_sync(kNCons);
         stamp(p, c, 5);
-        // normalise and store: lane (g,t) holds rows r0 / r1, columns nd*8 + 2t, +1
-        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-        const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
-        if (v0) {
-            __half* orow = p.attn + xt_index(m0, h0 * HD, p.mp) + 2 * t;      // a head's columns stay inside one 128-chunk
+
+        // ---- merge in key-block order, normalise, store: thread = (row, HD/16 consecutive columns)
+        {
+            constexpr int CPT = HD / 16;
+            const int row = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * CPT;
+            const int r = rt * 16 + row;
+            const int nw = a.nact < NS ? a.nact : NS;
+            if (r < QR) {
+                float mstar = -INFINITY;
+                for (int i = 0; i < nw; i++) {
+                    const int w = (int)((n0 + i) % NS);
+                    mstar = fmaxf(mstar, *reinterpret_cast<const float*>(c.ring + w * A::SLOT + (16 * OP + row * 2) * 4));
+                }
+                float acc[CPT];
 #pragma unroll
-            for (int nd = 0; nd < HD / 8; nd++)
-                *reinterpret_cast<__half2*>(orow + nd * 8) = __floats2half2_rn(o[nd][0] * inv0, o[nd][1] * inv0);
-        }
-        if (v1) {
-            __half* orow = p.attn + xt_index(m1, h1 * HD, p.mp) + 2 * t;
+                for (int e = 0; e < CPT; e++) acc[e] = 0.f;
+                float denom = 0.f;
+                for (int i = 0; i < nw; i++) {
+                    const int w = (int)((n0 + i) % NS);
+                    const float* base = reinterpret_cast<const float*>(c.ring + w * A::SLOT);
+                    const float2 ml = *reinterpret_cast<const float2*>(base + 16 * OP + row * 2);
+                    const float wgt = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - mstar);
+                    denom += ml.y * wgt;
 #pragma unroll
-            for (int nd = 0; nd < HD / 8; nd++)
-                *reinterpret_cast<__half2*>(orow + nd * 8) = __floats2half2_rn(o[nd][2] * inv1, o[nd][3] * inv1);
+                    for (int e = 0; e < CPT; e += 4) {
+                        const float4 v = *reinterpret_cast<const float4*>(base + row * OP + c0 + e);
+                        acc[e] += wgt * v.x; acc[e + 1] += wgt * v.y; acc[e + 2] += wgt * v.z; acc[e + 3] += wgt * v.w;
+                    }
+                }
+                const float inv = denom > 0.f ? 1.f / denom : 0.f;
+                const int m = r / Gq, hh = hk * Gq + (r - m * Gq);
+                __align__(16) __half out[CPT];
+#pragma unroll
+                for (int e = 0; e < CPT; e++) out[e] = __float2half_rn(acc[e] * inv);
+                __half* dst = p.attn + xt_index(m, hh * HD + c0, p.mp);       // a head's columns stay inside one 128-chunk
+                if (CPT == 8) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(out);
+                else *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(out);
+            }
         }
+        fence_proxy_async();           // the slots are refilled through the async proxy
+        consumer_sync(kNCons);         // merge done: the last slots can go back, the query tile can be rewritten
+        if (warp < NS && nmine > 0 && lane == 0) mbar_arrive(smem_u32(c.aempty + warp));
     }
 }
 
@@ -1348,7 +1450,12 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
     c.ring = smem;
     c.full = reinterpret_cast<uint64_t*>(smem + G::NST * G::STAGE);
     c.empty = c.full + G::NST;
-    c.scratch = smem + G::NST * G::STAGE + 128;
+    c.afull = c.empty + G::NST;
+    c.aempty = c.afull + kASlotsMax;
+    c.apos = 0;
+    c.ause = 0;
+    c.ans = AGeo<MT, HD>::NS;
+    c.scratch = smem + G::NST * G::STAGE + 256;
     {
         // every phase needs its layer's pointers the moment a barrier opens: keep the table on chip
         uint4* dst = reinterpret_cast<uint4*>(c.scratch + kScratch);
@@ -1372,6 +1479,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
         for (int s = 0; s < G::NST; s++) {
             mbar_init(smem_u32(c.full + s), 1);
             mbar_init(smem_u32(c.empty + s), kWN);
+        }
+#pragma unroll
+        for (int s = 0; s < kASlotsMax; s++) {
+            mbar_init(smem_u32(c.afull + s), 1);
+            mbar_init(smem_u32(c.aempty + s), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -1406,8 +1518,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             ad.kc = p.kv + (size_t)l * p.kv_layer_stride;
             ad.vc = ad.kc + p.kv_half_stride;
             if (attn_fused) {
-                if (producer) attn_fused_produce<MT, HD>(p, c, ad, l);
-                else attn_fused_consume<MT, HD>(p, c, ad);
+                if (producer) attn_bp_produce<MT, HD>(p, c, ad, l);
+                else attn_bp_consume<MT, HD>(p, c, ad);
             } else {
                 if (producer) attn_produce<MT, HD>(p, c, ad);
                 else attn_consume<MT, HD>(p, c, ad);
@@ -1472,7 +1584,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
 // Chooses, for one matmul phase, how the eight consumer warps split an item (kw K-parts x 8/kw
 // tiles) and whether K is also split across CTAs, with a small cost model in microseconds: a warp
 // spends about half a microsecond per record while all warps of an SM stream, a shared-memory
-// K reduction costs a few tenths, a split through global memory about three (partial sums out,
+// K reduction costs a few tenths, a split through global memory four to five (partial sums out,
 // ticket, partial sums back in).
 PhasePlan make_plan(int N, int K, int grid, int mt, bool dual) {
     const int nchunks = K / kChunkK;
@@ -1496,11 +1608,12 @@ PhasePlan make_plan(int N, int K, int grid, int mt, bool dual) {
             const long long items = (long long)row_items * splits;
             const long long rounds = (items + grid - 1) / grid;
             const int rec_per_warp = ((cps + kw - 1) / kw) * (dual ? 2 : 1);
-            // bulk copies cost ~0.06 us each to issue: whole blocks come as one run per stage, parts of a block chunk by chunk
+            // bulk copies cost ~0.03 us each to issue (lanes issue in parallel): whole blocks come as one run per
+            // stage, parts of a block chunk by chunk; measured: a split through global memory adds 4-5 us
             const int stages = (cps + kw * U - 1) / (kw * U);
             const int ops_per_stage = 1 + (dual ? 2 : 1) * (tpi >= 4 ? tpi / 4 : kw * U);
-            const double cost = rounds * (0.5 * rec_per_warp + 0.06 * stages * ops_per_stage + (kw > 1 ? 0.3 : 0.0) +
-                                          (splits > 1 ? 3.0 : 0.0) + 1.0);
+            const double cost = rounds * (0.5 * rec_per_warp + 0.03 * stages * ops_per_stage + (kw > 1 ? 0.3 : 0.0) +
+                                          (splits > 1 ? 4.5 : 0.0) + 1.0);
             if (cost < best_cost - 1e-9) {
                 best_cost = cost;
                 best.row_items = row_items; best.splits = splits; best.chunks_per_split = cps; best.kw = kw; best.U = U;
@@ -1702,7 +1815,7 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
         if (rc != B200_OK) return rc;
     }
     p.phase_mask = d->phase_mask ? (unsigned)d->phase_mask : 0xffu;
-    p.attn_fused_max = d->attn_split_blocks > 0 ? d->attn_split_blocks - 1 : (d->attn_split_blocks < 0 ? 0 : 8);
+    p.attn_fused_max = d->attn_split_blocks > 0 ? d->attn_split_blocks - 1 : (d->attn_split_blocks < 0 ? 0 : 32);
     p.timeline = static_cast<long long*>(d->timeline);
     p.timeline_pitch = d->timeline ? d->timeline_pitch : 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
