@@ -144,6 +144,59 @@ def qmm_roofline(be, torch, model, rows, reps):
     return alg, launches, sec
 
 
+def forward_algorithmic_bytes(model, rows, kv_rows):
+    """Bytes one forward pass of `rows` tokens has to move: every linear layer's packed weights, scales and
+    biases plus its activations in and out (the per-matmul formula), and the K/V rows attention reads."""
+    a = model.args
+    H, I = a.hidden_size, a.intermediate_size
+    nqkv = model.nq + 2 * model.nkv
+    resid = 2 * rows * H
+    per_layer = (_qmm_bytes(rows, nqkv, H, a.attention_bias)
+                 + _qmm_bytes(rows, H, model.nq) + resid
+                 + 2 * _qmm_bytes(rows, I, H) - 2 * rows * H - 2 * rows * I
+                 + _qmm_bytes(rows, H, I) + resid
+                 + 2 * kv_rows * a.num_key_value_heads * a.head_dim * 2)
+    return len(model.layers) * per_layer + _qmm_bytes(rows, a.vocab_size, H)
+
+
+def forward_roofline(torch, model, cache, rows, prefix, reps):
+    """Time the persistent forward kernel alone (one launch = one pass of `rows` tokens over a `prefix`-row
+    cache) as a CUDA graph, with CUDA events on the launching stream."""
+    f = model.fwd
+    g = torch.Generator().manual_seed(99)
+    f.tokens[:rows].copy_(torch.randint(0, model.args.vocab_size, (rows,), generator=g, dtype=torch.int32))
+    f.pos[:rows].copy_(prefix + torch.arange(rows, dtype=torch.int32))
+    f.mask[:rows].copy_(torch.tensor([(2 << i) - 1 for i in range(rows)], dtype=torch.int64))
+    f.prefix.fill_(prefix)
+
+    def run():
+        model.forward_device(rows, cache, 0, rows)
+
+    run()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    model.check_fused_error()
+    return forward_algorithmic_bytes(model, rows, prefix + rows), e0.elapsed_time(e1) / 1e3 / reps
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one forward_kernel<2,128> launch over its algorithmic bytes,
+# from one ncu capture of a 4-layer model of the same layer shape (842.4 MB against 846.8 MB; the 28-layer
+# launch holds 4.3 GB, too much to capture).  Traffic grows with the layers streamed, so the ratio carries
+# over to the launch timed here.
+FORWARD_KERNEL_DRAM_OVER_ALGORITHMIC = 0.995
+
+
 def cpu_sample(steps, warm=0, seed=0):
     """The CPU restatement on a bounded sample: `warm` untimed + `steps` timed speculative steps at the
     full shapes, with the 256 committed KV rows pre-filled (prompt ingestion is outside the metric's
@@ -202,6 +255,18 @@ def cpu_sample(steps, warm=0, seed=0):
     return n, sec, qmm_c.num_threads()
 
 
+def reduce_counters(dist, torch, world, produced, sec, e2e_tokens, e2e_sec, dev):
+    """Whole-job numbers from per-rank ones: tokens add up over the independent request streams, the time
+    is the slowest rank's.  The only collective of the multi-GPU path."""
+    if world <= 1:
+        return float(produced), float(sec), float(e2e_tokens), float(e2e_sec)
+    tot = torch.tensor([float(produced), sec, float(e2e_tokens), e2e_sec], dtype=torch.float64, device=dev)
+    sums, maxs = tot.clone(), tot.clone()
+    dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    dist.all_reduce(maxs, op=dist.ReduceOp.MAX)
+    return float(sums[0]), float(maxs[1]), float(sums[2]), float(maxs[3])
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
@@ -229,7 +294,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--roofline-only", action="store_true",
-                    help="only the quantised-matmul sweep of the target model (small profiling case)")
+                    help="only the target model's forward kernel at 16 rows (small profiling case with --layers)")
+    ap.add_argument("--layers", type=int, default=0, help="with --roofline-only: number of decoder layers (0 = all 28)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -252,11 +318,23 @@ def main():
     K = args.steps
 
     if args.roofline_only:
-        base = be.Model.random_init(be.shape_preset("qwen2-7b"), seed=2000, device=dev).relayout()
+        import dataclasses
+        shape = be.shape_preset("qwen2-7b")
+        if args.layers:
+            shape = dataclasses.replace(shape, num_hidden_layers=args.layers)
+        base = be.Model.random_init(shape, seed=2000, device=dev).relayout()
         peak, peak_src = _peaks()
-        alg, launches, qsec = qmm_roofline(be, torch, base, VERIFY + 1, reps=max(1, min(args.steps, 20)))
-        print(json.dumps({"roofline_only": True, "achieved_gbs": alg / qsec / 1e9, "peak": peak,
-                          "frac": alg / qsec / 1e9 / peak, "launches": launches, "us_per_launch": 1e6 * qsec / launches}))
+        reps = max(1, min(args.steps, 20))
+        if base.can_fuse():
+            cache = base.make_cache(512)
+            base(torch.randint(0, shape.vocab_size, (1, PROMPT)), cache=cache, logits_last_only=True)
+            alg, qsec = forward_roofline(torch, base, cache, VERIFY + 1, PROMPT, reps)
+            launches = 1
+        else:
+            alg, launches, qsec = qmm_roofline(be, torch, base, VERIFY + 1, reps=reps)
+        print(json.dumps({"roofline_only": True, "layers": shape.num_hidden_layers, "achieved_gbs": alg / qsec / 1e9,
+                          "peak": peak, "frac": alg / qsec / 1e9 / peak, "launches": launches,
+                          "algorithmic_bytes": alg, "us_per_launch": 1e6 * qsec / launches}))
         return
     draft = be.Model.random_init(be.shape_preset("qwen2-0.5b"), seed=1000 + rank, device=dev).relayout()
     base = be.Model.random_init(be.shape_preset("qwen2-7b"), seed=2000 + rank, device=dev).relayout()
@@ -303,20 +381,22 @@ def main():
     e2e_sec = time.perf_counter() - t0
     e2e_tokens, e2e_steps = res["produced"], max(res["steps_launched"], 1)
 
-    tot = torch.tensor([float(produced), sec, float(e2e_tokens), e2e_sec], dtype=torch.float64, device=dev)
-    if world > 1:
-        sums, maxs = tot.clone(), tot.clone()
-        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
-        dist.all_reduce(maxs, op=dist.ReduceOp.MAX)
-        produced_all, sec_all = float(sums[0]), float(maxs[1])
-        e2e_tokens_all, e2e_sec_all = float(sums[2]), float(maxs[3])
-    else:
-        produced_all, sec_all, e2e_tokens_all, e2e_sec_all = float(produced), sec, float(e2e_tokens), e2e_sec
+    produced_all, sec_all, e2e_tokens_all, e2e_sec_all = reduce_counters(dist, torch, world, produced, sec, e2e_tokens,
+                                                                         e2e_sec, dev)
 
     line = None
     if rank == 0:
         peak, peak_src = _peaks()
-        alg, qmm_launches, qsec = qmm_roofline(be, torch, base, VERIFY + 1, reps=20)
+        if base.can_fuse():
+            prefix_now = int(dec.ctl[0])
+            alg, qsec = forward_roofline(torch, base, dec.base_cache, VERIFY + 1, prefix_now, reps=20)
+            qmm_launches, traffic = 1, FORWARD_KERNEL_DRAM_OVER_ALGORITHMIC * alg
+            kernel_name = (f"forward_kernel<2,128>: one target pass of {VERIFY + 1} rows over a {prefix_now}-row cache "
+                           "(embedding, 28 layers, vocabulary projection) in one persistent launch")
+        else:
+            alg, qmm_launches, qsec = qmm_roofline(be, torch, base, VERIFY + 1, reps=20)
+            traffic = None
+            kernel_name = f"qmm_tiled_kernel, {qmm_launches} launches of one target pass at {VERIFY + 1} rows"
         achieved = alg / qsec / 1e9
         step_bytes = base.linear_weight_bytes() + (DEPTH + 1) * draft.linear_weight_bytes()
         line = {
@@ -334,8 +414,8 @@ def main():
                               "pinned read-back of the counters every step, token read-back"},
             "gpu_launches": dec.kernel_launches_per_step * K,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src,
-                         "kernel": f"qmm_tiled_kernel, {qmm_launches} launches of one target pass at {VERIFY + 1} rows",
+                         "traffic": traffic, "peak_source": peak_src,
+                         "kernel": kernel_name,
                          "algorithmic_bytes_per_launch": alg / qmm_launches, "us_per_launch": 1e6 * qsec / qmm_launches},
         }
         if not args.no_cpu_baseline and world == 1:
