@@ -37,6 +37,9 @@ extern "C" {
 #define B200_EPI_RESIDUAL 1  /* y = fp16(residual + fp16(acc))       (mlx_llama.py:246,248)  */
 #define B200_EPI_SILU_MUL 2  /* y = silu(fp16(acc_gate)) * fp16(acc_up), two weight sets     */
                              /*                                       (mlx_llama.py:215)      */
+#define B200_EPI_F32 3       /* b200_qmm_tiled only: y is float [M,N] and receives the fp32     */
+                             /* accumulator - the partial product of one K shard of a         */
+                             /* row-parallel layer, to be all-reduced across GPUs              */
 
 int b200_version(void);
 int b200_last_cuda_error(void);
@@ -137,6 +140,11 @@ int b200_embed_gather(const int* tokens, const uint32_t* wq, const void* scales,
  * mlx_eagle.py:404,408). */
 int b200_rms_norm(const void* x, const void* w, void* y, const int* row_index, int M, int H, float eps,
                   void* stream);
+
+/* Tensor-parallel residual epilogue: h[M,N] = fp16(h + fp16(sum)) with `sum` the all-reduced fp32 partial
+ * products of a row-parallel layer (o_proj / down_proj of mlx_llama.py:246,248 sharded along K).  No
+ * counterpart in the reference, which runs on one device. */
+int b200_residual_add_f32(void* h, const float* sum, int M, int N, void* stream);
 
 /* Tree-position RoPE fused with the KV-cache append.  qkv [M,(Hq+2Hkv)*hd] fp16 holds q|k|v of M
  * tokens; q is rotated in place, k rotated and v copied into cache row prefix[0]+write_off+m of
@@ -267,6 +275,10 @@ int b200_tree_finalize(int depth, int T, const float* pool_scores, const int* po
                        int* fwd_pos, unsigned long long* fwd_mask, int* fwd_prefix, int* tree_position_ids,
                        int* mask_index, int* draft_tokens, int* retrieve, int* tree_info, void* stream);
 int b200_logits_argmax(const void* logits, int R, int V, unsigned long long* best_key, void* stream);
+/* Vocabulary-parallel argmax across GPUs: turns the shard-local keys of b200_logits_argmax into global ones
+ * (index_offset = first vocabulary row of this GPU's shard) and toggles the top bit so that a signed 64-bit MAX
+ * all-reduce orders them; call again with index_offset 0 after the all-reduce to toggle the bit back. */
+int b200_argmax_key_shift(unsigned long long* best_key, int R, unsigned int index_offset, void* stream);
 /* evaluate_posterior_greedy (mlx_eagle.py:311-326) on per-node argmaxes, plus the loop bookkeeping of
  * generate_step (:587-599): next y, accept length, lengths of both caches, generated-token log.
  * accept_rows[0] = accept length, [1..] = accepted node indices (retrieve_indices[best, 1:1+a]). */

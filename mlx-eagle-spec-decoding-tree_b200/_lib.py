@@ -96,6 +96,10 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_forward_workspace_bytes.argtypes = [ctypes.POINTER(ForwardDesc)]
     l.b200_forward.restype = i32
     l.b200_forward.argtypes = [ctypes.POINTER(ForwardDesc), vp]
+    l.b200_residual_add_f32.restype = i32
+    l.b200_residual_add_f32.argtypes = [vp, vp, i32, i32, vp]
+    l.b200_argmax_key_shift.restype = i32
+    l.b200_argmax_key_shift.argtypes = [vp, i32, ctypes.c_uint, vp]
     l.b200_kv_compact.restype = i32
     l.b200_kv_compact.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp]
 

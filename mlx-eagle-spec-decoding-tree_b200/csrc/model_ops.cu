@@ -107,6 +107,19 @@ __global__ void rope_kv_append_kernel(__half* __restrict__ qkv, const int* __res
     }
 }
 
+// ---- tensor-parallel epilogue: h = fp16(h + fp16(sum)) where `sum` holds the all-reduced fp32 partial
+// products of a row-parallel linear layer (the rounding points of the unsharded residual epilogue).
+__global__ void residual_add_f32_kernel(__half* __restrict__ h, const float* __restrict__ sum, int n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    const float4 s = *reinterpret_cast<const float4*>(sum + i);
+    __half2* hp = reinterpret_cast<__half2*>(h + i);
+    hp[0] = __hadd2(hp[0], __floats2half2_rn(s.x, s.y));
+    hp[1] = __hadd2(hp[1], __floats2half2_rn(s.z, s.w));
+}
+
 // Stand-alone operator with the reference's tensor layout: in/out (B, H, L, D), offsets (B, L).
 __global__ void rope_positions_kernel(const __half* __restrict__ in, const int* __restrict__ offsets,
                                       const float* __restrict__ inv_freq, float scaling,
@@ -157,6 +170,15 @@ int b200_rope_kv_append(void* qkv, const int* pos, const float* inv_freq, float 
     dim3 grid(Hq + 2 * Hkv, M);
     b200::launch_kernel(b200::rope_kv_append_kernel, dim3(grid), dim3(hd / 2), 0, static_cast<cudaStream_t>(stream), static_cast<__half*>(qkv), pos, inv_freq, scaling, static_cast<__half*>(kcache),
         static_cast<__half*>(vcache), prefix, write_off, Hq, Hkv, hd, cache_rows);
+    return b200::check_launch();
+}
+
+int b200_residual_add_f32(void* h, const float* sum, int M, int N, void* stream) {
+    if (!h || !sum || M < 1 || N < 4 || (N % 4) != 0) return B200_EINVAL;
+    if (!b200::aligned16(h) || !b200::aligned16(sum)) return B200_EALIGN;
+    const int n = M * N;
+    b200::launch_kernel(b200::residual_add_f32_kernel, dim3((n / 4 + 255) / 256), dim3(256), 0,
+                        static_cast<cudaStream_t>(stream), static_cast<__half*>(h), sum, n);
     return b200::check_launch();
 }
 

@@ -284,6 +284,12 @@ __global__ void __launch_bounds__((WN + 1) * 32, 2) qmm_tiled_kernel(const Tiled
                         }
                     }
                     __align__(16) __half out[8];
+                    if (!DUAL && p.epilogue == B200_EPI_F32) {          // partial sums for a tensor-parallel all-reduce
+                        float* yf = reinterpret_cast<float*>(p.y) + (size_t)tok * p.N + n0;
+                        *reinterpret_cast<float4*>(yf) = make_float4(a0[0], a0[1], a0[2], a0[3]);
+                        *reinterpret_cast<float4*>(yf + 4) = make_float4(a0[4], a0[5], a0[6], a0[7]);
+                        continue;
+                    }
                     if (DUAL) {
 #pragma unroll
                         for (int e = 0; e < 8; e++) out[e] = __float2half_rn(silu_mul_f16(a0[e], a1[e]));
@@ -319,6 +325,10 @@ __global__ void __launch_bounds__((WN + 1) * 32, 2) qmm_tiled_kernel(const Tiled
                         const int tok = mt * 8 + 2 * t + (i & 1);
                         const int nn = nbase + ((i >> 1) ? 8 : 0);
                         if (tok >= p.M || nn >= p.N) continue;
+                        if (!DUAL && p.epilogue == B200_EPI_F32) {
+                            reinterpret_cast<float*>(p.y)[(size_t)tok * p.N + nn] = acc[s][mt][i];
+                            continue;
+                        }
                         __half o;
                         if (DUAL) {
                             o = __float2half_rn(silu_mul_f16(acc[0][mt][i], acc[S - 1][mt][i]));
@@ -491,7 +501,8 @@ size_t b200_qmm_tiled_workspace_bytes(int M, int N, int K) {
 int b200_qmm_tiled(const void* x, const void* wt, const void* wt2, const void* bias, const void* extra, void* y,
                    int M, int N, int K, int epilogue, void* workspace, size_t workspace_bytes, void* stream) {
     if (M < 1 || M > 32 || N < 8 || (N % 8) != 0 || K < b200::kChunkK || (K % b200::kChunkK) != 0) return B200_EINVAL;
-    if (epilogue < B200_EPI_NONE || epilogue > B200_EPI_SILU_MUL) return B200_EINVAL;
+    if (epilogue < B200_EPI_NONE || epilogue > B200_EPI_F32) return B200_EINVAL;
+    if (epilogue == B200_EPI_F32 && bias) return B200_EINVAL;
     const bool dual = epilogue == B200_EPI_SILU_MUL;
     if (!x || !wt || !y || !workspace || (dual && (!wt2 || bias)) || (epilogue == B200_EPI_RESIDUAL && !extra))
         return B200_EINVAL;

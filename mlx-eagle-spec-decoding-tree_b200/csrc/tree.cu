@@ -178,6 +178,13 @@ __global__ void row_argmax_kernel(const __half* __restrict__ logits, int V, unsi
     if ((threadIdx.x & 31) == 0) atomicMax(best_key + r, best);
 }
 
+__global__ void argmax_key_shift_kernel(unsigned long long* __restrict__ best_key, int R, unsigned int index_offset) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = threadIdx.x;
+    if (r < R) best_key[r] = (best_key[r] - index_offset) ^ 0x8000000000000000ull;   // low word: 0xffffffff - index
+}
+
 // ---------------------------------------------------------------- tree expansion (1 CTA, 8 warps)
 struct ExpandParams {
     const __half* logits;                // [R, V]
@@ -609,6 +616,16 @@ int b200_logits_argmax(const void* logits, int R, int V, unsigned long long* bes
     if (!logits || !best_key || R < 1 || R > 32 || V < 1) return B200_EINVAL;
     dim3 grid(b200::nblk_for(V), R);
     b200::launch_kernel(b200::row_argmax_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __half*>(logits), V, best_key);
+    return b200::check_launch();
+}
+
+// Vocabulary-parallel argmax: keys computed on a shard hold shard-local indices.  Shifts them to global
+// indices (index_offset = first vocabulary row of the shard) and toggles the top bit, so that a signed 64-bit
+// MAX all-reduce orders them like the unsigned keys; a second call with offset 0 toggles the bit back.
+int b200_argmax_key_shift(unsigned long long* best_key, int R, unsigned int index_offset, void* stream) {
+    if (!best_key || R < 1 || R > 1024) return B200_EINVAL;
+    b200::launch_kernel(b200::argmax_key_shift_kernel, dim3(1), dim3(((R + 31) / 32) * 32), 0,
+                        static_cast<cudaStream_t>(stream), best_key, R, index_offset);
     return b200::check_launch();
 }
 

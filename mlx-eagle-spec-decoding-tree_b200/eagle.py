@@ -93,7 +93,7 @@ class SpecDecoder:
         self.draft_cache.offset = 0
         self.draft(prompt[None], cache=self.draft_cache, logits_last_only=True)
         logits = self.base(prompt[None], cache=self.base_cache, logits_last_only=True)
-        first = int(torch.argmax(logits[0, -1].float()).item())
+        first = self.base.greedy_token(logits[0, -1])
         self.ctl.zero_()
         host = torch.zeros(16, dtype=torch.int32)
         host[CTL_BASE_LEN] = n
@@ -149,8 +149,14 @@ class SpecDecoder:
         L, p, ck = _lib.lib(), _lib.ptr, _lib.check
         st = _lib.stream_ptr(self.device)
         a = self.base.args
-        ck(L.b200_logits_argmax(p(self.base_logits), self.T + 1, a.vocab_size, p(self.argmax_key), st),
+        base = self.base
+        ck(L.b200_logits_argmax(p(self.base_logits), self.T + 1, base.vocab_local, p(self.argmax_key), st),
            "b200_logits_argmax")
+        if base.tp is not None:
+            # vocabulary-parallel head: per-node (max, argmax) keys of every shard, combined by a MAX all-reduce
+            ck(L.b200_argmax_key_shift(p(self.argmax_key), self.T + 1, base.vocab_offset, st), "b200_argmax_key_shift")
+            base.tp.all_reduce_max(self.argmax_key[: self.T + 1])
+            ck(L.b200_argmax_key_shift(p(self.argmax_key), self.T + 1, 0, st), "b200_argmax_key_shift")
         ck(L.b200_tree_accept(self.T, p(self.argmax_key), p(self.draft_tokens), p(self.retrieve), p(self.tree_info),
                               p(self.ctl), p(self.y), p(self.accept_rows), p(self.out_tokens), p(self.step_log), st),
            "b200_tree_accept")
@@ -187,7 +193,8 @@ class SpecDecoder:
         v = min(self.base.args.vocab_size, self.draft.args.vocab_size)
         self.prefill(torch.randint(0, v, (8,), generator=g, dtype=torch.int32))
         self.step()
-        if capture:
+        if capture and self.base.tp is None:
+            # (a tensor-parallel target all-reduces through torch.distributed: its step is launched eagerly)
             self.capture()
         torch.cuda.synchronize(self.device)
 

@@ -95,6 +95,36 @@ def rope_inv_freqs(args: ModelArgs):
     return (1.0 / freqs).float(), 1.0
 
 
+class TensorParallel:
+    """Which shard of a tensor-parallel model this process holds (``rank`` of ``world`` GPUs of one node) and
+    the ``torch.distributed`` group its all-reduces run in.  q/k/v, gate and up are column-parallel (heads,
+    MLP rows), o_proj and down_proj row-parallel (their K is cut; the fp32 partial products are all-reduced
+    before the residual add), the vocabulary projection is cut by vocabulary rows."""
+
+    def __init__(self, rank: int, world: int, group=None):
+        self.rank, self.world, self.group = int(rank), int(world), group
+
+    def all_reduce_sum(self, t: torch.Tensor):
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+
+    def all_reduce_max(self, t: torch.Tensor):
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+
+
+def _rows(lin: "QLinear", r0: int, r1: int) -> "QLinear":
+    """Output rows [r0, r1) of a linear layer (column-parallel shard)."""
+    return QLinear(lin.weight[r0:r1].contiguous(), lin.scales[r0:r1].contiguous(), lin.biases[r0:r1].contiguous(),
+                   None if lin.bias is None else lin.bias[r0:r1].contiguous())
+
+
+def _cols(lin: "QLinear", k0: int, k1: int) -> "QLinear":
+    """Input features [k0, k1) of a linear layer (row-parallel shard; k0, k1 multiples of 128)."""
+    return QLinear(lin.weight[:, k0 // 8:k1 // 8].contiguous(), lin.scales[:, k0 // 64:k1 // 64].contiguous(),
+                   lin.biases[:, k0 // 64:k1 // 64].contiguous(), None)
+
+
 class QLinear:
     """A 4-bit quantised linear layer: packed weights, fp16 scales / biases, optional fp16 bias."""
 
@@ -188,6 +218,9 @@ class Model:
         self._fwd_ws = None
         self._fwd_ws_key = None
         self._layer_table = None
+        self.tp: Optional[TensorParallel] = None         # set by shard(): this model is one shard of a tensor-parallel model
+        self.vocab_offset = 0
+        self.part32 = None
         self.timeline = None
         self.attn_split_blocks = 0                       # 0 = library default; < 0 = always split the keys across CTAs
         self.phase_mask = 0                              # profiling: run only some phase kinds (0 = all)
@@ -224,6 +257,57 @@ class Model:
         embed = qlin(args.vocab_size, H)
         lm_head = None if args.tie_word_embeddings else qlin(args.vocab_size, H)
         return Model(args, layers, embed, norm_w(), lm_head, device)
+
+    def shard(self, rank: int, world: int, group=None) -> "Model":
+        """This model's shard ``rank`` of ``world`` for tensor-parallel execution (call before ``relayout``).
+        Heads, kv heads, MLP rows and vocabulary rows are cut evenly; embeddings and norms are replicated."""
+        a = self.args
+        if any(v % world for v in (a.num_attention_heads, a.num_key_value_heads, a.vocab_size)) or \
+                (a.intermediate_size // world) % 128 or (self.nq // world) % 128 or (a.vocab_size // world) % 8:
+            raise _lib.B200Error("heads, kv heads, MLP width (in multiples of 128) and vocabulary must divide by the TP degree")
+        nq, nkv, I, V = self.nq // world, self.nkv // world, a.intermediate_size // world, a.vocab_size // world
+        layers = []
+        for lw in self.layers:
+            q = lw["qkv"]
+            if q.weight is None:
+                raise _lib.B200Error("shard() needs the row-major weights: call it before relayout()")
+            parts = [_rows(q, rank * nq, (rank + 1) * nq),
+                     _rows(q, self.nq + rank * nkv, self.nq + (rank + 1) * nkv),
+                     _rows(q, self.nq + self.nkv + rank * nkv, self.nq + self.nkv + (rank + 1) * nkv)]
+            qkv = QLinear(torch.cat([p_.weight for p_ in parts]), torch.cat([p_.scales for p_ in parts]),
+                          torch.cat([p_.biases for p_ in parts]),
+                          None if q.bias is None else torch.cat([p_.bias for p_ in parts]))
+            layers.append(dict(qkv=qkv, o=_cols(lw["o"], rank * nq, (rank + 1) * nq),
+                               gate=_rows(lw["gate"], rank * I, (rank + 1) * I), up=_rows(lw["up"], rank * I, (rank + 1) * I),
+                               down=_cols(lw["down"], rank * I, (rank + 1) * I),
+                               input_norm=lw["input_norm"], post_norm=lw["post_norm"]))
+        import dataclasses
+        largs = dataclasses.replace(a, num_attention_heads=a.num_attention_heads // world,
+                                    num_key_value_heads=a.num_key_value_heads // world, intermediate_size=I)
+        head = _rows(self.lm_head, rank * V, (rank + 1) * V)
+        m = Model(largs, layers, self.embed, self.norm, head, self.device)
+        m.tp = TensorParallel(rank, world, group)
+        m.vocab_offset = rank * V
+        m.part32 = torch.zeros(MAX_ROWS, a.hidden_size, dtype=torch.float32, device=self.device)
+        return m
+
+    def greedy_token(self, logits_row: torch.Tensor) -> int:
+        """Argmax of one row of logits over the whole vocabulary (ties to the lower id); under tensor
+        parallelism every GPU holds a slice and the slices' (max, argmax) pairs are gathered."""
+        v, i = torch.max(logits_row.float(), dim=-1)
+        if self.tp is None:
+            return int(i)
+        import torch.distributed as dist
+        mine = torch.stack([v.double(), (i + self.vocab_offset).double()])
+        allv = [torch.zeros_like(mine) for _ in range(self.tp.world)]
+        dist.all_gather(allv, mine, group=self.tp.group)
+        best = max(allv, key=lambda t: (float(t[0]), -float(t[1])))
+        return int(best[1])
+
+    @property
+    def vocab_local(self) -> int:
+        """Vocabulary rows this model's head produces (all of them unless it is a tensor-parallel shard)."""
+        return self.lm_head.out_features
 
     def state_numpy(self) -> dict:
         """All weights as numpy arrays (packed weights as uint32), for a CPU checker."""
@@ -286,7 +370,7 @@ class Model:
     def can_fuse(self) -> bool:
         """True when the pass can run as the single persistent kernel ``b200_forward``: every linear
         layer in the streaming layout, the embedding still row-major, sizes in multiples of 128."""
-        if not self.fused or os.environ.get("B200_FUSED_FORWARD", "1") == "0":
+        if not self.fused or self.tp is not None or os.environ.get("B200_FUSED_FORWARD", "1") == "0":
             return False
         a = self.args
         if any(lw[k].tiled is None for lw in self.layers for k in ("qkv", "o", "gate", "up", "down")):
@@ -358,6 +442,21 @@ class Model:
             self._fwd_ws[:4352].zero_()
             raise _lib.B200Error(f"b200_forward: a bounded wait gave up inside the kernel (code {code})")
 
+    def _row_parallel(self, x, lin: QLinear, M: int):
+        """h += x . W^T for o_proj / down_proj.  Under tensor parallelism W holds this GPU's K shard: the fp32
+        partial product is all-reduced (NCCL over NVLink), then added to the residual with the rounding points
+        of the unsharded epilogue."""
+        if self.tp is None:
+            self._linear(x, lin, self.h, M, qk.EPI_RESIDUAL, extra=self.h)
+            return
+        if lin.tiled is None:
+            raise _lib.B200Error("tensor-parallel layers need the streaming layout: call relayout() after shard()")
+        self._linear(x, lin, self.part32, M, qk.EPI_F32)
+        part = self.part32[:M]
+        self.tp.all_reduce_sum(part)
+        _lib.check(_lib.lib().b200_residual_add_f32(_lib.ptr(self.h), _lib.ptr(part), M, self.args.hidden_size,
+                                                    _lib.stream_ptr(self.device)), "b200_residual_add_f32")
+
     # ------------------------------------------------------------------ device-side forward
     def _attention_workspace(self, cache: KVCache):
         if self._attn_ws is None or self._attn_ws_rows < cache.rows:
@@ -403,14 +502,15 @@ class Model:
             ck(L.b200_tree_attention(p(self.qkv), nqkv, p(kc), p(vc), p(fwd.mask), p(fwd.prefix), tail,
                                      p(self.attn), M, Hq, Hkv, hd, cache.rows, cache.rows, self.scale,
                                      p(aws), aws.numel(), st), "b200_tree_attention")
-            self._linear(self.attn, lw["o"], self.h, M, qk.EPI_RESIDUAL, extra=self.h)
+            self._row_parallel(self.attn, lw["o"], M)
             ck(L.b200_rms_norm(p(self.h), p(lw["post_norm"]), p(self.xn), None, M, H, eps, st), "b200_rms_norm")
             self._linear(self.xn, lw["gate"], self.act, M, qk.EPI_SILU_MUL, lin2=lw["up"])
-            self._linear(self.act, lw["down"], self.h, M, qk.EPI_RESIDUAL, extra=self.h)
+            self._row_parallel(self.act, lw["down"], M)
         rows = M if logits_rows is None else logits_rows
         ck(L.b200_rms_norm(p(self.h), p(self.norm), p(self.xn), p(row_index), rows, H, eps, st), "final norm")
         self._linear(self.xn, self.lm_head, self.logits, rows, qk.EPI_NONE)
-        return self.logits[:rows]
+        vl = self.vocab_local                      # a tensor-parallel shard produces its slice of the vocabulary
+        return self.logits[:rows] if vl == a.vocab_size else self.logits.view(-1)[: rows * vl].view(rows, vl)
 
     # ------------------------------------------------------------------ reference-style call
     def __call__(self, inputs: torch.Tensor, cache: Optional[KVCache] = None, mask: Optional[torch.Tensor] = None,

@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 
-EPI_NONE, EPI_RESIDUAL, EPI_SILU_MUL = 0, 1, 2
+EPI_NONE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_F32 = 0, 1, 2, 3
 _WORKSPACE_BYTES = 32 << 20
 _workspaces: dict = {}
 
