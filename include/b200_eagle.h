@@ -238,9 +238,38 @@ typedef struct b200_forward_desc {
                             /* phase_mask: profiling only, 0 = run everything; else bit k set = run phase  */
                             /* kind k (0 embedding, 1 qkv, 2 attention, 3 merge, 4 o_proj, 5 gate/up,      */
                             /* 6 down_proj, 7 vocabulary projection); results are then meaningless         */
+    /* Tensor parallelism over the GPUs of one node (tp_world <= 1 = off, all fields below zero).  The call
+     * then runs shard tp_rank of tp_world: n_heads, n_kv_heads and intermediate are this shard's counts
+     * (heads and MLP rows cut evenly; o_proj / down_proj weights hold this shard's K columns), head_rows
+     * is the number of vocabulary rows in lm_head_tiled (logits [rows_out][head_rows]; 0 = vocab), the
+     * embedding and the norms are whole.  tp_peers[r] is rank r's exchange buffer
+     * (b200_forward_tp_buffer_bytes(hidden) bytes, zero before the first launch, 16-byte aligned) as
+     * mapped into this process: peer-accessible device memory, e.g. a CUDA IPC or symmetric-memory
+     * mapping.  o_proj and down_proj leave fp32 partial products in the GPU's own buffer; each GPU then
+     * raises a flag word in every peer's buffer, waits (bounded; error code 12 in the workspace's error
+     * word on timeout) for the peers' flags, and adds all partial products in rank order with plain
+     * loads over NVLink, so every GPU holds bit-identical hidden states.  tp_seq = exchanges done by
+     * all earlier launches on these buffers (2 * n_layers per launch, the same on every rank): flags
+     * only grow.  Every rank must launch the same sequence of passes; the kernels of one pass run
+     * concurrently, one per GPU, never two ranks on one GPU. */
+    int tp_world, tp_rank;
+    unsigned tp_seq;
+    int head_rows;
+    void* tp_peers[8];
 } b200_forward_desc;
 
 size_t b200_forward_workspace_bytes(const b200_forward_desc* desc);
+size_t b200_forward_tp_buffer_bytes(int hidden);
+
+/* Exchange buffers for tp_peers.  alloc: `bytes` of zeroed device memory on the current device plus a
+ * 64-byte handle to hand to the other processes of the node (any host channel); open: map a peer's
+ * buffer into this process (peer access is enabled on demand); close / free undo them.  The buffers
+ * must be zero and every rank must have opened all of them before the first tensor-parallel launch. */
+#define B200_TP_HANDLE_BYTES 64
+int b200_tp_exchange_alloc(size_t bytes, void** ptr, unsigned char* handle);
+int b200_tp_exchange_open(const unsigned char* handle, void** ptr);
+int b200_tp_exchange_close(void* ptr);
+int b200_tp_exchange_free(void* ptr);
 int b200_forward(const b200_forward_desc* desc, void* stream);
 
 /* ------------------------------------------------------------------------------------------

@@ -94,6 +94,16 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_tree_accept.argtypes = [i32] + [vp] * 10
     l.b200_forward_workspace_bytes.restype = sz
     l.b200_forward_workspace_bytes.argtypes = [ctypes.POINTER(ForwardDesc)]
+    l.b200_forward_tp_buffer_bytes.restype = sz
+    l.b200_forward_tp_buffer_bytes.argtypes = [i32]
+    l.b200_tp_exchange_alloc.restype = i32
+    l.b200_tp_exchange_alloc.argtypes = [sz, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]
+    l.b200_tp_exchange_open.restype = i32
+    l.b200_tp_exchange_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+    l.b200_tp_exchange_close.restype = i32
+    l.b200_tp_exchange_close.argtypes = [vp]
+    l.b200_tp_exchange_free.restype = i32
+    l.b200_tp_exchange_free.argtypes = [vp]
     l.b200_forward.restype = i32
     l.b200_forward.argtypes = [ctypes.POINTER(ForwardDesc), vp]
     l.b200_residual_add_f32.restype = i32
@@ -116,7 +126,8 @@ class ForwardDesc(ctypes.Structure):
             "final_norm", "lm_head_tiled", "layer_table", "h", "hw", "qkv", "attn", "act", "logits", "kv_cache",
             "workspace")]
         + [("workspace_bytes", ctypes.c_size_t), ("timeline", ctypes.c_void_p), ("timeline_pitch", ctypes.c_int),
-           ("phase_mask", ctypes.c_int)])
+           ("phase_mask", ctypes.c_int), ("tp_world", ctypes.c_int), ("tp_rank", ctypes.c_int),
+           ("tp_seq", ctypes.c_uint), ("head_rows", ctypes.c_int), ("tp_peers", ctypes.c_void_p * 8)])
 
 
 def check(rc: int, what: str) -> None:

@@ -62,8 +62,11 @@ constexpr int kCsPitch = 64;                  // cos/sin table: cs[token][i], i 
 // sync words (ints) at the head of the workspace
 constexpr int kSyncBar = 0, kSyncExit = 1, kSyncErr = 2;
 
-enum { EPI_QKV = 0, EPI_SILU = 1, EPI_RESID = 2, EPI_HEAD = 3 };
-enum { K_EMBED = 0, K_A = 1, K_B1 = 2, K_B2 = 3, K_C = 4, K_D = 5, K_E = 6, K_HEAD = 7 };
+enum { EPI_QKV = 0, EPI_SILU = 1, EPI_RESID = 2, EPI_HEAD = 3, EPI_TP = 4 };
+enum { K_EMBED = 0, K_A = 1, K_B1 = 2, K_B2 = 3, K_C = 4, K_D = 5, K_E = 6, K_HEAD = 7, K_R = 8 };
+constexpr int kMaxTp = 8;                     // GPUs of one tensor-parallel group
+constexpr uint32_t kTpWaitLimit = 1u << 24;   // polls of a peer's flag (a microsecond or so each) before giving up
+constexpr int kTpFlagBytes = 1024;            // head of every GPU's exchange buffer: one 64-byte flag line per peer
 enum { PLAN_A = 0, PLAN_C = 1, PLAN_D = 2, PLAN_E = 3, PLAN_HEAD = 4 };
 
 struct LayerPtrs {                 // one entry per layer, in device memory (8 pointers = 64 bytes)
@@ -110,6 +113,14 @@ struct FwdParams {
     float* partial;
     int nkb, qrp;
     PhasePlan plan[5];
+    // Tensor parallelism (tp_world > 1): this launch is rank tp_rank's shard.  o_proj / down_proj write fp32
+    // partial products into this GPU's exchange buffer; after a handshake through flag words in the peers'
+    // buffers every GPU adds the partial products of all ranks (plain loads over NVLink, rank order) and the
+    // residual.  tp_peers[r] = rank r's exchange buffer as mapped into this process.
+    int tp_world, tp_rank;
+    unsigned tp_seq;               // exchanges done by earlier launches (flags only ever grow)
+    unsigned char* tp_peers[kMaxTp];
+    int head_rows;                 // rows of the vocabulary projection held here (a vocabulary shard under TP)
     int attn_fused_max;            // single-phase attention while the cache spans at most this many key blocks
     unsigned phase_mask;           // bit per phase kind (K_*): kinds to run; all ones normally
     alignas(64) CUtensorMap kvmap; // the whole KV cache as a 2-D fp16 tensor [rows][head_dim], 64 x 64 boxes, 128-byte swizzle
@@ -158,6 +169,7 @@ struct Ctx {
     uint32_t ause;      // key blocks this consumer warp has taken from its slot so far
     int ans;            // number of key-block slots (attention geometry)
     uint32_t epoch;     // grid barriers before the current phase
+    uint32_t tpx;       // tensor-parallel exchanges done in this launch
     int lane, warp;
 };
 
@@ -214,7 +226,8 @@ __device__ void grid_barrier(const FwdParams& p, Ctx& c) {
             tl = p.timeline + ((size_t)blockIdx.x * p.timeline_pitch + (c.epoch - 1)) * 8;
             tl[0] = global_ns();
         }
-        __threadfence();               // cumulative: covers the CTA's writes ordered before the bar.sync
+        if (p.tp_world > 1) __threadfence_system();    // partial products are read by other GPUs
+        else __threadfence();          // cumulative: covers the CTA's writes ordered before the bar.sync
         fence_proxy_async_all();
         atomicAdd(p.sync + kSyncBar, 1);
         const int target = (int)(c.epoch * gridDim.x);
@@ -272,6 +285,88 @@ __device__ __forceinline__ bool drain_blocks(const FwdParams& p, Ctx& c) {
     ok = __all_sync(0xffffffffu, ok);
     if (!ok && c.lane == 0) raise_error(p, c, 9);
     return ok;
+}
+
+// ================================================================================ tensor parallelism
+// This GPU's buffer of fp32 partial products for the exchange in progress (two buffers, used in turn, so
+// that a GPU that is one exchange ahead never overwrites what a slower peer is still reading).
+__device__ __forceinline__ float* tp_partial_of(const FwdParams& p, int rank, uint32_t x) {
+    return reinterpret_cast<float*>(p.tp_peers[rank] + kTpFlagBytes) + (size_t)((p.tp_seq + x) & 1u) * 32 * p.H;
+}
+__device__ __forceinline__ float* tp_partial(const FwdParams& p, const Ctx& c) {
+    return tp_partial_of(p, p.tp_rank, c.tpx);
+}
+__device__ __forceinline__ float4 ld_sys_f4(const float* q) {
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(q) : "memory");
+    return v;
+}
+
+// The all-reduce of a row-parallel layer, after the local grid barrier that follows the partial products:
+// CTA 0 raises this GPU's flag in every peer's buffer (release at system scope), every CTA waits (bounded) for
+// the flags of all peers in its own GPU's buffer, then all consumer threads add the ranks' partial products in
+// rank order, add the residual and write h, h*w and the sums of squares exactly like the single-GPU epilogue.
+__device__ __forceinline__ void tp_reduce_phase(const FwdParams& p, Ctx& c, const __half* wn) {
+    const unsigned seq = p.tp_seq + c.tpx + 1;
+    if (blockIdx.x == 0 && threadIdx.x < (unsigned)p.tp_world && (int)threadIdx.x != p.tp_rank) {
+        unsigned* flag = reinterpret_cast<unsigned*>(p.tp_peers[threadIdx.x] + p.tp_rank * 64);
+        asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(flag), "r"(seq) : "memory");
+    }
+    if (threadIdx.x == 0 && !*c.abort_flag) {
+        bool ok = true;
+        for (int r = 0; r < p.tp_world && ok; r++) {
+            if (r == p.tp_rank) continue;
+            const unsigned* flag = reinterpret_cast<const unsigned*>(p.tp_peers[p.tp_rank] + r * 64);
+            ok = false;
+            for (uint32_t i = 0; i < kTpWaitLimit; i++) {
+                unsigned v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(flag) : "memory");
+                if ((int)(v - seq) >= 0) { ok = true; break; }
+            }
+        }
+        if (!ok) raise_error(p, c, 12);
+    }
+    consumer_sync(kNCons);
+    if (!*c.abort_flag) {
+        const int upt = p.H / 8;                       // 8-column units per token row
+        const int units = p.M * upt;
+        const int units32 = (units + 31) & ~31;
+        for (int i = blockIdx.x * kNCons + threadIdx.x; i < units32; i += gridDim.x * kNCons) {
+            const int tok = i / upt, n0 = (i - tok * upt) * 8;
+            const bool valid = i < units;
+            float ss = 0.f;
+            if (valid) {
+                float a[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) a[e] = 0.f;
+                for (int r = 0; r < p.tp_world; r++) {
+                    const float* src = tp_partial_of(p, r, c.tpx) + (size_t)tok * p.H + n0;
+                    const float4 u0 = ld_sys_f4(src);
+                    const float4 u1 = ld_sys_f4(src + 4);
+                    a[0] += u0.x; a[1] += u0.y; a[2] += u0.z; a[3] += u0.w;
+                    a[4] += u1.x; a[5] += u1.y; a[6] += u1.z; a[7] += u1.w;
+                }
+                const uint4 rv = __ldcg(reinterpret_cast<const uint4*>(p.h + (size_t)tok * p.H + n0));
+                const uint4 wv = *reinterpret_cast<const uint4*>(wn + n0);
+                const __half* rh = reinterpret_cast<const __half*>(&rv);
+                const __half* wh = reinterpret_cast<const __half*>(&wv);
+                __align__(16) __half out[8], hw[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    out[e] = __hadd(rh[e], __float2half_rn(a[e]));
+                    const float fv = __half2float(out[e]);
+                    ss += fv * fv;
+                    hw[e] = __hmul(out[e], wh[e]);
+                }
+                *reinterpret_cast<uint4*>(p.h + (size_t)tok * p.H + n0) = *reinterpret_cast<const uint4*>(out);
+                *reinterpret_cast<uint4*>(p.hw + xt_index(tok, n0, p.mp)) = *reinterpret_cast<const uint4*>(hw);
+            }
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);          // the two 8-column halves of a 16-column part
+            if (valid && (threadIdx.x & 1) == 0) p.ssq[(n0 >> 4) * kSsqPitch + tok] = ss;
+        }
+    }
+    c.tpx++;
 }
 
 // ================================================================================ QMM phases
@@ -435,7 +530,7 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
     const int rec_cstride = (TPI >= 4) ? 4 * kRec : chunk_bytes;
     const int nchunks_total = d.K / kChunkK;
     const int nitems = d.pl.row_items * d.pl.splits;
-    const bool need_rstd = (EPI != EPI_RESID);
+    const bool need_rstd = (EPI != EPI_RESID && EPI != EPI_TP);
     bool rstd_done = !need_rstd;
     stamp(p, c, 2);
 
@@ -595,7 +690,13 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
                         }
                     }
                     __align__(16) __half out[8];
-                    if (EPI == EPI_RESID) {
+                    if (EPI == EPI_TP) {
+                        if (valid) {
+                            float* dst = tp_partial(p, c) + (size_t)tok * d.N + n0;
+                            *reinterpret_cast<float4*>(dst) = make_float4(a0[0], a0[1], a0[2], a0[3]);
+                            *reinterpret_cast<float4*>(dst + 4) = make_float4(a0[4], a0[5], a0[6], a0[7]);
+                        }
+                    } else if (EPI == EPI_RESID) {
                         float ss = 0.f;
                         if (valid) {
                             const uint4 rv = __ldcg(reinterpret_cast<const uint4*>(p.h + (size_t)tok * d.N + n0));
@@ -642,7 +743,18 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
         } else if (leader) {
             // ---- direct epilogue from the registers of the tile's first warp
             const int nbase = tile_global * 16 + g;
-            if (EPI == EPI_RESID) {
+            if (EPI == EPI_TP) {
+                float* dst = tp_partial(p, c);
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int tok = mt * 8 + 2 * t + (i & 1);
+                        const int nn = nbase + ((i >> 1) ? 8 : 0);
+                        if (tok < d.xrows && nn < d.N) dst[(size_t)tok * d.N + nn] = acc[0][mt][i];
+                    }
+                }
+            } else if (EPI == EPI_RESID) {
                 // residuals and norm weights first, all loads in flight together (h is read and written here)
                 unsigned short res[MT][4];
 #pragma unroll
@@ -1469,6 +1581,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
     c.s_rstd = s_rstd;
     c.pos = 0;
     c.epoch = 0;
+    c.tpx = 0;
     c.lane = threadIdx.x & 31;
     c.warp = threadIdx.x >> 5;
 
@@ -1512,6 +1625,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             kind = K_A + (ph - 1) - 6 * l;
         }
         if (!((p.phase_mask >> kind) & 1u)) continue;
+        const __half* tp_wn = nullptr;
         if (kind == K_EMBED) {
             if (!producer) embed_phase(p, c);
         } else if (kind == K_B1) {
@@ -1534,7 +1648,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             d.row_lo = 0; d.row_cnt = p.M;
             d.y_tiled = false;
             d.w1 = nullptr; d.bias = nullptr; d.wn = nullptr;
-            int epi = EPI_RESID;
+            int epi = p.tp_world > 1 ? EPI_TP : EPI_RESID;
             if (kind == K_A) {
                 d.x = p.hw; d.w0 = lp.qkv_w; d.bias = lp.qkv_bias; d.y = p.qkv;
                 d.N = p.NQKV; d.K = p.H; d.pl = p.plan[PLAN_A]; epi = EPI_QKV;
@@ -1551,8 +1665,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             } else {                                   // K_HEAD, on the selected rows
                 d.row_lo = row_off; d.row_cnt = p.rows_out;       // all rows are multiplied, the selected ones stored
                 d.x = p.hw; d.w0 = p.head_w; d.y = p.logits;
-                d.N = p.V; d.K = p.H; d.pl = p.plan[PLAN_HEAD]; epi = EPI_HEAD;
+                d.N = p.head_rows; d.K = p.H; d.pl = p.plan[PLAN_HEAD]; epi = EPI_HEAD;
             }
+            tp_wn = d.wn;
             if (producer) {
                 qmm_produce<MT>(p, c, d, c.epoch, kind == K_D);
             } else if (kind == K_D) {
@@ -1564,6 +1679,15 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
         if (kind != K_HEAD) {
             if (producer) c.epoch++;
             else grid_barrier(p, c);
+        }
+        if (p.tp_world > 1 && (kind == K_C || kind == K_E)) {
+            // the partial products of all GPUs -> h, h*w, sums of squares (every GPU computes all of it)
+            if (producer) {
+                c.epoch++;
+            } else {
+                tp_reduce_phase(p, c, tp_wn);
+                grid_barrier(p, c);
+            }
         }
     }
 
@@ -1658,6 +1782,12 @@ bool fwd_shape_ok(const b200_forward_desc* d) {
     if (d->vocab < 8 || (d->vocab % 8) != 0 || d->n_layers < 1 || d->n_layers > kMaxLayers) return false;
     if (d->tail < 1 || d->tail > 64 || d->write_off < 0 || d->write_off + d->M > d->tail) return false;
     if (d->cache_rows < d->tail) return false;
+    if (d->head_rows < 0 || (d->head_rows % 8) != 0 || d->head_rows > d->vocab) return false;
+    if (d->tp_world > 1) {
+        if (d->tp_world > kMaxTp || d->tp_rank < 0 || d->tp_rank >= d->tp_world) return false;
+    } else if (d->tp_world < 0) {
+        return false;
+    }
     return true;
 }
 
@@ -1670,7 +1800,8 @@ WsLayout fwd_layout(const b200_forward_desc* d, PhasePlan (&plan)[5]) {
     plan[PLAN_C] = make_plan(d->hidden, d->n_heads * d->head_dim, grid, mt, false);
     plan[PLAN_D] = make_plan(d->intermediate, d->hidden, grid, mt, true);
     plan[PLAN_E] = make_plan(d->hidden, d->intermediate, grid, mt, false);
-    plan[PLAN_HEAD] = make_plan(d->vocab, d->hidden, grid, mt, false);
+    const int head_rows = d->head_rows > 0 ? d->head_rows : d->vocab;
+    plan[PLAN_HEAD] = make_plan(head_rows, d->hidden, grid, mt, false);
     // split-K scratch: sized for any row count up to 32, so one workspace serves every pass shape
     size_t pb = 0;
     for (int m = 1; m <= 4; m++) {
@@ -1678,7 +1809,7 @@ WsLayout fwd_layout(const b200_forward_desc* d, PhasePlan (&plan)[5]) {
                           make_plan(d->hidden, d->n_heads * d->head_dim, grid, m, false),
                           make_plan(d->intermediate, d->hidden, grid, m, true),
                           make_plan(d->hidden, d->intermediate, grid, m, false),
-                          make_plan(d->vocab, d->hidden, grid, m, false)};
+                          make_plan(head_rows, d->hidden, grid, m, false)};
         for (int i = 0; i < 5; i++) pb = std::max(pb, partial_bytes(q[i], m * 8, i == PLAN_D));
     }
     WsLayout w{};
@@ -1762,6 +1893,11 @@ extern "C" {
 
 using namespace b200;
 
+size_t b200_forward_tp_buffer_bytes(int hidden) {
+    if (hidden < 128 || (hidden % 128) != 0) return 0;
+    return (size_t)kTpFlagBytes + (size_t)2 * 32 * hidden * sizeof(float);
+}
+
 size_t b200_forward_workspace_bytes(const b200_forward_desc* d) {
     if (!fwd_shape_ok(d)) return 0;
     PhasePlan plan[5];
@@ -1813,6 +1949,17 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
     {
         const int rc = make_kv_map(&p.kvmap, d->kv_cache, d->n_layers, d->n_kv_heads, d->cache_rows, d->head_dim);
         if (rc != B200_OK) return rc;
+    }
+    p.head_rows = d->head_rows > 0 ? d->head_rows : d->vocab;
+    p.tp_world = d->tp_world > 1 ? d->tp_world : 1;
+    p.tp_rank = d->tp_world > 1 ? d->tp_rank : 0;
+    p.tp_seq = d->tp_seq;
+    if (p.tp_world > 1) {
+        for (int r = 0; r < p.tp_world; r++) {
+            if (!d->tp_peers[r]) return B200_EINVAL;
+            if (!aligned16(d->tp_peers[r])) return B200_EALIGN;
+            p.tp_peers[r] = static_cast<unsigned char*>(d->tp_peers[r]);
+        }
     }
     p.phase_mask = d->phase_mask ? (unsigned)d->phase_mask : 0xffu;
     p.attn_fused_max = d->attn_split_blocks > 0 ? d->attn_split_blocks - 1 : (d->attn_split_blocks < 0 ? 0 : 32);

@@ -103,6 +103,9 @@ class TensorParallel:
 
     def __init__(self, rank: int, world: int, group=None):
         self.rank, self.world, self.group = int(rank), int(world), group
+        # Exchange buffers of the persistent kernel's in-kernel all-reduce (one per GPU, mapped into every
+        # process of the group through CUDA IPC) and the number of exchanges launched so far (flags only grow).
+        self.peers, self.seq = None, 0
 
     def all_reduce_sum(self, t: torch.Tensor):
         import torch.distributed as dist
@@ -111,6 +114,42 @@ class TensorParallel:
     def all_reduce_max(self, t: torch.Tensor):
         import torch.distributed as dist
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+
+    def open_exchange(self, hidden: int):
+        """Allocate this GPU's exchange buffer, trade IPC handles over the process group and map the
+        peers' buffers; returns when every rank has done so (collective call)."""
+        import torch.distributed as dist
+        lib = _lib.lib()
+        nbytes = lib.b200_forward_tp_buffer_bytes(hidden)
+        mine, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        _lib.check(lib.b200_tp_exchange_alloc(nbytes, ctypes.byref(mine), handle), "b200_tp_exchange_alloc")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=self.group)
+        peers = []
+        for r, hb in enumerate(handles):
+            if r == self.rank:
+                peers.append(mine.value)
+                continue
+            q = ctypes.c_void_p()
+            _lib.check(lib.b200_tp_exchange_open(hb, ctypes.byref(q)), "b200_tp_exchange_open")
+            peers.append(q.value)
+        dist.barrier(group=self.group)
+        self.peers, self.seq = peers, 0
+
+    def close_exchange(self):
+        """Unmap the peers' buffers and free this GPU's (collective: no rank may still be inside a pass)."""
+        if self.peers is None:
+            return
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        lib = _lib.lib()
+        for r, q in enumerate(self.peers):
+            if r != self.rank:
+                lib.b200_tp_exchange_close(ctypes.c_void_p(q))
+        dist.barrier(group=self.group)
+        lib.b200_tp_exchange_free(ctypes.c_void_p(self.peers[self.rank]))
+        self.peers = None
 
 
 def _rows(lin: "QLinear", r0: int, r1: int) -> "QLinear":
@@ -370,15 +409,18 @@ class Model:
     def can_fuse(self) -> bool:
         """True when the pass can run as the single persistent kernel ``b200_forward``: every linear
         layer in the streaming layout, the embedding still row-major, sizes in multiples of 128."""
-        if not self.fused or self.tp is not None or os.environ.get("B200_FUSED_FORWARD", "1") == "0":
+        if not self.fused or os.environ.get("B200_FUSED_FORWARD", "1") == "0":
             return False
+        if self.tp is not None and (self.tp.peers is None or self.tp.world > 8):
+            return False                         # a shard fuses once open_exchange() has mapped the peers' buffers
         a = self.args
         if any(lw[k].tiled is None for lw in self.layers for k in ("qkv", "o", "gate", "up", "down")):
             return False
         if self.lm_head.tiled is None or self.embed.weight is None:
             return False
         return (a.hidden_size % 128 == 0 and a.hidden_size <= 8192 and a.intermediate_size % 128 == 0
-                and self.nq % 128 == 0 and a.head_dim in (64, 128) and a.vocab_size % 8 == 0)
+                and self.nq % 128 == 0 and a.head_dim in (64, 128) and a.vocab_size % 8 == 0
+                and self.vocab_local % 8 == 0)
 
     def _fused_desc(self, M, cache, write_off, tail, fwd, rows, row_index):
         a = self.args
@@ -405,6 +447,8 @@ class Model:
         d.h, d.hw, d.qkv, d.attn, d.act, d.logits = p(self.h), p(self.hw), p(self.qkv), p(self.xt_attn), \
             p(self.xt_act), p(self.logits)
         d.kv_cache = p(cache.data)
+        if self.tp is not None:
+            d.head_rows = self.vocab_local
         key = (cache.rows,)
         if self._fwd_ws is None or self._fwd_ws_key != key:
             d32 = _lib.ForwardDesc.from_buffer_copy(d)
@@ -417,6 +461,11 @@ class Model:
         d.workspace, d.workspace_bytes = p(self._fwd_ws), self._fwd_ws.numel()
         d.phase_mask = self.phase_mask
         d.attn_split_blocks = self.attn_split_blocks
+        if self.tp is not None:
+            d.tp_world, d.tp_rank, d.tp_seq, d.head_rows = self.tp.world, self.tp.rank, self.tp.seq & 0xffffffff, \
+                self.vocab_local
+            for r, q in enumerate(self.tp.peers):
+                d.tp_peers[r] = q
         if self.timeline is not None:
             d.timeline, d.timeline_pitch = p(self.timeline), self.timeline.shape[1]
         return d
@@ -428,7 +477,8 @@ class Model:
         (``self.timeline`` int64 ``[SMs, barriers + 1, 8]``; the last entry holds the end of the kernel)."""
         if on:
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-            self.timeline = torch.zeros(sms, 6 * self.args.num_hidden_layers + 2, 8, dtype=torch.int64,
+            per_layer = 6 if self.tp is None else 8          # a shard has two more barriers per layer
+            self.timeline = torch.zeros(sms, per_layer * self.args.num_hidden_layers + 2, 8, dtype=torch.int64,
                                         device=self.device)
         else:
             self.timeline = None
@@ -481,7 +531,10 @@ class Model:
             rows = M if logits_rows is None else logits_rows
             desc = self._fused_desc(M, cache, write_off, tail, fwd, rows, row_index)
             _lib.check(_lib.lib().b200_forward(ctypes.byref(desc), _lib.stream_ptr(self.device)), "b200_forward")
-            return self.logits[:rows]
+            vl = self.vocab_local
+            if self.tp is not None:
+                self.tp.seq += 2 * self.args.num_hidden_layers      # one exchange after o_proj, one after down_proj
+            return self.logits[:rows] if vl == self.args.vocab_size else self.logits.view(-1)[: rows * vl].view(rows, vl)
         a, L, lib = self.args, _lib.lib(), _lib.lib()
         st, p = _lib.stream_ptr(self.device), _lib.ptr
         ws = qk.workspace(self.device)

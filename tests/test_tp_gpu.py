@@ -1,6 +1,7 @@
-"""Tensor-parallel target (column/row-parallel shards, NCCL all-reduce of the row-parallel partial products,
-vocabulary-parallel argmax) on two GPUs: greedy speculative generation must equal the committed oracle output.
-Skipped when fewer than two GPUs are visible."""
+"""Tensor-parallel target (column/row-parallel shards, vocabulary-parallel argmax) on two GPUs, the row-parallel
+partial products reduced either by NCCL between per-op kernels or inside the persistent kernel over peer
+memory: greedy speculative generation must equal the committed oracle output both ways, and the two ways
+must agree on the logits.  Skipped when fewer than two GPUs are visible."""
 import json
 import os
 import sys
@@ -32,11 +33,24 @@ def _rank(rank, world, port, out):
     draft.norm.mul_(8.0)
     shard = base.shard(rank, world).relayout()
     draft.relayout()
-    res = be.generate_step(torch.tensor(g["prompt"]), shard, draft, depth=3, verify_num_tokens=15, max_tokens=40, N=40,
-                           verbose=False)
+    prompt = torch.tensor(g["prompt"])
+    assert not shard.can_fuse()
+    res = be.generate_step(prompt, shard, draft, depth=3, verify_num_tokens=15, max_tokens=40, N=40, verbose=False)
+    cache = shard.make_cache(128)
+    per_op = shard(prompt[None], cache=cache)[0].float().cpu()
+    # the same shard with the all-reduce inside the persistent kernel
+    shard.tp.open_exchange(args.hidden_size)
+    assert shard.can_fuse() and shard.launches_per_forward == 1
+    cache = shard.make_cache(128)
+    fused = shard(prompt[None], cache=cache)[0].float().cpu()
+    shard.check_fused_error()
+    res2 = be.generate_step(prompt, shard, draft, depth=3, verify_num_tokens=15, max_tokens=40, N=40, verbose=False)
+    shard.check_fused_error()
+    err = float(((fused - per_op).abs() - 2.0 ** -6 * per_op.abs()).max())      # <= 2e-2 wanted
     if rank == 0:
-        out.put((res["tokens"], res["accept_lengths"], res["decoder"].graph is not None))
+        out.put((res["tokens"], res["accept_lengths"], res2["tokens"], res2["accept_lengths"], err))
     dist.barrier()
+    shard.tp.close_exchange()
     dist.destroy_process_group()
 
 
@@ -53,7 +67,7 @@ def test_two_gpu_tensor_parallel_target_matches_golden_generation(cuda):
     for p in procs:
         p.start()
     try:
-        tokens, accept, graphed = out.get(timeout=150)
+        tokens, accept, tokens2, accept2, err = out.get(timeout=200)
         for p in procs:
             p.join(timeout=60)
             assert p.exitcode == 0
@@ -63,3 +77,6 @@ def test_two_gpu_tensor_parallel_target_matches_golden_generation(cuda):
                 p.kill()
     assert tokens == g["random_draft_d3_t15"]["tokens"]
     assert accept == g["random_draft_d3_t15"]["accept_lengths"]
+    assert err <= 2e-2                       # |fused - per-op| <= 2^-6 |per-op| + 2e-2 on every logit
+    assert tokens2 == g["random_draft_d3_t15"]["tokens"]
+    assert accept2 == g["random_draft_d3_t15"]["accept_lengths"]
