@@ -156,7 +156,7 @@ def forward_algorithmic_bytes(model, rows, kv_rows):
                  + 2 * _qmm_bytes(rows, I, H) - 2 * rows * H - 2 * rows * I
                  + _qmm_bytes(rows, H, I) + resid
                  + 2 * kv_rows * a.num_key_value_heads * a.head_dim * 2)
-    return len(model.layers) * per_layer + _qmm_bytes(rows, a.vocab_size, H)
+    return len(model.layers) * per_layer + _qmm_bytes(rows, model.vocab_local, H)
 
 
 def forward_roofline(torch, model, cache, rows, prefix, reps):
@@ -267,6 +267,133 @@ def reduce_counters(dist, torch, world, produced, sec, e2e_tokens, e2e_sec, dev)
     return float(sums[0]), float(maxs[1]), float(sums[2]), float(maxs[3])
 
 
+# Tensor-parallel workloads (--workload): one request stream, the target cut across all ranks, the draft
+# replicated.  name -> (target preset, draft preset, prompt, depth, verify tokens)
+TP_WORKLOADS = {
+    "tp70b": ("llama3-70b", "llama3-8b", 512, 3, 23),
+    "tp7b": ("qwen2-7b", "qwen2-0.5b", 256, 3, 15),
+}
+
+
+def run_tensor_parallel(args, rank, world, local_rank):
+    """One request stream with a tensor-parallel target: column/row-parallel shards, the all-reduce of the
+    row-parallel partial products inside the persistent kernel over peer memory, vocabulary-parallel argmax.
+    Also times one target pass both ways: the persistent kernel, and the per-op kernels with NCCL all-reduces."""
+    import torch
+    import torch.distributed as dist
+    import b200_eagle as be
+
+    tname, dname, prompt_len, depth, verify = TP_WORKLOADS[args.workload]
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world < 2:
+        raise SystemExit("--workload tp*: launch under torch.distributed.run with 2, 4 or 8 ranks")
+    dist.init_process_group("nccl", device_id=dev)
+    warmup, K = max(args.warmup, 3), args.steps
+    tshape, dshape = be.shape_preset(tname), be.shape_preset(dname)
+    draft = be.Model.random_init(dshape, seed=1000, device=dev).relayout()          # same weights on every rank
+    base = be.Model.random_init_shard(tshape, 2000, dev, rank, world).relayout()
+    base.tp.open_exchange(tshape.hidden_size)
+    assert base.can_fuse()
+    rows = ((prompt_len + 8 * (warmup + K + depth + 8) + verify + 128 + 63) // 64) * 64
+    dec = be.SpecDecoder(base, draft, depth, verify, cache_rows=rows, max_out_tokens=8 * (warmup + K) + 512,
+                         max_steps=warmup + K + 64)
+    dec.warmup(capture=True)
+    assert dec.graph is not None
+    g = torch.Generator().manual_seed(1234)
+    prompt_host = torch.randint(0, min(dshape.vocab_size, tshape.vocab_size), (prompt_len,), generator=g,
+                                dtype=torch.int32).pin_memory()
+    dec.prefill(prompt_host)
+    for _ in range(warmup):
+        dec.replay()
+    torch.cuda.synchronize()
+    n0 = int(dec.ctl[3])
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        dec.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    sec = e0.elapsed_time(e1) / 1e3
+    clocks = sampler.stop()
+    produced = int(dec.ctl[3]) - n0
+    base.check_fused_error()
+    log = dec.step_log[2 * warmup: 2 * (warmup + K)].cpu().view(-1, 2)
+    mean_accept = float(log[:, 0].float().mean())
+
+    n_e2e = min(K, 300)
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = time.perf_counter()
+    res = dec.generate(prompt_host, max_tokens=n_e2e, N=n_e2e)
+    torch.cuda.synchronize()
+    e2e_sec = time.perf_counter() - t0
+    e2e_steps = max(res["steps_launched"], 1)
+
+    # one target pass alone, both ways (collective: every rank runs it)
+    prefix_now = int(dec.ctl[0])
+    alg, fsec = forward_roofline(torch, base, dec.base_cache, verify + 1, prefix_now, reps=20)
+    base.fused = False                                # per-op kernels + NCCL all-reduce, launched eagerly
+    f = base.fwd
+    for _ in range(2):
+        base.forward_device(verify + 1, dec.base_cache, 0, verify + 1)
+    torch.cuda.synchronize()
+    dist.barrier()
+    n0e, n1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0e.record()
+    for _ in range(5):
+        base.forward_device(verify + 1, dec.base_cache, 0, verify + 1)
+    n1e.record()
+    torch.cuda.synchronize()
+    nccl_sec = n0e.elapsed_time(n1e) / 1e3 / 5
+    base.fused = True
+
+    t = torch.tensor([sec, e2e_sec, fsec, nccl_sec], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    sec, e2e_sec, fsec, nccl_sec = (float(v) for v in t)
+    if rank == 0:
+        peak, peak_src = _peaks()
+        achieved = alg / fsec / 1e9
+        step_bytes = base.linear_weight_bytes() + (depth + 1) * draft.linear_weight_bytes()
+        mt = (verify + 1 + 7) // 8
+        line = {
+            "metric": "accepted tokens/s (one request stream, tensor-parallel target)", "value": produced / sec,
+            "unit": UNIT, "n_gpus": world, "steps": K, "warmup": warmup, "ms_per_step": 1e3 * sec / K,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic (random-init weights drawn at shard shapes from one seed on every rank)",
+            "config": {"workload": f"spec-decode {tname}-shape target cut over {world} GPUs + replicated {dname}-shape "
+                                   f"draft, prompt {prompt_len}, depth {depth}, verify {verify}, greedy",
+                       "parallelism": f"tp{world} target (all-reduce inside the persistent kernel over peer memory), "
+                                      "replicated draft and tree logic",
+                       "l2": "inputs larger than L2 (weights streamed every step)", "mean_accept_length": mean_accept,
+                       "weight_bytes_per_step_per_gpu": step_bytes,
+                       "step_weight_stream_frac_of_peak": step_bytes / (sec / K) / 1e9 / peak,
+                       "target_pass_ms": {"persistent_kernel_peer_memory_allreduce": 1e3 * fsec,
+                                          "per_op_kernels_nccl_allreduce_eager": 1e3 * nccl_sec}},
+            "clocks": clocks,
+            "e2e": {"value": res["produced"] / e2e_sec, "unit": UNIT,
+                    "h2d_bytes_per_step": res["h2d_bytes"] / e2e_steps, "d2h_bytes_per_step": res["d2h_bytes"] / e2e_steps,
+                    "region": "SpecDecoder.generate on every rank: pinned-host prompt copy, prompt ingestion, decode loop "
+                              "with a pinned read-back of the counters every step, token read-back"},
+            "gpu_launches": dec.kernel_launches_per_step * K,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src,
+                         "kernel": f"forward_kernel<{mt},{tshape.head_dim}>: one target pass of {verify + 1} rows over a "
+                                   f"{prefix_now}-row cache on one shard of {world}, exchanges with the peers included",
+                         "algorithmic_bytes_per_launch": alg, "us_per_launch": 1e6 * fsec},
+            "cpu_baseline": None,
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    base.tp.close_exchange()
+    dist.destroy_process_group()
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
@@ -296,6 +423,9 @@ def main():
     ap.add_argument("--roofline-only", action="store_true",
                     help="only the target model's forward kernel at 16 rows (small profiling case with --layers)")
     ap.add_argument("--layers", type=int, default=0, help="with --roofline-only: number of decoder layers (0 = all 28)")
+    ap.add_argument("--workload", default="streams", choices=["streams"] + sorted(TP_WORKLOADS),
+                    help="streams: one independent request stream per GPU (the default, what --gpus N scales); "
+                         "tp70b / tp7b: one stream with the target cut across all ranks (needs 2+ ranks)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -310,6 +440,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    if args.workload != "streams":
+        run_tensor_parallel(args, rank, world, local_rank)
+        return
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:

@@ -245,16 +245,18 @@ typedef struct b200_forward_desc {
      * embedding and the norms are whole.  tp_peers[r] is rank r's exchange buffer
      * (b200_forward_tp_buffer_bytes(hidden) bytes, zero before the first launch, 16-byte aligned) as
      * mapped into this process: peer-accessible device memory, e.g. a CUDA IPC or symmetric-memory
-     * mapping.  o_proj and down_proj leave fp32 partial products in the GPU's own buffer; each GPU then
-     * raises a flag word in every peer's buffer, waits (bounded; error code 12 in the workspace's error
-     * word on timeout) for the peers' flags, and adds all partial products in rank order with plain
-     * loads over NVLink, so every GPU holds bit-identical hidden states.  tp_seq = exchanges done by
-     * all earlier launches on these buffers (2 * n_layers per launch, the same on every rank): flags
-     * only grow.  Every rank must launch the same sequence of passes; the kernels of one pass run
-     * concurrently, one per GPU, never two ranks on one GPU. */
+     * mapping.  o_proj and down_proj leave fp32 partial products in the GPU's own buffer; every CTA then
+     * adds one to an arrival counter in every GPU's buffer (remote atomics) and waits (bounded; error
+     * code 12 in the workspace's error word on timeout) until its own GPU's counter shows all CTAs of all
+     * GPUs; then every GPU adds all partial products in rank order with plain loads over NVLink, so
+     * every GPU holds bit-identical hidden states.  The running count of
+     * exchanges lives in the buffer (flags only grow), so a launch can be replayed from a CUDA graph.
+     * Every rank must launch the same sequence of passes; the kernels of one pass run concurrently,
+     * one per GPU, never two ranks on one GPU.  After an error code 12 the buffers of all ranks must
+     * be zeroed (with no launch in flight anywhere) before the next pass. */
     int tp_world, tp_rank;
-    unsigned tp_seq;
     int head_rows;
+    int reserved;
     void* tp_peers[8];
 } b200_forward_desc;
 
@@ -270,6 +272,18 @@ int b200_tp_exchange_alloc(size_t bytes, void** ptr, unsigned char* handle);
 int b200_tp_exchange_open(const unsigned char* handle, void** ptr);
 int b200_tp_exchange_close(void* ptr);
 int b200_tp_exchange_free(void* ptr);
+/* Error word of the argmax combine in this GPU's own buffer: 0, or 1 after a combine that gave up waiting
+ * for a peer (synchronous 4-byte copy; negative = B200_E*). */
+int b200_tp_exchange_error(const void* own_buffer);
+
+/* Vocabulary-parallel greedy argmax (the per-shard halves of evaluate_posterior_greedy's argmax,
+ * mlx_eagle.py:311-313): best_key[R] holds this shard's keys from b200_logits_argmax (shard-local
+ * indices); index_offset = first vocabulary row of the shard.  One small kernel per GPU shifts the keys
+ * to global indices, publishes them in its exchange buffer, raises its flag at every peer, waits (bounded)
+ * for the peers' flags and leaves the maximum over all shards in best_key on every GPU.  No host
+ * synchronisation, safe inside a CUDA graph; R <= 32. */
+int b200_tp_argmax_combine(unsigned long long* best_key, int R, unsigned int index_offset, int tp_world,
+                           int tp_rank, void* const* tp_peers, void* stream);
 int b200_forward(const b200_forward_desc* desc, void* stream);
 
 /* ------------------------------------------------------------------------------------------

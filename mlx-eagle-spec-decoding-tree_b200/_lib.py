@@ -104,6 +104,10 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_tp_exchange_close.argtypes = [vp]
     l.b200_tp_exchange_free.restype = i32
     l.b200_tp_exchange_free.argtypes = [vp]
+    l.b200_tp_exchange_error.restype = i32
+    l.b200_tp_exchange_error.argtypes = [vp]
+    l.b200_tp_argmax_combine.restype = i32
+    l.b200_tp_argmax_combine.argtypes = [vp, i32, ctypes.c_uint, i32, i32, ctypes.POINTER(ctypes.c_void_p), vp]
     l.b200_forward.restype = i32
     l.b200_forward.argtypes = [ctypes.POINTER(ForwardDesc), vp]
     l.b200_residual_add_f32.restype = i32
@@ -127,7 +131,7 @@ class ForwardDesc(ctypes.Structure):
             "workspace")]
         + [("workspace_bytes", ctypes.c_size_t), ("timeline", ctypes.c_void_p), ("timeline_pitch", ctypes.c_int),
            ("phase_mask", ctypes.c_int), ("tp_world", ctypes.c_int), ("tp_rank", ctypes.c_int),
-           ("tp_seq", ctypes.c_uint), ("head_rows", ctypes.c_int), ("tp_peers", ctypes.c_void_p * 8)])
+           ("head_rows", ctypes.c_int), ("reserved", ctypes.c_int), ("tp_peers", ctypes.c_void_p * 8)])
 
 
 def check(rc: int, what: str) -> None:

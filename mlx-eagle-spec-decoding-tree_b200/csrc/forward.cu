@@ -32,6 +32,7 @@
 #include <cuda.h>
 
 #include "pipeline.cuh"
+#include "tp_layout.cuh"
 #include "qmm_common.cuh"
 
 namespace b200 {
@@ -64,9 +65,7 @@ constexpr int kSyncBar = 0, kSyncExit = 1, kSyncErr = 2;
 
 enum { EPI_QKV = 0, EPI_SILU = 1, EPI_RESID = 2, EPI_HEAD = 3, EPI_TP = 4 };
 enum { K_EMBED = 0, K_A = 1, K_B1 = 2, K_B2 = 3, K_C = 4, K_D = 5, K_E = 6, K_HEAD = 7, K_R = 8 };
-constexpr int kMaxTp = 8;                     // GPUs of one tensor-parallel group
 constexpr uint32_t kTpWaitLimit = 1u << 24;   // polls of a peer's flag (a microsecond or so each) before giving up
-constexpr int kTpFlagBytes = 1024;            // head of every GPU's exchange buffer: one 64-byte flag line per peer
 enum { PLAN_A = 0, PLAN_C = 1, PLAN_D = 2, PLAN_E = 3, PLAN_HEAD = 4 };
 
 struct LayerPtrs {                 // one entry per layer, in device memory (8 pointers = 64 bytes)
@@ -117,8 +116,8 @@ struct FwdParams {
     // partial products into this GPU's exchange buffer; after a handshake through flag words in the peers'
     // buffers every GPU adds the partial products of all ranks (plain loads over NVLink, rank order) and the
     // residual.  tp_peers[r] = rank r's exchange buffer as mapped into this process.
+    // The count of exchanges done by earlier launches lives in the buffer (flags only ever grow).
     int tp_world, tp_rank;
-    unsigned tp_seq;               // exchanges done by earlier launches (flags only ever grow)
     unsigned char* tp_peers[kMaxTp];
     int head_rows;                 // rows of the vocabulary projection held here (a vocabulary shard under TP)
     int attn_fused_max;            // single-phase attention while the cache spans at most this many key blocks
@@ -168,8 +167,10 @@ struct Ctx {
     uint32_t apos;      // attention key blocks produced / assigned so far
     uint32_t ause;      // key blocks this consumer warp has taken from its slot so far
     int ans;            // number of key-block slots (attention geometry)
-    uint32_t epoch;     // grid barriers before the current phase
+    uint32_t epoch;     // barriers (device-wide or all-GPU) before the current phase
+    uint32_t lbar;      // of those, the device-wide ones (the local counter's target is lbar * CTAs)
     uint32_t tpx;       // tensor-parallel exchanges done in this launch
+    uint32_t tp_seq0;   // ... and by all earlier launches
     int lane, warp;
 };
 
@@ -219,6 +220,7 @@ __device__ __forceinline__ void raise_error(const FwdParams& p, Ctx& c, int code
 // leave the kernel resets it.
 __device__ void grid_barrier(const FwdParams& p, Ctx& c) {
     c.epoch++;
+    c.lbar++;
     consumer_sync(kNCons);
     if (threadIdx.x == 0 && !*c.abort_flag) {
         long long* tl = nullptr;
@@ -226,11 +228,10 @@ __device__ void grid_barrier(const FwdParams& p, Ctx& c) {
             tl = p.timeline + ((size_t)blockIdx.x * p.timeline_pitch + (c.epoch - 1)) * 8;
             tl[0] = global_ns();
         }
-        if (p.tp_world > 1) __threadfence_system();    // partial products are read by other GPUs
-        else __threadfence();          // cumulative: covers the CTA's writes ordered before the bar.sync
+        __threadfence();               // cumulative: covers the CTA's writes ordered before the bar.sync
         fence_proxy_async_all();
         atomicAdd(p.sync + kSyncBar, 1);
-        const int target = (int)(c.epoch * gridDim.x);
+        const int target = (int)(c.lbar * gridDim.x);
         bool ok = false;
         const volatile int* bar = p.sync + kSyncBar;
         for (uint32_t i = 0; i < kGridWaitLimit; i++) {
@@ -291,10 +292,10 @@ __device__ __forceinline__ bool drain_blocks(const FwdParams& p, Ctx& c) {
 // This GPU's buffer of fp32 partial products for the exchange in progress (two buffers, used in turn, so
 // that a GPU that is one exchange ahead never overwrites what a slower peer is still reading).
 __device__ __forceinline__ float* tp_partial_of(const FwdParams& p, int rank, uint32_t x) {
-    return reinterpret_cast<float*>(p.tp_peers[rank] + kTpFlagBytes) + (size_t)((p.tp_seq + x) & 1u) * 32 * p.H;
+    return reinterpret_cast<float*>(p.tp_peers[rank] + kTpHeader) + (size_t)(x & 1u) * 32 * p.H;
 }
 __device__ __forceinline__ float* tp_partial(const FwdParams& p, const Ctx& c) {
-    return tp_partial_of(p, p.tp_rank, c.tpx);
+    return tp_partial_of(p, p.tp_rank, c.tp_seq0 + c.tpx);
 }
 __device__ __forceinline__ float4 ld_sys_f4(const float* q) {
     float4 v;
@@ -303,30 +304,47 @@ __device__ __forceinline__ float4 ld_sys_f4(const float* q) {
     return v;
 }
 
-// The all-reduce of a row-parallel layer, after the local grid barrier that follows the partial products:
-// CTA 0 raises this GPU's flag in every peer's buffer (release at system scope), every CTA waits (bounded) for
-// the flags of all peers in its own GPU's buffer, then all consumer threads add the ranks' partial products in
-// rank order, add the residual and write h, h*w and the sums of squares exactly like the single-GPU epilogue.
-__device__ __forceinline__ void tp_reduce_phase(const FwdParams& p, Ctx& c, const __half* wn) {
-    const unsigned seq = p.tp_seq + c.tpx + 1;
-    if (blockIdx.x == 0 && threadIdx.x < (unsigned)p.tp_world && (int)threadIdx.x != p.tp_rank) {
-        unsigned* flag = reinterpret_cast<unsigned*>(p.tp_peers[threadIdx.x] + p.tp_rank * 64);
-        asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(flag), "r"(seq) : "memory");
-    }
+// Barrier over all CTAs of all GPUs of the group, after a phase that wrote partial products: thread 0 of
+// every CTA makes the CTA's writes visible system-wide, adds one to the arrival counter in every GPU's
+// exchange buffer (its own included) and waits (bounded) until its own GPU's counter shows the arrivals of
+// all CTAs of all GPUs for this exchange.  Counters only grow (compared modulo 2^32).
+__device__ void tp_all_barrier(const FwdParams& p, Ctx& c) {
+    c.epoch++;
+    consumer_sync(kNCons);
     if (threadIdx.x == 0 && !*c.abort_flag) {
-        bool ok = true;
-        for (int r = 0; r < p.tp_world && ok; r++) {
-            if (r == p.tp_rank) continue;
-            const unsigned* flag = reinterpret_cast<const unsigned*>(p.tp_peers[p.tp_rank] + r * 64);
-            ok = false;
-            for (uint32_t i = 0; i < kTpWaitLimit; i++) {
-                unsigned v;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(flag) : "memory");
-                if ((int)(v - seq) >= 0) { ok = true; break; }
-            }
+        long long* tl = nullptr;
+        if (p.timeline != nullptr && (int)c.epoch <= p.timeline_pitch) {
+            tl = p.timeline + ((size_t)blockIdx.x * p.timeline_pitch + (c.epoch - 1)) * 8;
+            tl[0] = global_ns();
+        }
+        __threadfence_system();
+        fence_proxy_async_all();
+        for (int r = 0; r < p.tp_world; r++) {
+            const int q = (p.tp_rank + r) % p.tp_world;          // own counter first
+            unsigned* cnt = reinterpret_cast<unsigned*>(p.tp_peers[q] + kTpFwdArrive);
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(cnt) : "memory");   // ordered by the fence above
+        }
+        const unsigned target = (c.tp_seq0 + c.tpx + 1) * (unsigned)p.tp_world * gridDim.x;
+        const unsigned* mine = reinterpret_cast<const unsigned*>(p.tp_peers[p.tp_rank] + kTpFwdArrive);
+        bool ok = false;
+        for (uint32_t i = 0; i < kTpWaitLimit; i++) {
+            if ((int)(ld_acquire_sys(mine) - target) >= 0) { ok = true; break; }
         }
         if (!ok) raise_error(p, c, 12);
+        __threadfence();
+        *c.s_epoch = c.epoch;
+        if (tl != nullptr) {
+            tl[1] = global_ns();
+            tl[7] = clock64();
+        }
     }
+    consumer_sync(kNCons);
+}
+
+// The all-reduce of a row-parallel layer, after the all-GPU barrier that follows the partial products: all
+// consumer threads add the ranks' partial products in rank order (plain loads, the peers' over NVLink), add
+// the residual and write h, h*w and the sums of squares exactly like the single-GPU epilogue.
+__device__ __forceinline__ void tp_reduce_phase(const FwdParams& p, Ctx& c, const __half* wn) {
     consumer_sync(kNCons);
     if (!*c.abort_flag) {
         const int upt = p.H / 8;                       // 8-column units per token row
@@ -341,7 +359,7 @@ __device__ __forceinline__ void tp_reduce_phase(const FwdParams& p, Ctx& c, cons
 #pragma unroll
                 for (int e = 0; e < 8; e++) a[e] = 0.f;
                 for (int r = 0; r < p.tp_world; r++) {
-                    const float* src = tp_partial_of(p, r, c.tpx) + (size_t)tok * p.H + n0;
+                    const float* src = tp_partial_of(p, r, c.tp_seq0 + c.tpx) + (size_t)tok * p.H + n0;
                     const float4 u0 = ld_sys_f4(src);
                     const float4 u1 = ld_sys_f4(src + 4);
                     a[0] += u0.x; a[1] += u0.y; a[2] += u0.z; a[3] += u0.w;
@@ -1581,7 +1599,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
     c.s_rstd = s_rstd;
     c.pos = 0;
     c.epoch = 0;
+    c.lbar = 0;
     c.tpx = 0;
+    c.tp_seq0 = p.tp_world > 1 ? *reinterpret_cast<const volatile unsigned*>(p.tp_peers[p.tp_rank] + kTpFwdCount) : 0u;
     c.lane = threadIdx.x & 31;
     c.warp = threadIdx.x >> 5;
 
@@ -1676,11 +1696,13 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
                 qmm_consume<MT, false>(p, c, d, epi);
             }
         }
+        const bool exchange = p.tp_world > 1 && (kind == K_C || kind == K_E);
         if (kind != K_HEAD) {
             if (producer) c.epoch++;
+            else if (exchange) tp_all_barrier(p, c);
             else grid_barrier(p, c);
         }
-        if (p.tp_world > 1 && (kind == K_C || kind == K_E)) {
+        if (exchange) {
             // the partial products of all GPUs -> h, h*w, sums of squares (every GPU computes all of it)
             if (producer) {
                 c.epoch++;
@@ -1701,6 +1723,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
         if (old == (int)gridDim.x - 1) {
             p.sync[kSyncBar] = 0;
             p.sync[kSyncExit] = 0;
+            if (p.tp_world > 1)            // every CTA read the old count before its first barrier
+                *reinterpret_cast<volatile unsigned*>(p.tp_peers[p.tp_rank] + kTpFwdCount) = c.tp_seq0 + c.tpx;
         }
     }
 }
@@ -1895,7 +1919,7 @@ using namespace b200;
 
 size_t b200_forward_tp_buffer_bytes(int hidden) {
     if (hidden < 128 || (hidden % 128) != 0) return 0;
-    return (size_t)kTpFlagBytes + (size_t)2 * 32 * hidden * sizeof(float);
+    return (size_t)kTpHeader + (size_t)2 * 32 * hidden * sizeof(float);
 }
 
 size_t b200_forward_workspace_bytes(const b200_forward_desc* d) {
@@ -1953,7 +1977,6 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
     p.head_rows = d->head_rows > 0 ? d->head_rows : d->vocab;
     p.tp_world = d->tp_world > 1 ? d->tp_world : 1;
     p.tp_rank = d->tp_world > 1 ? d->tp_rank : 0;
-    p.tp_seq = d->tp_seq;
     if (p.tp_world > 1) {
         for (int r = 0; r < p.tp_world; r++) {
             if (!d->tp_peers[r]) return B200_EINVAL;

@@ -80,6 +80,8 @@ class SpecDecoder:
         self.kernel_launches_per_step = (
             (depth + 1) * draft_model.launches_per_forward + base_model.launches_per_forward
             + 1 + (depth + 1) * 4 + 1 + 1 + 1 + 1)
+        if base_model.tp is not None:                    # argmax combine over peer memory, or two key shifts around NCCL
+            self.kernel_launches_per_step += 1 if base_model.tp.peers is not None else 2
 
     # ------------------------------------------------------------------ prompt ingestion
     def prefill(self, prompt: torch.Tensor, prefill_step_size: int = 512) -> int:
@@ -152,8 +154,13 @@ class SpecDecoder:
         base = self.base
         ck(L.b200_logits_argmax(p(self.base_logits), self.T + 1, base.vocab_local, p(self.argmax_key), st),
            "b200_logits_argmax")
-        if base.tp is not None:
-            # vocabulary-parallel head: per-node (max, argmax) keys of every shard, combined by a MAX all-reduce
+        if base.tp is not None and base.tp.peers is not None:
+            # vocabulary-parallel head: every shard's per-node (max, argmax) keys, combined over peer memory
+            tp = base.tp
+            ck(L.b200_tp_argmax_combine(p(self.argmax_key), self.T + 1, base.vocab_offset, tp.world, tp.rank,
+                                        tp.peer_array, st), "b200_tp_argmax_combine")
+        elif base.tp is not None:
+            # ... or, without exchange buffers, by a MAX all-reduce through torch.distributed
             ck(L.b200_argmax_key_shift(p(self.argmax_key), self.T + 1, base.vocab_offset, st), "b200_argmax_key_shift")
             base.tp.all_reduce_max(self.argmax_key[: self.T + 1])
             ck(L.b200_argmax_key_shift(p(self.argmax_key), self.T + 1, 0, st), "b200_argmax_key_shift")
@@ -193,8 +200,9 @@ class SpecDecoder:
         v = min(self.base.args.vocab_size, self.draft.args.vocab_size)
         self.prefill(torch.randint(0, v, (8,), generator=g, dtype=torch.int32))
         self.step()
-        if capture and self.base.tp is None:
-            # (a tensor-parallel target all-reduces through torch.distributed: its step is launched eagerly)
+        if capture and (self.base.tp is None or self.base.can_fuse()):
+            # (a tensor-parallel target without exchange buffers all-reduces through torch.distributed: its
+            # step is launched eagerly)
             self.capture()
         torch.cuda.synchronize(self.device)
 

@@ -103,9 +103,9 @@ class TensorParallel:
 
     def __init__(self, rank: int, world: int, group=None):
         self.rank, self.world, self.group = int(rank), int(world), group
-        # Exchange buffers of the persistent kernel's in-kernel all-reduce (one per GPU, mapped into every
-        # process of the group through CUDA IPC) and the number of exchanges launched so far (flags only grow).
-        self.peers, self.seq = None, 0
+        # Exchange buffers of the in-kernel all-reduce and argmax combine: one per GPU, mapped into every
+        # process of the group through CUDA IPC (addresses as seen by this process, by rank).
+        self.peers, self.peer_array = None, None
 
     def all_reduce_sum(self, t: torch.Tensor):
         import torch.distributed as dist
@@ -134,7 +134,15 @@ class TensorParallel:
             _lib.check(lib.b200_tp_exchange_open(hb, ctypes.byref(q)), "b200_tp_exchange_open")
             peers.append(q.value)
         dist.barrier(group=self.group)
-        self.peers, self.seq = peers, 0
+        self.peers = peers
+        self.peer_array = (ctypes.c_void_p * 8)(*peers)
+
+    def check_error(self):
+        """Raise if an argmax combine gave up waiting for a peer (synchronises)."""
+        if self.peers is not None:
+            rc = _lib.lib().b200_tp_exchange_error(ctypes.c_void_p(self.peers[self.rank]))
+            if rc != 0:
+                raise _lib.B200Error(f"tensor-parallel exchange: a bounded wait for a peer gave up ({rc})")
 
     def close_exchange(self):
         """Unmap the peers' buffers and free this GPU's (collective: no rank may still be inside a pass)."""
@@ -149,7 +157,7 @@ class TensorParallel:
                 lib.b200_tp_exchange_close(ctypes.c_void_p(q))
         dist.barrier(group=self.group)
         lib.b200_tp_exchange_free(ctypes.c_void_p(self.peers[self.rank]))
-        self.peers = None
+        self.peers = self.peer_array = None
 
 
 def _rows(lin: "QLinear", r0: int, r1: int) -> "QLinear":
@@ -267,7 +275,7 @@ class Model:
 
     # ------------------------------------------------------------------ construction
     @staticmethod
-    def random_init(args: ModelArgs, seed: int, device, gen_device=None) -> "Model":
+    def random_init(args: ModelArgs, seed: int, device, gen_device=None, head_rows: Optional[int] = None) -> "Model":
         """Seeded N(0, 0.02) weights quantised to 4 bit / group 64 (stands in for a checkpoint).
 
         ``gen_device`` is where the random numbers are drawn ("cpu" gives the same weights on any
@@ -294,8 +302,33 @@ class Model:
                 qkv=qlin(nq + 2 * nkv, H, bias=args.attention_bias), o=qlin(H, nq), gate=qlin(I, H), up=qlin(I, H),
                 down=qlin(H, I), input_norm=norm_w(), post_norm=norm_w()))
         embed = qlin(args.vocab_size, H)
-        lm_head = None if args.tie_word_embeddings else qlin(args.vocab_size, H)
+        if head_rows is not None:                       # a vocabulary shard of the head (see random_init_shard)
+            lm_head = _rows(embed, 0, head_rows) if args.tie_word_embeddings else qlin(head_rows, H)
+        else:
+            lm_head = None if args.tie_word_embeddings else qlin(args.vocab_size, H)
         return Model(args, layers, embed, norm_w(), lm_head, device)
+
+    @staticmethod
+    def random_init_shard(args: ModelArgs, seed: int, device, rank: int, world: int, group=None) -> "Model":
+        """A tensor-parallel shard drawn directly at shard shapes, for models too large to build whole on one
+        GPU.  Every rank must pass the same seed: embeddings and norms then agree across ranks (which the
+        replicated hidden state needs); the shards' own weights are the same random numbers on every rank,
+        which changes nothing about the work done.  Not a shard of ``random_init(args, seed)``."""
+        import dataclasses
+        a = args
+        hd = a.head_dim
+        if any(v % world for v in (a.num_attention_heads, a.num_key_value_heads, a.vocab_size)) or \
+                (a.intermediate_size // world) % 128 or (a.num_attention_heads * hd // world) % 128 or \
+                (a.vocab_size // world) % 8:
+            raise _lib.B200Error("heads, kv heads, MLP width (in multiples of 128) and vocabulary must divide by the TP degree")
+        largs = dataclasses.replace(a, num_attention_heads=a.num_attention_heads // world,
+                                    num_key_value_heads=a.num_key_value_heads // world,
+                                    intermediate_size=a.intermediate_size // world)
+        m = Model.random_init(largs, seed, device, head_rows=a.vocab_size // world)
+        m.tp = TensorParallel(rank, world, group)
+        m.vocab_offset = rank * (a.vocab_size // world)
+        m.part32 = torch.zeros(MAX_ROWS, a.hidden_size, dtype=torch.float32, device=m.device)
+        return m
 
     def shard(self, rank: int, world: int, group=None) -> "Model":
         """This model's shard ``rank`` of ``world`` for tensor-parallel execution (call before ``relayout``).
@@ -462,8 +495,7 @@ class Model:
         d.phase_mask = self.phase_mask
         d.attn_split_blocks = self.attn_split_blocks
         if self.tp is not None:
-            d.tp_world, d.tp_rank, d.tp_seq, d.head_rows = self.tp.world, self.tp.rank, self.tp.seq & 0xffffffff, \
-                self.vocab_local
+            d.tp_world, d.tp_rank, d.head_rows = self.tp.world, self.tp.rank, self.vocab_local
             for r, q in enumerate(self.tp.peers):
                 d.tp_peers[r] = q
         if self.timeline is not None:
@@ -491,6 +523,8 @@ class Model:
         if code != 0:
             self._fwd_ws[:4352].zero_()
             raise _lib.B200Error(f"b200_forward: a bounded wait gave up inside the kernel (code {code})")
+        if self.tp is not None:
+            self.tp.check_error()
 
     def _row_parallel(self, x, lin: QLinear, M: int):
         """h += x . W^T for o_proj / down_proj.  Under tensor parallelism W holds this GPU's K shard: the fp32
@@ -532,8 +566,6 @@ class Model:
             desc = self._fused_desc(M, cache, write_off, tail, fwd, rows, row_index)
             _lib.check(_lib.lib().b200_forward(ctypes.byref(desc), _lib.stream_ptr(self.device)), "b200_forward")
             vl = self.vocab_local
-            if self.tp is not None:
-                self.tp.seq += 2 * self.args.num_hidden_layers      # one exchange after o_proj, one after down_proj
             return self.logits[:rows] if vl == self.args.vocab_size else self.logits.view(-1)[: rows * vl].view(rows, vl)
         a, L, lib = self.args, _lib.lib(), _lib.lib()
         st, p = _lib.stream_ptr(self.device), _lib.ptr

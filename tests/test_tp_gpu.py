@@ -48,7 +48,8 @@ def _rank(rank, world, port, out):
     shard.check_fused_error()
     err = float(((fused - per_op).abs() - 2.0 ** -6 * per_op.abs()).max())      # <= 2e-2 wanted
     if rank == 0:
-        out.put((res["tokens"], res["accept_lengths"], res2["tokens"], res2["accept_lengths"], err))
+        out.put((res["tokens"], res["accept_lengths"], res2["tokens"], res2["accept_lengths"], err,
+                 res2["decoder"].graph is not None))
     dist.barrier()
     shard.tp.close_exchange()
     dist.destroy_process_group()
@@ -67,7 +68,7 @@ def test_two_gpu_tensor_parallel_target_matches_golden_generation(cuda):
     for p in procs:
         p.start()
     try:
-        tokens, accept, tokens2, accept2, err = out.get(timeout=200)
+        tokens, accept, tokens2, accept2, err, graphed = out.get(timeout=200)
         for p in procs:
             p.join(timeout=60)
             assert p.exitcode == 0
@@ -80,3 +81,4 @@ def test_two_gpu_tensor_parallel_target_matches_golden_generation(cuda):
     assert err <= 2e-2                       # |fused - per-op| <= 2^-6 |per-op| + 2e-2 on every logit
     assert tokens2 == g["random_draft_d3_t15"]["tokens"]
     assert accept2 == g["random_draft_d3_t15"]["accept_lengths"]
+    assert graphed                           # with the exchange inside the kernels the step replays as one CUDA graph
