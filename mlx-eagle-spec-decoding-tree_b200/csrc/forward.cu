@@ -65,7 +65,7 @@ constexpr int kSyncBar = 0, kSyncExit = 1, kSyncErr = 2;
 
 enum { EPI_QKV = 0, EPI_SILU = 1, EPI_RESID = 2, EPI_HEAD = 3, EPI_TP = 4 };
 enum { K_EMBED = 0, K_A = 1, K_B1 = 2, K_B2 = 3, K_C = 4, K_D = 5, K_E = 6, K_HEAD = 7, K_R = 8 };
-constexpr uint32_t kTpWaitLimit = 1u << 24;   // polls of a peer's flag (a microsecond or so each) before giving up
+constexpr uint32_t kTpWaitLimit = 1u << 22;   // polls of a peer's flag (a microsecond or so each) before giving up
 enum { PLAN_A = 0, PLAN_C = 1, PLAN_D = 2, PLAN_E = 3, PLAN_HEAD = 4 };
 
 struct LayerPtrs {                 // one entry per layer, in device memory (8 pointers = 64 bytes)
@@ -344,46 +344,63 @@ __device__ void tp_all_barrier(const FwdParams& p, Ctx& c) {
 // The all-reduce of a row-parallel layer, after the all-GPU barrier that follows the partial products: all
 // consumer threads add the ranks' partial products in rank order (plain loads, the peers' over NVLink), add
 // the residual and write h, h*w and the sums of squares exactly like the single-GPU epilogue.
-__device__ __forceinline__ void tp_reduce_phase(const FwdParams& p, Ctx& c, const __half* wn) {
-    consumer_sync(kNCons);
-    if (!*c.abort_flag) {
-        const int upt = p.H / 8;                       // 8-column units per token row
-        const int units = p.M * upt;
-        const int units32 = (units + 31) & ~31;
-        for (int i = blockIdx.x * kNCons + threadIdx.x; i < units32; i += gridDim.x * kNCons) {
-            const int tok = i / upt, n0 = (i - tok * upt) * 8;
-            const bool valid = i < units;
-            float ss = 0.f;
-            if (valid) {
-                float a[8];
+// (Not inlined: its registers, one pair of loads per rank, stay out of the matmul phases' allocation.)
+__device__ __noinline__ void tp_reduce_rows(const FwdParams& p, const __half* wn, uint32_t xchg) {
+    const int upt = p.H / 4;                           // 4-column units per token row: a warp reads 512 contiguous bytes
+    const int units = p.M * upt;
+    const int units32 = (units + 31) & ~31;
+    const int stride = gridDim.x * kNCons;
+    // two units per thread and trip, all ranks' loads of both in flight together (a peer's take microseconds)
+    for (int i0 = blockIdx.x * kNCons + threadIdx.x; i0 < units32; i0 += 2 * stride) {
+        float4 u[2][kMaxTp];
+        int tok[2], n0[2];
+        bool valid[2];
 #pragma unroll
-                for (int e = 0; e < 8; e++) a[e] = 0.f;
-                for (int r = 0; r < p.tp_world; r++) {
-                    const float* src = tp_partial_of(p, r, c.tp_seq0 + c.tpx) + (size_t)tok * p.H + n0;
-                    const float4 u0 = ld_sys_f4(src);
-                    const float4 u1 = ld_sys_f4(src + 4);
-                    a[0] += u0.x; a[1] += u0.y; a[2] += u0.z; a[3] += u0.w;
-                    a[4] += u1.x; a[5] += u1.y; a[6] += u1.z; a[7] += u1.w;
+        for (int j = 0; j < 2; j++) {
+            const int i = i0 + j * stride;
+            valid[j] = i < units;
+            tok[j] = valid[j] ? i / upt : 0;
+            n0[j] = valid[j] ? (i - tok[j] * upt) * 4 : 0;
+#pragma unroll
+            for (int r = 0; r < kMaxTp; r++)
+                if (r < p.tp_world && valid[j])
+                    u[j][r] = ld_sys_f4(tp_partial_of(p, r, xchg) + (size_t)tok[j] * p.H + n0[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            if (i0 + j * stride >= units32) break;              // warp-uniform
+            float ss = 0.f;
+            if (valid[j]) {
+                const uint2 rv = __ldcg(reinterpret_cast<const uint2*>(p.h + (size_t)tok[j] * p.H + n0[j]));
+                const uint2 wv = *reinterpret_cast<const uint2*>(wn + n0[j]);
+                float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int r = 0; r < kMaxTp; r++) {             // rank order: every GPU rounds identically
+                    if (r < p.tp_world) { a[0] += u[j][r].x; a[1] += u[j][r].y; a[2] += u[j][r].z; a[3] += u[j][r].w; }
                 }
-                const uint4 rv = __ldcg(reinterpret_cast<const uint4*>(p.h + (size_t)tok * p.H + n0));
-                const uint4 wv = *reinterpret_cast<const uint4*>(wn + n0);
                 const __half* rh = reinterpret_cast<const __half*>(&rv);
                 const __half* wh = reinterpret_cast<const __half*>(&wv);
-                __align__(16) __half out[8], hw[8];
+                __align__(8) __half out[4], hw[4];
 #pragma unroll
-                for (int e = 0; e < 8; e++) {
+                for (int e = 0; e < 4; e++) {
                     out[e] = __hadd(rh[e], __float2half_rn(a[e]));
                     const float fv = __half2float(out[e]);
                     ss += fv * fv;
                     hw[e] = __hmul(out[e], wh[e]);
                 }
-                *reinterpret_cast<uint4*>(p.h + (size_t)tok * p.H + n0) = *reinterpret_cast<const uint4*>(out);
-                *reinterpret_cast<uint4*>(p.hw + xt_index(tok, n0, p.mp)) = *reinterpret_cast<const uint4*>(hw);
+                *reinterpret_cast<uint2*>(p.h + (size_t)tok[j] * p.H + n0[j]) = *reinterpret_cast<const uint2*>(out);
+                *reinterpret_cast<uint2*>(p.hw + xt_index(tok[j], n0[j], p.mp)) = *reinterpret_cast<const uint2*>(hw);
             }
-            ss += __shfl_xor_sync(0xffffffffu, ss, 1);          // the two 8-column halves of a 16-column part
-            if (valid && (threadIdx.x & 1) == 0) p.ssq[(n0 >> 4) * kSsqPitch + tok] = ss;
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);          // the four 4-column quarters of a 16-column part
+            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            if (valid[j] && (threadIdx.x & 3) == 0) p.ssq[(n0[j] >> 4) * kSsqPitch + tok[j]] = ss;
         }
     }
+}
+
+__device__ __forceinline__ void tp_reduce_phase(const FwdParams& p, Ctx& c, const __half* wn) {
+    consumer_sync(kNCons);
+    if (!*c.abort_flag) tp_reduce_rows(p, wn, c.tp_seq0 + c.tpx);
     c.tpx++;
 }
 
@@ -529,7 +546,7 @@ __device__ __forceinline__ void compute_rstd(const FwdParams& p, Ctx& c, int row
     consumer_sync(kNCons);
 }
 
-template <int MT, bool DUAL>
+template <int MT, bool DUAL, bool TP>
 __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QDesc& d, const int EPI) {
     using G = Geo<MT>;
     constexpr int S = DUAL ? 2 : 1;
@@ -548,7 +565,7 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
     const int rec_cstride = (TPI >= 4) ? 4 * kRec : chunk_bytes;
     const int nchunks_total = d.K / kChunkK;
     const int nitems = d.pl.row_items * d.pl.splits;
-    const bool need_rstd = (EPI != EPI_RESID && EPI != EPI_TP);
+    const bool need_rstd = (EPI != EPI_RESID && !(TP && EPI == EPI_TP));
     bool rstd_done = !need_rstd;
     stamp(p, c, 2);
 
@@ -708,7 +725,7 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
                         }
                     }
                     __align__(16) __half out[8];
-                    if (EPI == EPI_TP) {
+                    if (TP && EPI == EPI_TP) {
                         if (valid) {
                             float* dst = tp_partial(p, c) + (size_t)tok * d.N + n0;
                             *reinterpret_cast<float4*>(dst) = make_float4(a0[0], a0[1], a0[2], a0[3]);
@@ -761,7 +778,7 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
         } else if (leader) {
             // ---- direct epilogue from the registers of the tile's first warp
             const int nbase = tile_global * 16 + g;
-            if (EPI == EPI_TP) {
+            if (TP && EPI == EPI_TP) {
                 float* dst = tp_partial(p, c);
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++) {
@@ -1569,13 +1586,14 @@ __device__ __forceinline__ void attn_merge(const FwdParams& p, Ctx& c, const ADe
 }
 
 // ================================================================================ the kernel
-template <int MT, int HD>
+template <int MT, int HD, bool TP>
 __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_constant__ FwdParams p) {
     using G = Geo<MT>;
     extern __shared__ __align__(1024) unsigned char smem[];      // swizzled TMA boxes want 1024-byte aligned stages
     __shared__ int s_abort, s_is_last;
     __shared__ uint32_t s_epoch;
     __shared__ float s_rstd[32];
+
     Ctx c;
     c.ring = smem;
     c.full = reinterpret_cast<uint64_t*>(smem + G::NST * G::STAGE);
@@ -1597,11 +1615,12 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
     c.s_epoch = &s_epoch;
     c.is_last = &s_is_last;
     c.s_rstd = s_rstd;
+
     c.pos = 0;
     c.epoch = 0;
     c.lbar = 0;
     c.tpx = 0;
-    c.tp_seq0 = p.tp_world > 1 ? *reinterpret_cast<const volatile unsigned*>(p.tp_peers[p.tp_rank] + kTpFwdCount) : 0u;
+    c.tp_seq0 = TP ? *reinterpret_cast<const volatile unsigned*>(p.tp_peers[p.tp_rank] + kTpFwdCount) : 0u;
     c.lane = threadIdx.x & 31;
     c.warp = threadIdx.x >> 5;
 
@@ -1668,7 +1687,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             d.row_lo = 0; d.row_cnt = p.M;
             d.y_tiled = false;
             d.w1 = nullptr; d.bias = nullptr; d.wn = nullptr;
-            int epi = p.tp_world > 1 ? EPI_TP : EPI_RESID;
+            int epi = TP ? EPI_TP : EPI_RESID;
             if (kind == K_A) {
                 d.x = p.hw; d.w0 = lp.qkv_w; d.bias = lp.qkv_bias; d.y = p.qkv;
                 d.N = p.NQKV; d.K = p.H; d.pl = p.plan[PLAN_A]; epi = EPI_QKV;
@@ -1691,12 +1710,12 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             if (producer) {
                 qmm_produce<MT>(p, c, d, c.epoch, kind == K_D);
             } else if (kind == K_D) {
-                qmm_consume<MT, true>(p, c, d, EPI_SILU);
+                qmm_consume<MT, true, false>(p, c, d, EPI_SILU);
             } else {
-                qmm_consume<MT, false>(p, c, d, epi);
+                qmm_consume<MT, false, TP>(p, c, d, epi);
             }
         }
-        const bool exchange = p.tp_world > 1 && (kind == K_C || kind == K_E);
+        const bool exchange = TP && (kind == K_C || kind == K_E);
         if (kind != K_HEAD) {
             if (producer) c.epoch++;
             else if (exchange) tp_all_barrier(p, c);
@@ -1723,7 +1742,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
         if (old == (int)gridDim.x - 1) {
             p.sync[kSyncBar] = 0;
             p.sync[kSyncExit] = 0;
-            if (p.tp_world > 1)            // every CTA read the old count before its first barrier
+            if (TP)                        // every CTA read the old count before its first barrier
                 *reinterpret_cast<volatile unsigned*>(p.tp_peers[p.tp_rank] + kTpFwdCount) = c.tp_seq0 + c.tpx;
         }
     }
@@ -1882,9 +1901,9 @@ int make_kv_map(CUtensorMap* map, void* cache, int layers, int hkv, int cap, int
     return B200_OK;
 }
 
-template <int MT, int HD>
+template <int MT, int HD, bool TP>
 int launch_forward(const FwdParams& p, cudaStream_t stream) {
-    auto kern = forward_kernel<MT, HD>;
+    auto kern = forward_kernel<MT, HD, TP>;
     bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<MT>::SMEM) != cudaSuccess)
@@ -1907,7 +1926,9 @@ int launch_forward(const FwdParams& p, cudaStream_t stream) {
 
 template <int MT>
 int launch_forward_hd(const FwdParams& p, cudaStream_t stream) {
-    return p.HD == 128 ? launch_forward<MT, 128>(p, stream) : launch_forward<MT, 64>(p, stream);
+    if (p.tp_world > 1)         // a shard: the variant with the exchange phases
+        return p.HD == 128 ? launch_forward<MT, 128, true>(p, stream) : launch_forward<MT, 64, true>(p, stream);
+    return p.HD == 128 ? launch_forward<MT, 128, false>(p, stream) : launch_forward<MT, 64, false>(p, stream);
 }
 
 }  // namespace

@@ -12,7 +12,7 @@
 namespace b200 {
 namespace {
 
-constexpr unsigned kCombineWaitLimit = 1u << 24;     // polls of one flag before giving up
+constexpr unsigned kCombineWaitLimit = 1u << 22;     // polls of one flag before giving up
 
 __global__ void __launch_bounds__(32) tp_argmax_combine_kernel(unsigned long long* __restrict__ best_key, int R,
                                                                unsigned index_offset, TpPeers peers, int world, int rank) {
