@@ -124,6 +124,16 @@ size_t b200_qmm_tiled_workspace_bytes(int M, int N, int K);
 int b200_qmm_tiled(const void* x, const void* wt, const void* wt2, const void* bias, const void* extra, void* y,
                    int M, int N, int K, int epilogue, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same product (plain epilogue: y = fp16(acc) [+ bias, in fp16]) on the tcgen05 tensor cores: the
+ * dequantised fp16 weights (exact q*s+b, rounded once) go through shared memory as 128-row tiles, one thread per
+ * CTA issues tcgen05.mma with the accumulator in tensor memory.  Same streaming weight layout; M <= 32,
+ * N % 128 == 0, K % 128 == 0.  workspace: b200_qmm_umma_workspace_bytes bytes (the activations re-laid for the
+ * tensor cores + an error word, int 0 of the workspace, non-zero if a bounded wait gave up; zero it before
+ * the first use).  Replaces qmm_kernel.py:79-124 like b200_qmm. */
+size_t b200_qmm_umma_workspace_bytes(int M, int K);
+int b200_qmm_umma(const void* x, const void* w_tiled, const void* bias, void* y, int M, int N, int K,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Per-token model kernels (one decoder layer = rms_norm, qmm(+bias), rope_kv_append,
  * tree_attention, qmm(residual), rms_norm, qmm(silu-mul), qmm(residual)).

@@ -64,6 +64,10 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_qmm_tiled_workspace_bytes.argtypes = [i32, i32, i32]
     l.b200_qmm_tiled.restype = i32
     l.b200_qmm_tiled.argtypes = [vp] * 6 + [i32] * 4 + [vp, sz, vp]
+    l.b200_qmm_umma_workspace_bytes.restype = sz
+    l.b200_qmm_umma_workspace_bytes.argtypes = [i32, i32]
+    l.b200_qmm_umma.restype = i32
+    l.b200_qmm_umma.argtypes = [vp] * 4 + [i32] * 3 + [vp, sz, vp]
     l.b200_embed_gather.restype = i32
     l.b200_embed_gather.argtypes = [vp] * 5 + [i32] * 3 + [vp]
     l.b200_rms_norm.restype = i32

@@ -1,0 +1,344 @@
+// 4-bit affine quantised matmul for <= 32 token rows on the fifth-generation tensor cores (tcgen05, TMEM).
+//
+//   y[M][N] = x[M][K] . dequant(W)[N][K]^T     (+ bias), fp16 in, fp32 accumulate, fp16 out
+//
+// W is in the streaming layout of b200_qmm_relayout (records of 16 rows x 128 k, 1152 bytes, ordered
+// [64-row block][k chunk][4 records]).  One CTA owns items of 128 weight rows (the M of one tcgen05.mma):
+//
+//   producer warp   bulk-copies, per k chunk, the two 4608-byte record runs of the item and the chunk's
+//                   activations into a ring of packed stages;
+//   8 dequant warps each expands its record (exact q*s+b, rounded once to fp16, like every other kernel of
+//                   this library) into a 128 x 128 fp16 tile in shared memory, in the canonical K-major layout
+//                   of the tensor cores without swizzle (core matrix = 8 rows x 16 bytes, contiguous): a lane's
+//                   8 dequantised halves are exactly one core-matrix row, a warp's store covers 512 contiguous
+//                   bytes; they also move the chunk's activations next to the tile;
+//   MMA warp        one thread issues 8 tcgen05.mma (128 x N x 16, N = 16 or 32 tokens) per chunk into a TMEM
+//                   accumulator and commits to the mbarriers that free the tile and publish the accumulator;
+//   epilogue        the dequant warps read the accumulator (tcgen05.ld, one weight row per thread) and store fp16.
+//
+// The activations come in the same canonical layout ([chunk][token group of 8][k group of 8][8 tokens][8 halves],
+// token rows padded with zeros to 16 or 32), written by a small relayout kernel into the caller's workspace.
+// Every wait is bounded; a wait that gives up sets the error word in the workspace and the CTA runs to its end
+// (TMEM is always freed).  No copy uses cluster multicast.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "b200_eagle.h"
+#include "common.cuh"
+#include "pipeline.cuh"
+#include "qmm_common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kRecBytes = 1152;
+constexpr int kRunBytes = 4 * kRecBytes;        // the four records of a 64-row block for one chunk
+constexpr int kItemRows = 128;
+constexpr int kDeqWarps = 8;
+constexpr int kUThreads = (kDeqWarps + 2) * 32;  // + producer warp + MMA warp
+constexpr int kPackedStages = 6;
+constexpr int kTileStages = 3;
+constexpr int kLBO = 128;                        // bytes between core matrices along K
+constexpr int kSBO = (kChunkK / 8) * 128;        // bytes between 8-row groups of a 128-k tile
+constexpr int kTileBytes = kItemRows * kChunkK * 2;   // 32 KB of fp16 weights
+constexpr uint32_t kUmmaWaitPolls = 1u << 20;    // x <= 1 us each
+
+template <int NT>                                // token columns of the MMA: 16 or 32
+struct UGeo {
+    static constexpr int XBYTES = NT * kChunkK * 2;                  // activations of one chunk
+    static constexpr int PSTAGE = 2 * kRunBytes + XBYTES;            // packed stage
+    static constexpr int TSTAGE = kTileBytes + XBYTES;               // fp16 tile + its activations
+    static constexpr int BAR_OFF = kPackedStages * PSTAGE + kTileStages * TSTAGE;
+    static constexpr int SMEM = BAR_OFF + 256 + 1024;                // + barriers, + alignment slack
+};
+
+struct UParams {
+    const unsigned char* w;     // streaming layout
+    const __half* xc;           // activations, canonical layout [chunk][NT/8][16][8][8]
+    const __half* bias;
+    __half* y;                  // [M][N]
+    int* err;
+    int M, N, K;
+};
+
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    // shared-memory matrix descriptor, no swizzle: start >> 4 | LBO >> 4 at bit 16 | SBO >> 4 at bit 32 | version 1 at bit 46
+    return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)(kLBO >> 4) << 16) | ((uint64_t)(kSBO >> 4) << 32) |
+           ((uint64_t)1 << 46);
+}
+
+__device__ __forceinline__ bool uwait(uint32_t bar, uint32_t parity) {
+    return mbar_wait_timed(bar, parity, kUmmaWaitPolls, 1000u);
+}
+
+__global__ void x_canonical_kernel(const __half* __restrict__ x, __half* __restrict__ xc, int M, int K, int NT) {
+    pdl_wait();
+    pdl_launch_dependents();
+    // one 16-byte unit (token, k group of 8) per thread
+    const int units = NT * (K / 8);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < units; i += gridDim.x * blockDim.x) {
+        const int tok = i / (K / 8), kg_all = i - tok * (K / 8);
+        const int c = kg_all >> 4, kg = kg_all & 15;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (tok < M) v = *reinterpret_cast<const uint4*>(x + (size_t)tok * K + kg_all * 8);
+        *reinterpret_cast<uint4*>(xc + ((((size_t)c * (NT / 8) + tok / 8) * 16 + kg) * 8 + (tok & 7)) * 8) = v;
+    }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_constant__ UParams p) {
+    using G = UGeo<NT>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* packed = smem;
+    unsigned char* tiles = smem + kPackedStages * G::PSTAGE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G::BAR_OFF);
+    uint64_t* pfull = bars;                          // packed stage landed            (producer -> dequant warps)
+    uint64_t* pempty = pfull + kPackedStages;        // packed stage read              (8 dequant warps -> producer)
+    uint64_t* tready = pempty + kPackedStages;       // tile written                   (8 dequant warps -> MMA warp)
+    uint64_t* tfree = tready + kTileStages;          // tile's MMAs complete           (tcgen05.commit -> dequant warps)
+    uint64_t* accfull = tfree + kTileStages;         // item's accumulator complete    (tcgen05.commit -> epilogue)
+    uint64_t* accempty = accfull + 2;                // accumulator read               (8 warps -> MMA warp)
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nchunks = p.K / kChunkK;
+    const int nitems = p.N / kItemRows;
+    const size_t block_stride = (size_t)nchunks * kRunBytes;        // bytes of one 64-row block
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < kPackedStages; s++) {
+            mbar_init(smem_u32(pfull + s), 1);
+            mbar_init(smem_u32(pempty + s), kDeqWarps);
+        }
+        for (int s = 0; s < kTileStages; s++) {
+            mbar_init(smem_u32(tready + s), kDeqWarps);
+            mbar_init(smem_u32(tfree + s), 1);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(smem_u32(accfull + s), 1);
+            mbar_init(smem_u32(accempty + s), kDeqWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == kDeqWarps + 1) {                     // the MMA warp owns the tensor memory: 64 columns = two accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 64;\n" ::"r"(smem_u32(&s_tmem)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    volatile int* abort_flag = &s_abort;
+    pdl_wait();
+    pdl_launch_dependents();
+
+    if (warp == kDeqWarps) {
+        // ------------------------------------------------------------------ producer
+        const uint64_t pol = make_evict_first_policy();
+        uint32_t n = 0;
+        for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+            const unsigned char* w0 = p.w + (size_t)(2 * item) * block_stride;
+            for (int c = 0; c < nchunks; c++, n++) {
+                const uint32_t s = n % kPackedStages, use = n / kPackedStages;
+                if (*abort_flag) break;
+                if (use > 0 && !__all_sync(0xffffffffu, uwait(smem_u32(pempty + s), (use - 1) & 1u))) {
+                    if (lane == 0) { *abort_flag = 1; atomicCAS(p.err, 0, 1); }
+                    break;
+                }
+                if (lane == 0) {
+                    const uint32_t bar = smem_u32(pfull + s);
+                    const uint32_t dst = smem_u32(packed + s * G::PSTAGE);
+                    mbar_expect_tx(bar, G::PSTAGE);
+                    bulk_copy_g2s_hint(dst, w0 + (size_t)c * kRunBytes, kRunBytes, bar, pol);
+                    bulk_copy_g2s_hint(dst + kRunBytes, w0 + block_stride + (size_t)c * kRunBytes, kRunBytes, bar, pol);
+                    bulk_copy_g2s(dst + 2 * kRunBytes, p.xc + (size_t)c * NT * kChunkK, G::XBYTES, bar);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == kDeqWarps + 1) {
+        // ------------------------------------------------------------------ MMA issuer (one thread)
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(kItemRows >> 4) << 24);
+            uint32_t n = 0, it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, it++) {
+                const uint32_t ab = it & 1u;
+                if (it >= 2) ok = uwait(smem_u32(accempty + ab), ((it >> 1) - 1) & 1u);     // epilogue of item it-2 done
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                for (int c = 0; c < nchunks && ok; c++, n++) {
+                    const uint32_t ts = n % kTileStages, use = n / kTileStages;
+                    ok = !*abort_flag && uwait(smem_u32(tready + ts), use & 1u);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint32_t a0 = smem_u32(tiles + ts * G::TSTAGE);
+                    const uint32_t b0 = a0 + kTileBytes;
+#pragma unroll
+                    for (int ks = 0; ks < kChunkK / 16; ks++) {
+                        const uint64_t da = umma_desc(a0 + ks * 2 * kLBO);
+                        const uint64_t db = umma_desc(b0 + ks * 2 * kLBO);
+                        const uint32_t accumulate = (c > 0 || ks > 0) ? 1u : 0u;
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem + ab * 32),
+                            "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+                            : "memory");
+                    }
+                    // the tile (and its activations) may be rewritten once these MMAs have read it
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
+                                     smem_u32(tfree + ts))
+                                 : "memory");
+                }
+                if (ok)
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
+                                     smem_u32(accfull + ab))
+                                 : "memory");
+            }
+            if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(p.err, 0, 2); }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ dequant warps + epilogue
+        const int g = lane >> 2, t = lane & 3;
+        uint32_t n = 0, it = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, it++) {
+            for (int c = 0; c < nchunks && ok; c++, n++) {
+                const uint32_t ps = n % kPackedStages, ts = n % kTileStages, tuse = n / kTileStages;
+                ok = !*abort_flag && uwait(smem_u32(pfull + ps), (n / kPackedStages) & 1u);
+                if (ok && tuse > 0) ok = uwait(smem_u32(tfree + ts), (tuse - 1) & 1u);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const unsigned char* stage = packed + ps * G::PSTAGE;
+                unsigned char* tile = tiles + ts * G::TSTAGE;
+                // the chunk's activations move next to the tile (they are read by the MMAs, the packed stage is freed now)
+                for (int i = threadIdx.x; i < G::XBYTES / 16; i += kDeqWarps * 32)
+                    *reinterpret_cast<uint4*>(tile + kTileBytes + i * 16) =
+                        *reinterpret_cast<const uint4*>(stage + 2 * kRunBytes + i * 16);
+                // this warp's record: 64-row block warp / 4, record warp % 4; rows 16 * warp + g and + 8
+                const unsigned char* rec = stage + (warp >> 2) * kRunBytes + (warp & 3) * kRecBytes;
+                const uint4 w0 = *reinterpret_cast<const uint4*>(rec + lane * 16);
+                const uint4 w1 = *reinterpret_cast<const uint4*>(rec + 512 + lane * 16);
+                const uint2 sb0 = *reinterpret_cast<const uint2*>(rec + 1024 + g * 8);
+                const uint2 sb1 = *reinterpret_cast<const uint2*>(rec + 1024 + (8 + g) * 8);
+                unsigned char* dst0 = tile + (2 * warp) * kSBO + g * 16;           // rows 16 * warp + g
+                unsigned char* dst1 = dst0 + kSBO;                                 // rows 16 * warp + 8 + g
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const __half2 p0 = u32_as_h2((j < 2) ? sb0.x : sb0.y);         // {scale, bias} of the k group of 64
+                    const __half2 p1 = u32_as_h2((j < 2) ? sb1.x : sb1.y);
+                    uint32_t d0[4], d1[4];
+                    dequant_pack(comp(w0, j), __low2half2(p0), __high2half2(p0), d0);
+                    dequant_pack(comp(w1, j), __low2half2(p1), __high2half2(p1), d1);
+                    // k group 4 j + t: the lane's 8 halves are one core-matrix row
+                    *reinterpret_cast<uint4*>(dst0 + (4 * j + t) * kLBO) = make_uint4(d0[0], d0[1], d0[2], d0[3]);
+                    *reinterpret_cast<uint4*>(dst1 + (4 * j + t) * kLBO) = make_uint4(d1[0], d1[1], d1[2], d1[3]);
+                }
+                fence_proxy_async();                  // generic-proxy stores -> visible to the tensor cores' reads
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(smem_u32(pempty + ps));
+                    mbar_arrive(smem_u32(tready + ts));
+                }
+            }
+            if (!ok) break;
+            // ---- epilogue: thread = weight row 32 * (warp % 4) + lane of the item, half of the token columns
+            const uint32_t ab = it & 1u;
+            ok = __all_sync(0xffffffffu, !*abort_flag && uwait(smem_u32(accfull + ab), (it >> 1) & 1u));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            constexpr int CH = NT / 2;                // columns per warp: 8 or 16
+            const int col0 = (warp >> 2) * CH;
+            const uint32_t taddr = tmem + ab * 32 + col0 + ((uint32_t)((warp & 3) * 32) << 16);
+            uint32_t r[CH];
+            if constexpr (CH == 8) {
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                             : "r"(taddr)
+                             : "memory");
+            } else {
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                    : "r"(taddr)
+                    : "memory");
+            }
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(accempty + ab));
+            const int row = item * kItemRows + (warp & 3) * 32 + lane;
+            const __half bv = p.bias != nullptr ? p.bias[row] : __ushort_as_half(0);
+#pragma unroll
+            for (int i = 0; i < CH; i++) {
+                const int tok = col0 + i;
+                if (tok < p.M) {
+                    __half o = __float2half_rn(__uint_as_float(r[i]));
+                    if (p.bias != nullptr) o = __hadd(o, bv);
+                    p.y[(size_t)tok * p.N + row] = o;
+                }
+            }
+        }
+        if (!ok && lane == 0 && !*abort_flag) { *abort_flag = 1; atomicCAS(p.err, 0, 3); }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == kDeqWarps + 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 64;\n" ::"r"(tmem) : "memory");
+}
+
+template <int NT>
+int launch_umma(const UParams& p, cudaStream_t stream) {
+    auto kern = qmm_umma_kernel<NT>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, UGeo<NT>::SMEM) != cudaSuccess)
+        return check_launch();
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int nitems = p.N / kItemRows;
+    launch_kernel(kern, dim3(nitems < sms ? nitems : sms), dim3(kUThreads), (size_t)UGeo<NT>::SMEM, stream, p);
+    return check_launch();
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" {
+
+using namespace b200;
+
+size_t b200_qmm_umma_workspace_bytes(int M, int K) {
+    if (M < 1 || M > 32 || K < kChunkK || (K % kChunkK) != 0) return 0;
+    const int nt = M <= 16 ? 16 : 32;
+    return 256 + (size_t)nt * K * sizeof(__half);
+}
+
+int b200_qmm_umma(const void* x, const void* w_tiled, const void* bias, void* y, int M, int N, int K, void* workspace,
+                  size_t workspace_bytes, void* stream) {
+    if (!x || !w_tiled || !y || !workspace || M < 1 || M > 32 || N < kItemRows || K < kChunkK) return B200_EINVAL;
+    if ((N % kItemRows) != 0 || (K % kChunkK) != 0) return B200_EUNSUPPORTED;
+    if (!aligned16(x) || !aligned16(w_tiled) || !aligned16(y) || !aligned16(workspace)) return B200_EALIGN;
+    if (workspace_bytes < b200_qmm_umma_workspace_bytes(M, K)) return B200_EWORKSPACE;
+    const int nt = M <= 16 ? 16 : 32;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    __half* xc = reinterpret_cast<__half*>(static_cast<char*>(workspace) + 256);
+    const int units = nt * (K / 8);
+    launch_kernel(x_canonical_kernel, dim3((units + 255) / 256), dim3(256), 0, st, static_cast<const __half*>(x), xc, M, K, nt);
+    if (check_launch() != B200_OK) return B200_ECUDA;
+    UParams p{};
+    p.w = static_cast<const unsigned char*>(w_tiled);
+    p.xc = xc;
+    p.bias = static_cast<const __half*>(bias);
+    p.y = static_cast<__half*>(y);
+    p.err = static_cast<int*>(workspace);
+    p.M = M; p.N = N; p.K = K;
+    return nt == 16 ? launch_umma<16>(p, st) : launch_umma<32>(p, st);
+}
+
+}  // extern "C"

@@ -113,3 +113,32 @@ def matmul_tiled(x, wt, n, *, epilogue=EPI_NONE, wt2=None, bias=None, extra=None
 def stream_error(device) -> int:
     """Non-zero if a bounded wait inside the tiled kernel ever gave up on this device (reads the flag)."""
     return int(workspace(device)[4092:4096].view(torch.int32).item())
+
+
+_umma_ws = {}
+
+
+def matmul_umma(x, wt, n, *, bias=None, out=None):
+    """``x (M<=32, K) @ W.T`` on re-laid-out weights ``wt`` through the tcgen05 tensor cores
+    (``b200_qmm_umma``; ``n`` and K multiples of 128, plain epilogue)."""
+    _lib.require_cuda(x, wt)
+    m, k = x.shape
+    y = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=x.device)
+    need = _lib.lib().b200_qmm_umma_workspace_bytes(m, k)
+    if need == 0:
+        raise _lib.B200Error("b200_qmm_umma: need 1 <= M <= 32 and K a multiple of 128")
+    key = (x.device, torch.cuda.current_stream(x.device).cuda_stream)
+    ws = _umma_ws.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=x.device)
+        _umma_ws[key] = ws
+    rc = _lib.lib().b200_qmm_umma(_lib.ptr(x), _lib.ptr(wt), _lib.ptr(bias), _lib.ptr(y), m, n, k, _lib.ptr(ws),
+                                  ws.numel(), _lib.stream_ptr(x.device))
+    _lib.check(rc, "b200_qmm_umma")
+    return y
+
+
+def umma_error(device) -> int:
+    """Non-zero if a bounded wait inside the tcgen05 kernel ever gave up on this device's current stream."""
+    ws = _umma_ws.get((device, torch.cuda.current_stream(device).cuda_stream))
+    return 0 if ws is None else int(ws[:4].view(torch.int32).item())
