@@ -394,6 +394,41 @@ def run_tensor_parallel(args, rank, world, local_rank):
     dist.destroy_process_group()
 
 
+def operator_sweep(torch, be, dev, reps=20):
+    """The two matmul operators on re-laid-out weights at the 7B-shape target's big layers, 16 rows: the streaming
+    kernel on mma.sync (b200_qmm_tiled) and the tcgen05 kernel (b200_qmm_umma).  CUDA events; the launches rotate
+    through more than 126 MB of weights so that no launch finds its weights in L2."""
+    qk = be.qmm_kernel
+    out = []
+    for (m, n, k) in [(16, 18944, 3584), (16, 152064, 3584), (8, 151936, 896)]:
+        g = torch.Generator(device=dev).manual_seed(1)
+        nbytes = n * k // 2 + n * k // 16
+        copies = max(2, int(300e6 // nbytes) + 1)
+        wts = []
+        for _ in range(copies):
+            wq, s, b = be.quantize.quantize(torch.randn(n, k, generator=g, device=dev) * 0.02)
+            wts.append(qk.relayout(wq, s, b))
+        x = torch.randn(m, k, generator=g, device=dev).half()
+        y = torch.empty(m, n, dtype=torch.float16, device=dev)
+        row = {"M": m, "N": n, "K": k, "weight_bytes": nbytes}
+        for name, fn in (("qmm_tiled", qk.matmul_tiled), ("qmm_umma", qk.matmul_umma)):
+            for i in range(3):
+                fn(x, wts[i % copies], n, out=y)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(reps):
+                fn(x, wts[i % copies], n, out=y)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / reps * 1e3
+            row[name] = {"us": us, "GBs": nbytes / us / 1e3}
+        row["umma_error_word"] = qk.umma_error(dev)
+        out.append(row)
+        del wts
+    return out
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
@@ -423,6 +458,8 @@ def main():
     ap.add_argument("--roofline-only", action="store_true",
                     help="only the target model's forward kernel at 16 rows (small profiling case with --layers)")
     ap.add_argument("--layers", type=int, default=0, help="with --roofline-only: number of decoder layers (0 = all 28)")
+    ap.add_argument("--operator-sweep", action="store_true",
+                    help="only time the two matmul operators (mma.sync streaming kernel, tcgen05 kernel) at big layer shapes")
     ap.add_argument("--workload", default="streams", choices=["streams"] + sorted(TP_WORKLOADS),
                     help="streams: one independent request stream per GPU (the default, what --gpus N scales); "
                          "tp70b / tp7b: one stream with the target cut across all ranks (needs 2+ ranks)")
@@ -442,6 +479,11 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
     if args.workload != "streams":
         run_tensor_parallel(args, rank, world, local_rank)
+        return
+    if args.operator_sweep:
+        torch.cuda.set_device(local_rank)
+        print(json.dumps({"operator_sweep": operator_sweep(torch, be, torch.device("cuda", local_rank),
+                                                           reps=max(1, min(args.steps, 20)))}))
         return
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)

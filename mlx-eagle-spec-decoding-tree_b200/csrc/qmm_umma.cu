@@ -17,7 +17,8 @@
 //   epilogue        the dequant warps read the accumulator (tcgen05.ld, one weight row per thread) and store fp16.
 //
 // The activations come in the same canonical layout ([chunk][token group of 8][k group of 8][8 tokens][8 halves],
-// token rows padded with zeros to 16 or 32), written by a small relayout kernel into the caller's workspace.
+// k groups 160 bytes apart, token rows padded with zeros to 16 or 32), written by a small relayout kernel into the
+// caller's workspace.
 // Every wait is bounded; a wait that gives up sets the error word in the workspace and the CTA runs to its end
 // (TMEM is always freed).  No copy uses cluster multicast.
 #include <cuda_fp16.h>
@@ -38,25 +39,28 @@ constexpr int kRunBytes = 4 * kRecBytes;        // the four records of a 64-row 
 constexpr int kItemRows = 128;
 constexpr int kDeqWarps = 8;
 constexpr int kUThreads = (kDeqWarps + 2) * 32;  // + producer warp + MMA warp
-constexpr int kPackedStages = 6;
-constexpr int kTileStages = 3;
-constexpr int kLBO = 128;                        // bytes between core matrices along K
-constexpr int kSBO = (kChunkK / 8) * 128;        // bytes between 8-row groups of a 128-k tile
-constexpr int kTileBytes = kItemRows * kChunkK * 2;   // 32 KB of fp16 weights
+// Core matrices (8 rows x 16 bytes = 128 bytes) are spaced 160 bytes apart along K: the four lanes of a row that
+// store the k groups 4j .. 4j+3 in one instruction then fall into different banks (with 128 they collide 4-way,
+// measured: 65 % of the shared-memory wavefronts were conflicts).
+constexpr int kLBO = 160;                        // bytes between core matrices along K
+constexpr int kSBO = (kChunkK / 8) * kLBO;       // bytes between 8-row groups of a 128-k tile
+constexpr int kTileBytes = (kItemRows / 8) * kSBO;    // 40 KB: 128 x 128 fp16 weights in that layout
 constexpr uint32_t kUmmaWaitPolls = 1u << 20;    // x <= 1 us each
 
 template <int NT>                                // token columns of the MMA: 16 or 32
 struct UGeo {
-    static constexpr int XBYTES = NT * kChunkK * 2;                  // activations of one chunk
+    static constexpr int XBYTES = (NT / 8) * kSBO;                   // activations of one chunk, same layout
     static constexpr int PSTAGE = 2 * kRunBytes + XBYTES;            // packed stage
     static constexpr int TSTAGE = kTileBytes + XBYTES;               // fp16 tile + its activations
-    static constexpr int BAR_OFF = kPackedStages * PSTAGE + kTileStages * TSTAGE;
+    static constexpr int NP = NT == 16 ? 6 : 5;                      // packed stages
+    static constexpr int NTS = NT == 16 ? 3 : 2;                     // tile stages
+    static constexpr int BAR_OFF = NP * PSTAGE + NTS * TSTAGE;
     static constexpr int SMEM = BAR_OFF + 256 + 1024;                // + barriers, + alignment slack
 };
 
 struct UParams {
     const unsigned char* w;     // streaming layout
-    const __half* xc;           // activations, canonical layout [chunk][NT/8][16][8][8]
+    const __half* xc;           // activations, canonical layout [chunk][NT/8 token groups][16 k groups, 160 bytes apart][8][8]
     const __half* bias;
     __half* y;                  // [M][N]
     int* err;
@@ -83,7 +87,8 @@ __global__ void x_canonical_kernel(const __half* __restrict__ x, __half* __restr
         const int c = kg_all >> 4, kg = kg_all & 15;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (tok < M) v = *reinterpret_cast<const uint4*>(x + (size_t)tok * K + kg_all * 8);
-        *reinterpret_cast<uint4*>(xc + ((((size_t)c * (NT / 8) + tok / 8) * 16 + kg) * 8 + (tok & 7)) * 8) = v;
+        *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(xc) + ((size_t)c * (NT / 8) + tok / 8) * kSBO + kg * kLBO +
+                                  (tok & 7) * 16) = v;
     }
 }
 
@@ -93,13 +98,13 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* packed = smem;
-    unsigned char* tiles = smem + kPackedStages * G::PSTAGE;
+    unsigned char* tiles = smem + G::NP * G::PSTAGE;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G::BAR_OFF);
     uint64_t* pfull = bars;                          // packed stage landed            (producer -> dequant warps)
-    uint64_t* pempty = pfull + kPackedStages;        // packed stage read              (8 dequant warps -> producer)
-    uint64_t* tready = pempty + kPackedStages;       // tile written                   (8 dequant warps -> MMA warp)
-    uint64_t* tfree = tready + kTileStages;          // tile's MMAs complete           (tcgen05.commit -> dequant warps)
-    uint64_t* accfull = tfree + kTileStages;         // item's accumulator complete    (tcgen05.commit -> epilogue)
+    uint64_t* pempty = pfull + G::NP;        // packed stage read              (8 dequant warps -> producer)
+    uint64_t* tready = pempty + G::NP;       // tile written                   (8 dequant warps -> MMA warp)
+    uint64_t* tfree = tready + G::NTS;          // tile's MMAs complete           (tcgen05.commit -> dequant warps)
+    uint64_t* accfull = tfree + G::NTS;         // item's accumulator complete    (tcgen05.commit -> epilogue)
     uint64_t* accempty = accfull + 2;                // accumulator read               (8 warps -> MMA warp)
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
@@ -111,11 +116,11 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < kPackedStages; s++) {
+        for (int s = 0; s < G::NP; s++) {
             mbar_init(smem_u32(pfull + s), 1);
             mbar_init(smem_u32(pempty + s), kDeqWarps);
         }
-        for (int s = 0; s < kTileStages; s++) {
+        for (int s = 0; s < G::NTS; s++) {
             mbar_init(smem_u32(tready + s), kDeqWarps);
             mbar_init(smem_u32(tfree + s), 1);
         }
@@ -144,7 +149,7 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
         for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
             const unsigned char* w0 = p.w + (size_t)(2 * item) * block_stride;
             for (int c = 0; c < nchunks; c++, n++) {
-                const uint32_t s = n % kPackedStages, use = n / kPackedStages;
+                const uint32_t s = n % G::NP, use = n / G::NP;
                 if (*abort_flag) break;
                 if (use > 0 && !__all_sync(0xffffffffu, uwait(smem_u32(pempty + s), (use - 1) & 1u))) {
                     if (lane == 0) { *abort_flag = 1; atomicCAS(p.err, 0, 1); }
@@ -156,7 +161,8 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
                     mbar_expect_tx(bar, G::PSTAGE);
                     bulk_copy_g2s_hint(dst, w0 + (size_t)c * kRunBytes, kRunBytes, bar, pol);
                     bulk_copy_g2s_hint(dst + kRunBytes, w0 + block_stride + (size_t)c * kRunBytes, kRunBytes, bar, pol);
-                    bulk_copy_g2s(dst + 2 * kRunBytes, p.xc + (size_t)c * NT * kChunkK, G::XBYTES, bar);
+                    bulk_copy_g2s(dst + 2 * kRunBytes, reinterpret_cast<const unsigned char*>(p.xc) + (size_t)c * G::XBYTES,
+                                  G::XBYTES, bar);
                 }
                 __syncwarp();
             }
@@ -172,7 +178,7 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
                 if (it >= 2) ok = uwait(smem_u32(accempty + ab), ((it >> 1) - 1) & 1u);     // epilogue of item it-2 done
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 for (int c = 0; c < nchunks && ok; c++, n++) {
-                    const uint32_t ts = n % kTileStages, use = n / kTileStages;
+                    const uint32_t ts = n % G::NTS, use = n / G::NTS;
                     ok = !*abort_flag && uwait(smem_u32(tready + ts), use & 1u);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -209,8 +215,8 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
         bool ok = true;
         for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, it++) {
             for (int c = 0; c < nchunks && ok; c++, n++) {
-                const uint32_t ps = n % kPackedStages, ts = n % kTileStages, tuse = n / kTileStages;
-                ok = !*abort_flag && uwait(smem_u32(pfull + ps), (n / kPackedStages) & 1u);
+                const uint32_t ps = n % G::NP, ts = n % G::NTS, tuse = n / G::NTS;
+                ok = !*abort_flag && uwait(smem_u32(pfull + ps), (n / G::NP) & 1u);
                 if (ok && tuse > 0) ok = uwait(smem_u32(tfree + ts), (tuse - 1) & 1u);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -316,7 +322,7 @@ using namespace b200;
 size_t b200_qmm_umma_workspace_bytes(int M, int K) {
     if (M < 1 || M > 32 || K < kChunkK || (K % kChunkK) != 0) return 0;
     const int nt = M <= 16 ? 16 : 32;
-    return 256 + (size_t)nt * K * sizeof(__half);
+    return 256 + (size_t)(K / kChunkK) * (nt / 8) * kSBO;
 }
 
 int b200_qmm_umma(const void* x, const void* w_tiled, const void* bias, void* y, int M, int N, int K, void* workspace,
