@@ -464,6 +464,8 @@ def main():
                     help="streams: one independent request stream per GPU (the default, what --gpus N scales); "
                          "tp70b / tp7b: one stream with the target cut across all ranks (needs 2+ ranks)")
     args = ap.parse_args()
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"        # NCCL writes its version banner to stdout, which carries the JSON line
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
