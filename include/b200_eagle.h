@@ -282,6 +282,9 @@ int b200_tp_exchange_alloc(size_t bytes, void** ptr, unsigned char* handle);
 int b200_tp_exchange_open(const unsigned char* handle, void** ptr);
 int b200_tp_exchange_close(void* ptr);
 int b200_tp_exchange_free(void* ptr);
+/* Zero this GPU's own buffer again (synchronous).  After a pass that reported a timeout every rank calls it with
+ * no launch in flight anywhere (the host synchronises the ranks before and after), then passes may resume. */
+int b200_tp_exchange_reset(void* own_buffer, size_t bytes);
 /* Error word of the argmax combine in this GPU's own buffer: 0, or 1 after a combine that gave up waiting
  * for a peer (synchronous 4-byte copy; negative = B200_E*). */
 int b200_tp_exchange_error(const void* own_buffer);

@@ -108,6 +108,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_tp_exchange_close.argtypes = [vp]
     l.b200_tp_exchange_free.restype = i32
     l.b200_tp_exchange_free.argtypes = [vp]
+    l.b200_tp_exchange_reset.restype = i32
+    l.b200_tp_exchange_reset.argtypes = [vp, sz]
     l.b200_tp_exchange_error.restype = i32
     l.b200_tp_exchange_error.argtypes = [vp]
     l.b200_tp_argmax_combine.restype = i32

@@ -130,6 +130,13 @@ int b200_tp_argmax_combine(unsigned long long* best_key, int R, unsigned int ind
     return b200::check_launch();
 }
 
+int b200_tp_exchange_reset(void* own_buffer, size_t bytes) {
+    if (!own_buffer || bytes == 0) return B200_EINVAL;
+    cudaError_t e = cudaMemset(own_buffer, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    return e == cudaSuccess ? B200_OK : fail(e);
+}
+
 int b200_tp_exchange_free(void* ptr) {
     if (!ptr) return B200_EINVAL;
     const cudaError_t e = cudaFree(ptr);

@@ -135,6 +135,7 @@ class TensorParallel:
             peers.append(q.value)
         dist.barrier(group=self.group)
         self.peers = peers
+        self.nbytes = nbytes
         self.peer_array = (ctypes.c_void_p * 8)(*peers)
 
     def check_error(self):
@@ -143,6 +144,18 @@ class TensorParallel:
             rc = _lib.lib().b200_tp_exchange_error(ctypes.c_void_p(self.peers[self.rank]))
             if rc != 0:
                 raise _lib.B200Error(f"tensor-parallel exchange: a bounded wait for a peer gave up ({rc})")
+
+    def reset_exchange(self):
+        """After a pass that reported a timeout: zero every GPU's exchange buffer (collective; the caller also
+        clears the models' error words, ``Model.check_fused_error`` does that when it raises)."""
+        if self.peers is None:
+            return
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        lib = _lib.lib()
+        _lib.check(lib.b200_tp_exchange_reset(ctypes.c_void_p(self.peers[self.rank]), self.nbytes), "b200_tp_exchange_reset")
+        dist.barrier(group=self.group)
 
     def close_exchange(self):
         """Unmap the peers' buffers and free this GPU's (collective: no rank may still be inside a pass)."""

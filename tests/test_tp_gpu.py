@@ -51,6 +51,11 @@ def _rank(rank, world, port, out):
         out.put((res["tokens"], res["accept_lengths"], res2["tokens"], res2["accept_lengths"], err,
                  res2["decoder"].graph is not None))
     dist.barrier()
+    # the reset a host does after a reported timeout leaves the group usable (no timeout is provoked here)
+    shard.tp.reset_exchange()
+    again = shard(prompt[None], cache=shard.make_cache(128))[0].float().cpu()
+    shard.check_fused_error()
+    assert torch.equal(again, fused)
     shard.tp.close_exchange()
     dist.destroy_process_group()
 
