@@ -7,7 +7,7 @@
 //
 //   producer warp   bulk-copies, per k chunk, the two 4608-byte record runs of the item and the chunk's
 //                   activations into a ring of packed stages;
-//   8 dequant warps each expands its record (exact q*s+b, rounded once to fp16, like every other kernel of
+//   16 dequant warps in two groups of 8 that take the chunks in turn; each warp expands its record (exact q*s+b, rounded once to fp16, like every other kernel of
 //                   this library) into a 128 x 128 fp16 tile in shared memory, in the canonical K-major layout
 //                   of the tensor cores without swizzle (core matrix = 8 rows x 16 bytes, contiguous): a lane's
 //                   8 dequantised halves are exactly one core-matrix row, a warp's store covers 512 contiguous
@@ -37,7 +37,8 @@ namespace {
 constexpr int kRecBytes = 1152;
 constexpr int kRunBytes = 4 * kRecBytes;        // the four records of a 64-row block for one chunk
 constexpr int kItemRows = 128;
-constexpr int kDeqWarps = 8;
+constexpr int kGroupWarps = 8;                   // warps that expand one chunk together (one 16-row record each)
+constexpr int kDeqWarps = 2 * kGroupWarps;       // two such groups take the chunks in turn
 constexpr int kUThreads = (kDeqWarps + 2) * 32;  // + producer warp + MMA warp
 // Core matrices (8 rows x 16 bytes = 128 bytes) are spaced 160 bytes apart along K: the four lanes of a row that
 // store the k groups 4j .. 4j+3 in one instruction then fall into different banks (with 128 they collide 4-way,
@@ -45,7 +46,7 @@ constexpr int kUThreads = (kDeqWarps + 2) * 32;  // + producer warp + MMA warp
 constexpr int kLBO = 160;                        // bytes between core matrices along K
 constexpr int kSBO = (kChunkK / 8) * kLBO;       // bytes between 8-row groups of a 128-k tile
 constexpr int kTileBytes = (kItemRows / 8) * kSBO;    // 40 KB: 128 x 128 fp16 weights in that layout
-constexpr uint32_t kUmmaWaitPolls = 1u << 20;    // x <= 1 us each
+constexpr uint32_t kUmmaWaitPolls = 1u << 24;    // x <= 32 ns each (short suspensions: the handshakes are on the critical path)
 
 template <int NT>                                // token columns of the MMA: 16 or 32
 struct UGeo {
@@ -74,7 +75,7 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
 }
 
 __device__ __forceinline__ bool uwait(uint32_t bar, uint32_t parity) {
-    return mbar_wait_timed(bar, parity, kUmmaWaitPolls, 1000u);
+    return mbar_wait_timed(bar, parity, kUmmaWaitPolls, 32u);
 }
 
 __global__ void x_canonical_kernel(const __half* __restrict__ x, __half* __restrict__ xc, int M, int K, int NT) {
@@ -118,10 +119,10 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
         s_abort = 0;
         for (int s = 0; s < G::NP; s++) {
             mbar_init(smem_u32(pfull + s), 1);
-            mbar_init(smem_u32(pempty + s), kDeqWarps);
+            mbar_init(smem_u32(pempty + s), kGroupWarps);
         }
         for (int s = 0; s < G::NTS; s++) {
-            mbar_init(smem_u32(tready + s), kDeqWarps);
+            mbar_init(smem_u32(tready + s), kGroupWarps);
             mbar_init(smem_u32(tfree + s), 1);
         }
         for (int s = 0; s < 2; s++) {
@@ -155,15 +156,16 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
                     if (lane == 0) { *abort_flag = 1; atomicCAS(p.err, 0, 1); }
                     break;
                 }
-                if (lane == 0) {
-                    const uint32_t bar = smem_u32(pfull + s);
-                    const uint32_t dst = smem_u32(packed + s * G::PSTAGE);
-                    mbar_expect_tx(bar, G::PSTAGE);
-                    bulk_copy_g2s_hint(dst, w0 + (size_t)c * kRunBytes, kRunBytes, bar, pol);
-                    bulk_copy_g2s_hint(dst + kRunBytes, w0 + block_stride + (size_t)c * kRunBytes, kRunBytes, bar, pol);
+                // one lane per copy (a bulk copy costs ~150 cycles to issue from a single lane, whatever its size)
+                const uint32_t bar = smem_u32(pfull + s);
+                const uint32_t dst = smem_u32(packed + s * G::PSTAGE);
+                if (lane == 0) mbar_expect_tx(bar, G::PSTAGE);
+                __syncwarp();
+                if (lane < 2)
+                    bulk_copy_g2s_hint(dst + lane * kRunBytes, w0 + lane * block_stride + (size_t)c * kRunBytes, kRunBytes, bar, pol);
+                else if (lane == 2)
                     bulk_copy_g2s(dst + 2 * kRunBytes, reinterpret_cast<const unsigned char*>(p.xc) + (size_t)c * G::XBYTES,
                                   G::XBYTES, bar);
-                }
                 __syncwarp();
             }
         }
@@ -211,10 +213,13 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
     } else {
         // ------------------------------------------------------------------ dequant warps + epilogue
         const int g = lane >> 2, t = lane & 3;
+        const uint32_t grp = warp / kGroupWarps;     // this warp's group takes the chunks with n % 2 == grp
+        const int wl = warp % kGroupWarps;
         uint32_t n = 0, it = 0;
         bool ok = true;
         for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, it++) {
             for (int c = 0; c < nchunks && ok; c++, n++) {
+                if ((n & 1u) != grp) continue;
                 const uint32_t ps = n % G::NP, ts = n % G::NTS, tuse = n / G::NTS;
                 ok = !*abort_flag && uwait(smem_u32(pfull + ps), (n / G::NP) & 1u);
                 if (ok && tuse > 0) ok = uwait(smem_u32(tfree + ts), (tuse - 1) & 1u);
@@ -223,17 +228,17 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
                 const unsigned char* stage = packed + ps * G::PSTAGE;
                 unsigned char* tile = tiles + ts * G::TSTAGE;
                 // the chunk's activations move next to the tile (they are read by the MMAs, the packed stage is freed now)
-                for (int i = threadIdx.x; i < G::XBYTES / 16; i += kDeqWarps * 32)
+                for (int i = wl * 32 + lane; i < G::XBYTES / 16; i += kGroupWarps * 32)
                     *reinterpret_cast<uint4*>(tile + kTileBytes + i * 16) =
                         *reinterpret_cast<const uint4*>(stage + 2 * kRunBytes + i * 16);
-                // this warp's record: 64-row block warp / 4, record warp % 4; rows 16 * warp + g and + 8
-                const unsigned char* rec = stage + (warp >> 2) * kRunBytes + (warp & 3) * kRecBytes;
+                // this warp's record: 64-row block wl / 4, record wl % 4; rows 16 * wl + g and + 8
+                const unsigned char* rec = stage + (wl >> 2) * kRunBytes + (wl & 3) * kRecBytes;
                 const uint4 w0 = *reinterpret_cast<const uint4*>(rec + lane * 16);
                 const uint4 w1 = *reinterpret_cast<const uint4*>(rec + 512 + lane * 16);
                 const uint2 sb0 = *reinterpret_cast<const uint2*>(rec + 1024 + g * 8);
                 const uint2 sb1 = *reinterpret_cast<const uint2*>(rec + 1024 + (8 + g) * 8);
-                unsigned char* dst0 = tile + (2 * warp) * kSBO + g * 16;           // rows 16 * warp + g
-                unsigned char* dst1 = dst0 + kSBO;                                 // rows 16 * warp + 8 + g
+                unsigned char* dst0 = tile + (2 * wl) * kSBO + g * 16;             // rows 16 * wl + g
+                unsigned char* dst1 = dst0 + kSBO;                                 // rows 16 * wl + 8 + g
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     const __half2 p0 = u32_as_h2((j < 2) ? sb0.x : sb0.y);         // {scale, bias} of the k group of 64
@@ -253,27 +258,25 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
                 }
             }
             if (!ok) break;
-            // ---- epilogue: thread = weight row 32 * (warp % 4) + lane of the item, half of the token columns
+            // ---- epilogue: thread = weight row 32 * (warp % 4) + lane of the item, a quarter of the token columns
             const uint32_t ab = it & 1u;
             ok = __all_sync(0xffffffffu, !*abort_flag && uwait(smem_u32(accfull + ab), (it >> 1) & 1u));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            constexpr int CH = NT / 2;                // columns per warp: 8 or 16
+            constexpr int CH = NT / 4;                // columns per warp: 4 or 8
             const int col0 = (warp >> 2) * CH;
             const uint32_t taddr = tmem + ab * 32 + col0 + ((uint32_t)((warp & 3) * 32) << 16);
             uint32_t r[CH];
-            if constexpr (CH == 8) {
+            if constexpr (CH == 4) {
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                             : "r"(taddr)
+                             : "memory");
+            } else {
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
                              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                              : "r"(taddr)
                              : "memory");
-            } else {
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                    : "r"(taddr)
-                    : "memory");
             }
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
