@@ -5,20 +5,23 @@
 // W is in the streaming layout of b200_qmm_relayout (records of 16 rows x 128 k, 1152 bytes, ordered
 // [64-row block][k chunk][4 records]).  One CTA owns items of 128 weight rows (the M of one tcgen05.mma):
 //
-//   producer warp   bulk-copies, per k chunk, the two 4608-byte record runs of the item and the chunk's
-//                   activations into a ring of packed stages;
-//   16 dequant warps in two groups of 8 that take the chunks in turn; each warp expands its record (exact q*s+b, rounded once to fp16, like every other kernel of
-//                   this library) into a 128 x 128 fp16 tile in shared memory, in the canonical K-major layout
-//                   of the tensor cores without swizzle (core matrix = 8 rows x 16 bytes, contiguous): a lane's
-//                   8 dequantised halves are exactly one core-matrix row, a warp's store covers 512 contiguous
-//                   bytes; they also move the chunk's activations next to the tile;
-//   MMA warp        one thread issues 8 tcgen05.mma (128 x N x 16, N = 16 or 32 tokens) per chunk into a TMEM
-//                   accumulator and commits to the mbarriers that free the tile and publish the accumulator;
-//   epilogue        the dequant warps read the accumulator (tcgen05.ld, one weight row per thread) and store fp16.
+//   producer warp    bulk-copies, per k chunk, the two 4608-byte record runs of the item and the chunk's
+//                    activations into a ring of packed stages (one lane per copy);
+//   16 dequant warps in two groups of 8 that take the chunks in turn.  Thread = weight row: a row's 16 packs
+//                    of a chunk are 64 contiguous bytes of its record; the thread expands its half of them
+//                    (exact q*s+b, rounded once to fp16, like every other kernel of this library) and writes
+//                    the fp16 pairs with tcgen05.st into its own lane of a 128-lane x 64-column tile in tensor
+//                    memory (lane = weight row, column = two k values): the A operand never touches shared
+//                    memory.  The group also moves the chunk's activations to the slot that goes with the tile;
+//   MMA warp         one thread issues 8 tcgen05.mma (128 x N x 16, N = 16 or 32 tokens; A from tensor memory,
+//                    B = activations from shared memory) per chunk into a TMEM accumulator and commits to the
+//                    mbarriers that free the tile and publish the accumulator;
+//   epilogue         the dequant warps read the accumulator (tcgen05.ld, one weight row per thread) and store fp16.
 //
-// The activations come in the same canonical layout ([chunk][token group of 8][k group of 8][8 tokens][8 halves],
-// k groups 160 bytes apart, token rows padded with zeros to 16 or 32), written by a small relayout kernel into the
-// caller's workspace.
+// The activations come in the tensor cores' canonical K-major layout without swizzle ([chunk][token group of 8]
+// [k group of 8][8 tokens][8 halves]: a core matrix is 8 rows x 16 bytes; k groups 160 bytes apart, token rows
+// padded with zeros to 16 or 32), written by a small relayout kernel into the caller's workspace.
+// Tensor memory: all 512 columns of the SM (4 tiles of 64 columns, 2 accumulators of 32).
 // Every wait is bounded; a wait that gives up sets the error word in the workspace and the CTA runs to its end
 // (TMEM is always freed).  No copy uses cluster multicast.
 #include <cuda_fp16.h>
@@ -40,21 +43,23 @@ constexpr int kItemRows = 128;
 constexpr int kGroupWarps = 8;                   // warps that expand one chunk together (one 16-row record each)
 constexpr int kDeqWarps = 2 * kGroupWarps;       // two such groups take the chunks in turn
 constexpr int kUThreads = (kDeqWarps + 2) * 32;  // + producer warp + MMA warp
-// Core matrices (8 rows x 16 bytes = 128 bytes) are spaced 160 bytes apart along K: the four lanes of a row that
-// store the k groups 4j .. 4j+3 in one instruction then fall into different banks (with 128 they collide 4-way,
-// measured: 65 % of the shared-memory wavefronts were conflicts).
+// Core matrices (8 rows x 16 bytes = 128 bytes) of the activation tile are spaced 160 bytes apart along K (any
+// multiple of 16 is allowed): stores of one row's neighbouring k groups then fall into different banks.
 constexpr int kLBO = 160;                        // bytes between core matrices along K
 constexpr int kSBO = (kChunkK / 8) * kLBO;       // bytes between 8-row groups of a 128-k tile
-constexpr int kTileBytes = (kItemRows / 8) * kSBO;    // 40 KB: 128 x 128 fp16 weights in that layout
+constexpr int kAStages = 4;                      // dequantised weight tiles in tensor memory
+constexpr int kAColumns = kChunkK / 2;           // 64 columns of 32 bits: 128 fp16 k values per weight row
+constexpr int kAccColumn = kAStages * kAColumns; // the two accumulators follow the tiles
+// (the CTA allocates all 512 columns of the SM's tensor memory: 4 x 64 for tiles, 2 x 32 for accumulators)
 constexpr uint32_t kUmmaWaitPolls = 1u << 24;    // x <= 32 ns each (short suspensions: the handshakes are on the critical path)
 
 template <int NT>                                // token columns of the MMA: 16 or 32
 struct UGeo {
     static constexpr int XBYTES = (NT / 8) * kSBO;                   // activations of one chunk, same layout
     static constexpr int PSTAGE = 2 * kRunBytes + XBYTES;            // packed stage
-    static constexpr int TSTAGE = kTileBytes + XBYTES;               // fp16 tile + its activations
-    static constexpr int NP = NT == 16 ? 6 : 5;                      // packed stages
-    static constexpr int NTS = NT == 16 ? 3 : 2;                     // tile stages
+    static constexpr int TSTAGE = XBYTES;                            // the activations that go with a tile in tensor memory
+    static constexpr int NP = 8;                                     // packed stages
+    static constexpr int NTS = kAStages;                             // tile stages
     static constexpr int BAR_OFF = NP * PSTAGE + NTS * TSTAGE;
     static constexpr int SMEM = BAR_OFF + 256 + 1024;                // + barriers, + alignment slack
 };
@@ -132,7 +137,7 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == kDeqWarps + 1) {                     // the MMA warp owns the tensor memory: 64 columns = two accumulators
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 64;\n" ::"r"(smem_u32(&s_tmem)) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(smem_u32(&s_tmem)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -184,17 +189,16 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
                     ok = !*abort_flag && uwait(smem_u32(tready + ts), use & 1u);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const uint32_t a0 = smem_u32(tiles + ts * G::TSTAGE);
-                    const uint32_t b0 = a0 + kTileBytes;
+                    const uint32_t a0 = tmem + ts * kAColumns;        // the tile: lane = weight row, column = two k values
+                    const uint32_t b0 = smem_u32(tiles + ts * G::TSTAGE);
 #pragma unroll
                     for (int ks = 0; ks < kChunkK / 16; ks++) {
-                        const uint64_t da = umma_desc(a0 + ks * 2 * kLBO);
                         const uint64_t db = umma_desc(b0 + ks * 2 * kLBO);
                         const uint32_t accumulate = (c > 0 || ks > 0) ? 1u : 0u;
                         asm volatile(
                             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem + ab * 32),
-                            "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+                            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem + kAccColumn + ab * 32),
+                            "r"(a0 + ks * 8), "l"(db), "r"(idesc), "r"(accumulate)
                             : "memory");
                     }
                     // the tile (and its activations) may be rewritten once these MMAs have read it
@@ -212,7 +216,6 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ dequant warps + epilogue
-        const int g = lane >> 2, t = lane & 3;
         const uint32_t grp = warp / kGroupWarps;     // this warp's group takes the chunks with n % 2 == grp
         const int wl = warp % kGroupWarps;
         uint32_t n = 0, it = 0;
@@ -226,30 +229,37 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const unsigned char* stage = packed + ps * G::PSTAGE;
-                unsigned char* tile = tiles + ts * G::TSTAGE;
-                // the chunk's activations move next to the tile (they are read by the MMAs, the packed stage is freed now)
+                unsigned char* xslot = tiles + ts * G::TSTAGE;
+                // the chunk's activations move to the slot of the tile (the MMAs read them; the packed stage is freed now)
                 for (int i = wl * 32 + lane; i < G::XBYTES / 16; i += kGroupWarps * 32)
-                    *reinterpret_cast<uint4*>(tile + kTileBytes + i * 16) =
-                        *reinterpret_cast<const uint4*>(stage + 2 * kRunBytes + i * 16);
-                // this warp's record: 64-row block wl / 4, record wl % 4; rows 16 * wl + g and + 8
-                const unsigned char* rec = stage + (wl >> 2) * kRunBytes + (wl & 3) * kRecBytes;
-                const uint4 w0 = *reinterpret_cast<const uint4*>(rec + lane * 16);
-                const uint4 w1 = *reinterpret_cast<const uint4*>(rec + 512 + lane * 16);
-                const uint2 sb0 = *reinterpret_cast<const uint2*>(rec + 1024 + g * 8);
-                const uint2 sb1 = *reinterpret_cast<const uint2*>(rec + 1024 + (8 + g) * 8);
-                unsigned char* dst0 = tile + (2 * wl) * kSBO + g * 16;             // rows 16 * wl + g
-                unsigned char* dst1 = dst0 + kSBO;                                 // rows 16 * wl + 8 + g
+                    *reinterpret_cast<uint4*>(xslot + i * 16) = *reinterpret_cast<const uint4*>(stage + 2 * kRunBytes + i * 16);
+                // Thread = weight row 32 * (wl % 4) + lane of the item (the tensor-memory lane this warp may write);
+                // warps 0-3 of the group take the k groups 4j+0, 4j+1, warps 4-7 the k groups 4j+2, 4j+3.  A row's 16
+                // packs are 64 contiguous bytes of its record: pack j of k group 4j+t at byte 16 t + 4 j.
+                const int q = wl & 3, kh = wl >> 2;
+                const int tile_i = 2 * q + (lane >> 4), r = lane & 15;
+                const unsigned char* rec = stage + (tile_i >> 2) * kRunBytes + (tile_i & 3) * kRecBytes;
+                const unsigned char* rowp = rec + (r >> 3) * 512 + (r & 7) * 64 + kh * 32;
+                const uint4 u0 = *reinterpret_cast<const uint4*>(rowp);
+                const uint4 u1 = *reinterpret_cast<const uint4*>(rowp + 16);
+                const uint2 sb = *reinterpret_cast<const uint2*>(rec + 1024 + r * 8);
+                const uint32_t trow = tmem + ts * kAColumns + ((uint32_t)(q * 32) << 16);
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const __half2 p0 = u32_as_h2((j < 2) ? sb0.x : sb0.y);         // {scale, bias} of the k group of 64
-                    const __half2 p1 = u32_as_h2((j < 2) ? sb1.x : sb1.y);
-                    uint32_t d0[4], d1[4];
-                    dequant_pack(comp(w0, j), __low2half2(p0), __high2half2(p0), d0);
-                    dequant_pack(comp(w1, j), __low2half2(p1), __high2half2(p1), d1);
-                    // k group 4 j + t: the lane's 8 halves are one core-matrix row
-                    *reinterpret_cast<uint4*>(dst0 + (4 * j + t) * kLBO) = make_uint4(d0[0], d0[1], d0[2], d0[3]);
-                    *reinterpret_cast<uint4*>(dst1 + (4 * j + t) * kLBO) = make_uint4(d1[0], d1[1], d1[2], d1[3]);
+                for (int tt = 0; tt < 2; tt++) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const __half2 sbj = u32_as_h2((j < 2) ? sb.x : sb.y);      // {scale, bias} of the k group of 64
+                        uint32_t d[4];
+                        dequant_pack(comp(tt == 0 ? u0 : u1, j), __low2half2(sbj), __high2half2(sbj), d);
+                        // k group 4 j + t = columns 16 j + 4 t .. + 3 (two k values per column)
+                        asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(
+                                         trow + 16 * j + 4 * (2 * kh + tt)),
+                                     "r"(d[0]), "r"(d[1]), "r"(d[2]), "r"(d[3])
+                                     : "memory");
+                    }
                 }
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
                 fence_proxy_async();                  // generic-proxy stores -> visible to the tensor cores' reads
                 __syncwarp();
                 if (lane == 0) {
@@ -265,7 +275,7 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             constexpr int CH = NT / 4;                // columns per warp: 4 or 8
             const int col0 = (warp >> 2) * CH;
-            const uint32_t taddr = tmem + ab * 32 + col0 + ((uint32_t)((warp & 3) * 32) << 16);
+            const uint32_t taddr = tmem + kAccColumn + ab * 32 + col0 + ((uint32_t)((warp & 3) * 32) << 16);
             uint32_t r[CH];
             if constexpr (CH == 4) {
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];\n"
@@ -300,7 +310,7 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     if (warp == kDeqWarps + 1)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 64;\n" ::"r"(tmem) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
 }
 
 template <int NT>
