@@ -395,12 +395,17 @@ def run_tensor_parallel(args, rank, world, local_rank):
 
 
 def operator_sweep(torch, be, dev, reps=20):
-    """The two matmul operators on re-laid-out weights at the 7B-shape target's big layers, 16 rows: the streaming
-    kernel on mma.sync (b200_qmm_tiled) and the tcgen05 kernel (b200_qmm_umma).  CUDA events; the launches rotate
+    """The two matmul operators on re-laid-out weights at the 7B-shape target's big layers, at decode row counts and
+    at 128 rows (prompt ingestion; the streaming kernel then needs four launches): the streaming kernel on mma.sync
+    (b200_qmm_tiled) and the tcgen05 kernel (b200_qmm_umma).  CUDA events; the launches rotate
     through more than 126 MB of weights so that no launch finds its weights in L2."""
     qk = be.qmm_kernel
     out = []
-    for (m, n, k) in [(16, 18944, 3584), (16, 152064, 3584), (8, 151936, 896)]:
+    def tiled_blocks(x, wt, n, out):              # the streaming kernel takes 32 rows per launch
+        for r in range(0, x.shape[0], 32):
+            qk.matmul_tiled(x[r:r + 32], wt, n, out=out[r:r + 32])
+
+    for (m, n, k) in [(16, 18944, 3584), (16, 152064, 3584), (8, 151936, 896), (128, 18944, 3584), (128, 152064, 3584)]:
         g = torch.Generator(device=dev).manual_seed(1)
         nbytes = n * k // 2 + n * k // 16
         copies = max(2, int(300e6 // nbytes) + 1)
@@ -411,7 +416,7 @@ def operator_sweep(torch, be, dev, reps=20):
         x = torch.randn(m, k, generator=g, device=dev).half()
         y = torch.empty(m, n, dtype=torch.float16, device=dev)
         row = {"M": m, "N": n, "K": k, "weight_bytes": nbytes}
-        for name, fn in (("qmm_tiled", qk.matmul_tiled), ("qmm_umma", qk.matmul_umma)):
+        for name, fn in (("qmm_tiled", tiled_blocks if m > 32 else qk.matmul_tiled), ("qmm_umma", qk.matmul_umma)):
             for i in range(3):
                 fn(x, wts[i % copies], n, out=y)
             torch.cuda.synchronize()

@@ -126,7 +126,8 @@ int b200_qmm_tiled(const void* x, const void* wt, const void* wt2, const void* b
 
 /* The same product (plain epilogue: y = fp16(acc) [+ bias, in fp16]) on the tcgen05 tensor cores: the
  * dequantised fp16 weights (exact q*s+b, rounded once) go through shared memory as 128-row tiles, one thread per
- * CTA issues tcgen05.mma with the accumulator in tensor memory.  Same streaming weight layout; M <= 32,
+ * CTA issues tcgen05.mma with the accumulator in tensor memory.  Same streaming weight layout; M <= 128 (one
+ * weight read serves up to 128 token rows: the shape of prompt ingestion),
  * N % 128 == 0, K % 128 == 0.  workspace: b200_qmm_umma_workspace_bytes bytes (the activations re-laid for the
  * tensor cores + an error word, int 0 of the workspace, non-zero if a bounded wait gave up; zero it before
  * the first use).  Replaces qmm_kernel.py:79-124 like b200_qmm. */

@@ -1,4 +1,4 @@
-// 4-bit affine quantised matmul for <= 32 token rows on the fifth-generation tensor cores (tcgen05, TMEM).
+// 4-bit affine quantised matmul for <= 128 token rows on the fifth-generation tensor cores (tcgen05, TMEM).
 //
 //   y[M][N] = x[M][K] . dequant(W)[N][K]^T     (+ bias), fp16 in, fp32 accumulate, fp16 out
 //
@@ -13,15 +13,15 @@
 //                    the fp16 pairs with tcgen05.st into its own lane of a 128-lane x 64-column tile in tensor
 //                    memory (lane = weight row, column = two k values): the A operand never touches shared
 //                    memory.  The group also moves the chunk's activations to the slot that goes with the tile;
-//   MMA warp         one thread issues 8 tcgen05.mma (128 x N x 16, N = 16 or 32 tokens; A from tensor memory,
+//   MMA warp         one thread issues 8 tcgen05.mma (128 x N x 16, N = 16 .. 128 tokens; A from tensor memory,
 //                    B = activations from shared memory) per chunk into a TMEM accumulator and commits to the
 //                    mbarriers that free the tile and publish the accumulator;
 //   epilogue         the dequant warps read the accumulator (tcgen05.ld, one weight row per thread) and store fp16.
 //
 // The activations come in the tensor cores' canonical K-major layout without swizzle ([chunk][token group of 8]
 // [k group of 8][8 tokens][8 halves]: a core matrix is 8 rows x 16 bytes; k groups 160 bytes apart, token rows
-// padded with zeros to 16 or 32), written by a small relayout kernel into the caller's workspace.
-// Tensor memory: all 512 columns of the SM (4 tiles of 64 columns, 2 accumulators of 32).
+// padded with zeros to 16, 32, 64 or 128), written by a small relayout kernel into the caller's workspace.
+// Tensor memory: all 512 columns of the SM (4 tiles of 64 columns, then 2 accumulators of up to 128).
 // Every wait is bounded; a wait that gives up sets the error word in the workspace and the CTA runs to its end
 // (TMEM is always freed).  No copy uses cluster multicast.
 #include <cuda_fp16.h>
@@ -58,8 +58,9 @@ struct UGeo {
     static constexpr int XBYTES = (NT / 8) * kSBO;                   // activations of one chunk, same layout
     static constexpr int PSTAGE = 2 * kRunBytes + XBYTES;            // packed stage
     static constexpr int TSTAGE = XBYTES;                            // the activations that go with a tile in tensor memory
-    static constexpr int NP = 8;                                     // packed stages
-    static constexpr int NTS = kAStages;                             // tile stages
+    static constexpr int NP = NT <= 32 ? 8 : (NT == 64 ? 4 : 2);      // packed stages
+    static constexpr int NTS = NT <= 64 ? kAStages : 2;              // tile stages (tensor-memory tiles + activation slots)
+    static constexpr int ACC = NT < 32 ? 32 : NT;                    // columns of one accumulator
     static constexpr int BAR_OFF = NP * PSTAGE + NTS * TSTAGE;
     static constexpr int SMEM = BAR_OFF + 256 + 1024;                // + barriers, + alignment slack
 };
@@ -197,7 +198,7 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
                         const uint32_t accumulate = (c > 0 || ks > 0) ? 1u : 0u;
                         asm volatile(
                             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem + kAccColumn + ab * 32),
+                            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem + kAccColumn + ab * G::ACC),
                             "r"(a0 + ks * 8), "l"(db), "r"(idesc), "r"(accumulate)
                             : "memory");
                     }
@@ -273,21 +274,16 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
             ok = __all_sync(0xffffffffu, !*abort_flag && uwait(smem_u32(accfull + ab), (it >> 1) & 1u));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            constexpr int CH = NT / 4;                // columns per warp: 4 or 8
+            constexpr int CH = NT / 4;                // columns per warp: 4 .. 32
             const int col0 = (warp >> 2) * CH;
-            const uint32_t taddr = tmem + kAccColumn + ab * 32 + col0 + ((uint32_t)((warp & 3) * 32) << 16);
+            const uint32_t taddr = tmem + kAccColumn + ab * G::ACC + col0 + ((uint32_t)((warp & 3) * 32) << 16);
             uint32_t r[CH];
-            if constexpr (CH == 4) {
+#pragma unroll
+            for (int c4 = 0; c4 < CH; c4 += 4)        // four columns per load
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];\n"
-                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                             : "r"(taddr)
+                             : "=r"(r[c4]), "=r"(r[c4 + 1]), "=r"(r[c4 + 2]), "=r"(r[c4 + 3])
+                             : "r"(taddr + c4)
                              : "memory");
-            } else {
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
-                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                             : "r"(taddr)
-                             : "memory");
-            }
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
@@ -333,18 +329,18 @@ extern "C" {
 using namespace b200;
 
 size_t b200_qmm_umma_workspace_bytes(int M, int K) {
-    if (M < 1 || M > 32 || K < kChunkK || (K % kChunkK) != 0) return 0;
-    const int nt = M <= 16 ? 16 : 32;
+    if (M < 1 || M > 128 || K < kChunkK || (K % kChunkK) != 0) return 0;
+    const int nt = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     return 256 + (size_t)(K / kChunkK) * (nt / 8) * kSBO;
 }
 
 int b200_qmm_umma(const void* x, const void* w_tiled, const void* bias, void* y, int M, int N, int K, void* workspace,
                   size_t workspace_bytes, void* stream) {
-    if (!x || !w_tiled || !y || !workspace || M < 1 || M > 32 || N < kItemRows || K < kChunkK) return B200_EINVAL;
+    if (!x || !w_tiled || !y || !workspace || M < 1 || M > 128 || N < kItemRows || K < kChunkK) return B200_EINVAL;
     if ((N % kItemRows) != 0 || (K % kChunkK) != 0) return B200_EUNSUPPORTED;
     if (!aligned16(x) || !aligned16(w_tiled) || !aligned16(y) || !aligned16(workspace)) return B200_EALIGN;
     if (workspace_bytes < b200_qmm_umma_workspace_bytes(M, K)) return B200_EWORKSPACE;
-    const int nt = M <= 16 ? 16 : 32;
+    const int nt = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     __half* xc = reinterpret_cast<__half*>(static_cast<char*>(workspace) + 256);
     const int units = nt * (K / 8);
@@ -357,7 +353,12 @@ int b200_qmm_umma(const void* x, const void* w_tiled, const void* bias, void* y,
     p.y = static_cast<__half*>(y);
     p.err = static_cast<int*>(workspace);
     p.M = M; p.N = N; p.K = K;
-    return nt == 16 ? launch_umma<16>(p, st) : launch_umma<32>(p, st);
+    switch (nt) {
+        case 16: return launch_umma<16>(p, st);
+        case 32: return launch_umma<32>(p, st);
+        case 64: return launch_umma<64>(p, st);
+        default: return launch_umma<128>(p, st);
+    }
 }
 
 }  // extern "C"

@@ -119,14 +119,14 @@ _umma_ws = {}
 
 
 def matmul_umma(x, wt, n, *, bias=None, out=None):
-    """``x (M<=32, K) @ W.T`` on re-laid-out weights ``wt`` through the tcgen05 tensor cores
+    """``x (M<=128, K) @ W.T`` on re-laid-out weights ``wt`` through the tcgen05 tensor cores
     (``b200_qmm_umma``; ``n`` and K multiples of 128, plain epilogue)."""
     _lib.require_cuda(x, wt)
     m, k = x.shape
     y = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=x.device)
     need = _lib.lib().b200_qmm_umma_workspace_bytes(m, k)
     if need == 0:
-        raise _lib.B200Error("b200_qmm_umma: need 1 <= M <= 32 and K a multiple of 128")
+        raise _lib.B200Error("b200_qmm_umma: need 1 <= M <= 128 and K a multiple of 128")
     key = (x.device, torch.cuda.current_stream(x.device).cuda_stream)
     ws = _umma_ws.get(key)
     if ws is None or ws.numel() < need:

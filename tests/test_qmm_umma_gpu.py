@@ -9,7 +9,8 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("m,n,k,bias", [(1, 128, 128, False), (8, 256, 896, True), (16, 1280, 3584, False),
-                                        (24, 384, 1024, True), (32, 2048, 512, False)])
+                                        (24, 384, 1024, True), (32, 2048, 512, False), (50, 256, 640, True),
+                                        (64, 1152, 896, False), (100, 384, 2048, True), (128, 1280, 1024, False)])
 def test_umma_matches_gold_and_streaming_kernel(be, cuda, m, n, k, bias):
     g = torch.Generator().manual_seed(100 + m)
     w = torch.randn(n, k, generator=g) * 0.02
@@ -21,7 +22,8 @@ def test_umma_matches_gold_and_streaming_kernel(be, cuda, m, n, k, bias):
     y = be.qmm_kernel.matmul_umma(x.to(dev), wt, n, bias=None if bv is None else bv.to(dev))
     torch.cuda.synchronize()
     assert be.qmm_kernel.umma_error(dev) == 0
-    y_t = be.qmm_kernel.matmul_tiled(x.to(dev), wt, n, bias=None if bv is None else bv.to(dev))
+    y_t = torch.cat([be.qmm_kernel.matmul_tiled(x[r:r + 32].to(dev), wt, n, bias=None if bv is None else bv.to(dev))
+                     for r in range(0, m, 32)])          # the streaming kernel takes 32 rows at a time
     gold = qmm_ref.qmm_gold(x.numpy(), wq.numpy().view(np.uint32), s.numpy(), b.numpy())
     if bv is not None:
         gold = gold + bv.numpy().astype(np.float64)
@@ -40,5 +42,5 @@ def test_umma_rejects_unsupported_shapes(be, cuda):
     y = torch.zeros(8, 192, dtype=torch.float16, device=dev)
     p = be._lib.ptr
     assert lib.b200_qmm_umma(p(x), p(ws), None, p(y), 8, 192, 256, p(ws), ws.numel(), None) == -3      # N % 128
-    assert lib.b200_qmm_umma(p(x), p(ws), None, p(y), 33, 128, 256, p(ws), ws.numel(), None) == -1     # M > 32
+    assert lib.b200_qmm_umma(p(x), p(ws), None, p(y), 129, 128, 256, p(ws), ws.numel(), None) == -1    # M > 128
     assert lib.b200_qmm_umma(p(x), p(ws), None, p(y), 8, 128, 256, p(ws), 64, None) == -4              # workspace
