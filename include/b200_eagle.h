@@ -47,6 +47,12 @@ int b200_last_cuda_error(void);
  * predecessor drains and waits on the device before touching dependent data); 0 turns the launch
  * attribute off (plain stream order).  Process-wide; default on. */
 void b200_set_pdl(int enabled);
+/* Every device-side wait on another CTA or another GPU (grid barrier and all-GPU barrier of b200_forward,
+ * the peer flags of b200_tp_argmax_combine) polls a bounded number of times, then sets an error word the host
+ * can read and lets the kernel run to its end.  `polls` replaces the built-in limits (a few seconds) for
+ * launches made after the call; 0 restores them.  Process-wide.  Meant for hosts that want a tighter
+ * failure-detection time, and for testing the give-up path without a failing peer. */
+void b200_set_wait_limit(unsigned int polls);
 
 /* Bytes of scratch b200_qmm / b200_qmm_fused want for a given problem (split-K partial sums and
  * tile counters).  0 means the problem runs without scratch. */
@@ -94,11 +100,14 @@ int b200_qmm_fused(const void* x, const uint32_t* wq, const void* scales, const 
  * the split-K scratch is a fixed 4 MiB array inside the library image instead of a caller buffer:
  * nothing is allocated or freed, by this call or by anything it calls.  Every GPU that loads the
  * library carries those 4 MiB until the process exits.
- *   - Problems whose scratch need (b200_qmm_workspace_bytes) exceeds
+ *   - Problems whose split-K scratch for the plain product (what b200_qmm itself would use; the
+ *     gate/up pair counted by b200_qmm_workspace_bytes does not run here) exceeds
  *     b200_qmm_noalloc_max_scratch_bytes() are refused with B200_ELIMIT; nothing is launched
- *     (e.g. 32 rows x 4608 x 3584 wants 5.6 MiB: use b200_qmm with a caller buffer for those).
+ *     (e.g. 32 rows x 3584 x 18944 wants 5.3 MiB: use b200_qmm with a caller buffer for those).
  *   - The first call on each device looks up the array's device address (with that device
- *     current); make that first call outside any stream capture.
+ *     current); make that first call outside any stream capture, and do not let two host threads
+ *     make their first call on the same device at the same time (the cached address is written
+ *     without a lock; both would store the same value).
  *   - All calls on a device share the one array and it keeps the previous call's contents; the call
  *     re-zeroes the part that must start at zero.  Two calls that overlap on the GPU (different
  *     streams, no ordering) race on it: order them.

@@ -46,6 +46,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_last_cuda_error.restype = i32
     l.b200_set_pdl.restype = None
     l.b200_set_pdl.argtypes = [i32]
+    l.b200_set_wait_limit.restype = None
+    l.b200_set_wait_limit.argtypes = [ctypes.c_uint]
     l.b200_qmm_workspace_bytes.restype = sz
     l.b200_qmm_workspace_bytes.argtypes = [i32, i32, i32]
     l.b200_qmm.restype = i32

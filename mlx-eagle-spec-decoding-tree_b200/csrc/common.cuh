@@ -28,6 +28,10 @@ inline int check_launch() {
 // kernel wrote and before its first global write.  0 disables the launch attribute.
 extern int g_use_pdl;
 
+// Poll limit of the device-side waits on other CTAs or other GPUs (grid barrier, all-GPU barrier, argmax
+// combine), set by b200_set_wait_limit; 0 = each kernel's built-in default (seconds).
+extern unsigned g_wait_limit;
+
 template <typename... KArgs, typename... Args>
 inline void launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                           Args&&... args) {

@@ -122,6 +122,7 @@ struct FwdParams {
     int head_rows;                 // rows of the vocabulary projection held here (a vocabulary shard under TP)
     int attn_fused_max;            // single-phase attention while the cache spans at most this many key blocks
     unsigned phase_mask;           // bit per phase kind (K_*): kinds to run; all ones normally
+    uint32_t grid_wait_limit, tp_wait_limit;   // polls before a wait on other CTAs / other GPUs gives up
     alignas(64) CUtensorMap kvmap; // the whole KV cache as a 2-D fp16 tensor [rows][head_dim], 64 x 64 boxes, 128-byte swizzle
     long long* timeline;           // optional [CTAs][timeline_pitch][8] timer stamps per barrier: arrive, leave, then
                                    // six stamps inside the matmul phase that ends at that barrier
@@ -234,7 +235,7 @@ __device__ void grid_barrier(const FwdParams& p, Ctx& c) {
         const int target = (int)(c.lbar * gridDim.x);
         bool ok = false;
         const volatile int* bar = p.sync + kSyncBar;
-        for (uint32_t i = 0; i < kGridWaitLimit; i++) {
+        for (uint32_t i = 0; i < p.grid_wait_limit; i++) {
             if (*bar >= target) { ok = true; break; }
         }
         if (!ok) raise_error(p, c, 10);
@@ -254,7 +255,7 @@ __device__ bool producer_grid_wait(const FwdParams& p, Ctx& c, uint32_t need_epo
     int ok = 1;
     if (need_epoch > 0 && c.lane == 0) {
         ok = 0;
-        for (uint32_t i = 0; i < (kGridWaitLimit << 4) && !*c.abort_flag; i++) {
+        for (uint32_t i = 0; i < (p.grid_wait_limit << 4) && !*c.abort_flag; i++) {
             if (*c.s_epoch >= need_epoch) { ok = 1; break; }
         }
         if (!ok && !*c.abort_flag) raise_error(p, c, 11);
@@ -327,7 +328,7 @@ __device__ void tp_all_barrier(const FwdParams& p, Ctx& c) {
         const unsigned target = (c.tp_seq0 + c.tpx + 1) * (unsigned)p.tp_world * gridDim.x;
         const unsigned* mine = reinterpret_cast<const unsigned*>(p.tp_peers[p.tp_rank] + kTpFwdArrive);
         bool ok = false;
-        for (uint32_t i = 0; i < kTpWaitLimit; i++) {
+        for (uint32_t i = 0; i < p.tp_wait_limit; i++) {
             if ((int)(ld_acquire_sys(mine) - target) >= 0) { ok = true; break; }
         }
         if (!ok) raise_error(p, c, 12);
@@ -2006,6 +2007,8 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
         }
     }
     p.phase_mask = d->phase_mask ? (unsigned)d->phase_mask : 0xffu;
+    p.grid_wait_limit = g_wait_limit ? (g_wait_limit < (1u << 27) ? g_wait_limit : (1u << 27)) : kGridWaitLimit;
+    p.tp_wait_limit = g_wait_limit ? g_wait_limit : kTpWaitLimit;
     p.attn_fused_max = d->attn_split_blocks > 0 ? d->attn_split_blocks - 1 : (d->attn_split_blocks < 0 ? 0 : 32);
     p.timeline = static_cast<long long*>(d->timeline);
     p.timeline_pitch = d->timeline ? d->timeline_pitch : 0;

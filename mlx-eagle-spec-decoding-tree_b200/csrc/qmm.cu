@@ -307,12 +307,9 @@ Plan make_plan(int M, int N, int K, bool dual, long long ws_bytes) {
 template <int MT, int S, int WN, bool DUAL>
 int launch_one(const QmmParams& p, const Plan& pl, cudaStream_t stream) {
     auto kern = qmm_kernel<MT, S, WN, DUAL>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)
-            return check_launch();
-        attr_set = true;
-    }
+    // the attribute is per device: set it on every launch (a process may drive several GPUs)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)
+        return check_launch();
     dim3 grid(pl.row_tiles, pl.splits, 1);
     launch_kernel(kern, dim3(grid), dim3(WN * 32), pl.smem_bytes, stream, p);
     return check_launch();
@@ -454,7 +451,10 @@ int b200_qmm_noalloc(const void* x, const uint32_t* wq, const void* scales, cons
                      const void* bias, void* y, int M, int N, int K, int group_size, int dtype, void* stream) {
     if (M < 1 || M > 32) return B200_EINVAL;
     // The problem must fit the fixed scratch with the split it would normally use; no silent downgrade.
-    const size_t need = b200_qmm_workspace_bytes(M, N, K);
+    // (Only the plain epilogue runs here, so only its plan counts, not the gate/up pair's.)
+    if (N < 8 || K < b200::kChunkK || (K % b200::kChunkK) != 0) return B200_EINVAL;
+    const b200::Plan plain = b200::make_plan(M, N, K, false, -1);
+    const size_t need = plain.splits > 1 ? b200::kCounterBytes + plain.partial_bytes : 0;
     if (need > b200::kStaticScratchBytes) return B200_ELIMIT;
     void* scratch = nullptr;
     int rc = b200::static_scratch_address(&scratch);

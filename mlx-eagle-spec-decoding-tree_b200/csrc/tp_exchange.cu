@@ -15,7 +15,8 @@ namespace {
 constexpr unsigned kCombineWaitLimit = 1u << 22;     // polls of one flag before giving up
 
 __global__ void __launch_bounds__(32) tp_argmax_combine_kernel(unsigned long long* __restrict__ best_key, int R,
-                                                               unsigned index_offset, TpPeers peers, int world, int rank) {
+                                                               unsigned index_offset, TpPeers peers, int world, int rank,
+                                                               unsigned wait_limit) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ int s_fail;
@@ -34,7 +35,7 @@ __global__ void __launch_bounds__(32) tp_argmax_combine_kernel(unsigned long lon
         st_release_sys(reinterpret_cast<unsigned*>(peers.p[t] + kTpKeyFlags + rank * kTpFlagStride), seq + 1);
         const unsigned* flag = reinterpret_cast<const unsigned*>(own + kTpKeyFlags + t * kTpFlagStride);
         bool ok = false;
-        for (unsigned i = 0; i < kCombineWaitLimit; i++) {
+        for (unsigned i = 0; i < wait_limit; i++) {
             if ((int)(ld_acquire_sys(flag) - (seq + 1)) >= 0) { ok = true; break; }
         }
         if (!ok) s_fail = 1;
@@ -126,7 +127,8 @@ int b200_tp_argmax_combine(unsigned long long* best_key, int R, unsigned int ind
         peers.p[r] = static_cast<unsigned char*>(tp_peers[r]);
     }
     b200::launch_kernel(b200::tp_argmax_combine_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream),
-                        best_key, R, index_offset, peers, tp_world, tp_rank);
+                        best_key, R, index_offset, peers, tp_world, tp_rank,
+                        b200::g_wait_limit ? b200::g_wait_limit : b200::kCombineWaitLimit);
     return b200::check_launch();
 }
 

@@ -21,7 +21,12 @@ constexpr int kMaxPool = kK + kK * kK * kMaxDepth;
 
 // ctl words
 enum { CTL_BASE_LEN = 0, CTL_DRAFT_LEN = 1, CTL_ACCEPT = 2, CTL_NGEN = 3, CTL_STEP = 4, CTL_DRAFT_OFF = 5,
-       CTL_OUT_CAP = 6, CTL_LAST_BEST = 7, CTL_WORDS = 16 };
+       CTL_OUT_CAP = 6, CTL_LAST_BEST = 7,
+       CTL_LOG_CAP = 8,      // steps the step log can hold; later steps are counted but not logged
+       CTL_EOS = 9,          // end-of-sequence token id + 1 (0 = none)
+       CTL_DONE = 10,        // set once an accepted token was the end-of-sequence token
+       CTL_STOP_N = 11,      // generated-token count up to and including that token
+       CTL_WORDS = 16 };
 
 // ---------------------------------------------------------------- ordering keys
 __device__ __forceinline__ uint32_t order_bits(float f) {
@@ -493,8 +498,20 @@ __global__ void tree_accept_kernel(const AcceptParams p) {
         p.y[accept] = bonus;
         if (n + accept < cap) p.out_tokens[n + accept] = bonus;
         const int step = p.ctl[CTL_STEP];
-        p.step_log[2 * step] = accept;
-        p.step_log[2 * step + 1] = best;
+        if (step < p.ctl[CTL_LOG_CAP]) {                                // the log has a fixed capacity; CTL_STEP keeps counting
+            p.step_log[2 * step] = accept;
+            p.step_log[2 * step + 1] = best;
+        }
+        const int eos1 = p.ctl[CTL_EOS];
+        if (eos1 > 0 && !p.ctl[CTL_DONE]) {                             // first end-of-sequence token among this step's tokens
+            for (int j = 0; j <= accept; j++) {
+                if (p.y[j] == eos1 - 1) {
+                    p.ctl[CTL_DONE] = 1;
+                    p.ctl[CTL_STOP_N] = n + j + 1;
+                    break;
+                }
+            }
+        }
         p.ctl[CTL_DRAFT_LEN] = p.ctl[CTL_DRAFT_OFF];                    // draft cache rewound (mlx_eagle.py:593-594)
         p.ctl[CTL_BASE_LEN] = P + accept + 1;                           // mlx_eagle.py:376
         p.ctl[CTL_ACCEPT] = accept;

@@ -30,6 +30,7 @@ from .llama import KVCache, Model, ModelArgs, MAX_ROWS, shape_preset
 K = 8                      # children per node (mlx_eagle.py:750)
 RETRIEVE_W = 9             # row width of the retrieve-index matrix (max depth 7 + 2)
 CTL_BASE_LEN, CTL_DRAFT_LEN, CTL_ACCEPT, CTL_NGEN, CTL_STEP, CTL_DRAFT_OFF, CTL_OUT_CAP, CTL_BEST = range(8)
+CTL_LOG_CAP, CTL_EOS, CTL_DONE, CTL_STOP_N = 8, 9, 10, 11
 
 
 class SpecDecoder:
@@ -84,8 +85,9 @@ class SpecDecoder:
             self.kernel_launches_per_step += 1 if base_model.tp.peers is not None else 2
 
     # ------------------------------------------------------------------ prompt ingestion
-    def prefill(self, prompt: torch.Tensor, prefill_step_size: int = 512) -> int:
-        """Feed the prompt to both models (``mlx_eagle.py:522-535``) and take the first token greedily."""
+    def prefill(self, prompt: torch.Tensor, prefill_step_size: int = 512, eos_token_id: Optional[int] = None) -> int:
+        """Feed the prompt to both models (``mlx_eagle.py:522-535``) and take the first token greedily.
+        ``eos_token_id`` arms the device-side stop test of ``b200_tree_accept`` for this request."""
         prompt = prompt.reshape(-1).to(torch.int32).to(self.device)
         n = prompt.numel()
         need = n + 8 * (self.depth + 1) + 40
@@ -101,6 +103,10 @@ class SpecDecoder:
         host[CTL_BASE_LEN] = n
         host[CTL_DRAFT_LEN] = n
         host[CTL_OUT_CAP] = self.out_tokens.numel()
+        host[CTL_LOG_CAP] = self.max_steps
+        host[CTL_EOS] = 0 if eos_token_id is None else int(eos_token_id) + 1
+        if eos_token_id is not None and first == int(eos_token_id):
+            host[CTL_DONE], host[CTL_STOP_N] = 1, 0
         self.ctl.copy_(host)
         self.y.zero_()
         self.y[0] = first
@@ -206,22 +212,31 @@ class SpecDecoder:
             self.capture()
         torch.cuda.synchronize(self.device)
 
-    def generate(self, prompt: torch.Tensor, max_tokens: int = 128, N: int = 20, prefill_step_size: int = 512):
+    def generate(self, prompt: torch.Tensor, max_tokens: int = 128, N: int = 20, prefill_step_size: int = 512,
+                 eos_token_id: Optional[int] = None, clip: bool = False):
         """Greedy tree-speculative generation for one prompt (host or device tensor of token ids).
 
         Runs at most ``N`` steps and stops at the first step boundary where ``max_tokens`` were generated
         (``mlx_eagle.py:544-546``).  Steps are enqueued ahead of the host: the stop test reads a pinned
         copy of the device counters that trails the device by two steps, so the device never waits for
         the host; steps launched past the stop point are discarded from the result.
+
+        Two stop rules the reference lacks: with ``eos_token_id`` the request ends at the first generated
+        token equal to it (found on the device by ``b200_tree_accept``; the token itself is kept, everything
+        after it is dropped), and ``clip=True`` cuts the result to exactly ``max_tokens`` generated tokens
+        instead of a whole number of steps.  The token fed to the step that never ran (the last ``y``, which
+        the reference computes but never prints, ``mlx_eagle.py:573,596-601``) is part of the result.
+
         Returns a dict: tokens (first token + every step's accepted tokens and bonus token),
-        accept_lengths, generated, steps, steps_launched, seconds (decode loop only, as the reference
-        times it, ``:541``), tokens_per_second, and the byte counts copied between host and device.
+        accept_lengths, generated, steps, steps_launched, finish_reason ("eos", "length" or "steps"),
+        seconds (decode loop only, as the reference times it, ``:541``), tokens_per_second, and the byte
+        counts copied between host and device.
         """
         if N + 4 > self.max_steps or max_tokens + 8 * 4 > self.out_tokens.numel():
             raise _lib.B200Error("generate: N / max_tokens exceed the decoder's log capacity")
         if prompt.numel() + max_tokens + 8 * (self.depth + 2) + self.T + 64 > self.base_cache.rows:
             raise _lib.B200Error("generate: prompt + max_tokens do not fit the KV cache")
-        first = self.prefill(prompt, prefill_step_size)
+        first = self.prefill(prompt, prefill_step_size, eos_token_id)
         torch.cuda.synchronize(self.device)
         tic = time.perf_counter()
         lead = 2
@@ -230,7 +245,8 @@ class SpecDecoder:
             self._events = [torch.cuda.Event() for _ in range(4)]
         pinned, events = self._pinned, self._events
         i = 0
-        while i < N:
+        first_is_eos = eos_token_id is not None and first == int(eos_token_id)
+        while i < N and not first_is_eos:
             self.replay()
             pinned[i % 4].copy_(self.ctl, non_blocking=True)
             events[i % 4].record()
@@ -238,28 +254,37 @@ class SpecDecoder:
             j = i - 1 - lead
             if j >= 0:
                 events[j % 4].synchronize()
-                if int(pinned[j % 4][CTL_NGEN]) >= max_tokens:
+                if int(pinned[j % 4][CTL_NGEN]) >= max_tokens or int(pinned[j % 4][CTL_DONE]):
                     break
         torch.cuda.synchronize(self.device)
         total = time.perf_counter() - tic
         self.base.check_fused_error()
         self.draft.check_fused_error()
         steps_run = i
+        ctl = self.ctl.cpu().tolist()
+        stop_n = ctl[CTL_STOP_N] if ctl[CTL_DONE] else None
         log = self.step_log[: 2 * steps_run].cpu().tolist()
         produced = sum(1 + log[2 * s] for s in range(steps_run))
         toks = self.out_tokens[:produced].cpu().tolist()
         n, steps, accept_lengths = 0, 0, []
         for s in range(steps_run):
-            if n >= max_tokens:
+            if n >= max_tokens or (stop_n is not None and n >= stop_n):
                 break
             accept_lengths.append(log[2 * s])
             n += 1 + log[2 * s]
             steps += 1
+        reason = "steps"
+        if stop_n is not None and stop_n <= n:
+            n, reason = stop_n, "eos"
+        if n >= max_tokens:
+            reason = "length" if not (reason == "eos" and n <= max_tokens) else "eos"
+            if clip:
+                n = max_tokens
         d2h = steps_run * 64 + 8 * steps_run + 4 * produced
         return dict(tokens=[first] + toks[:n], generated=n, steps=steps, steps_launched=steps_run,
                     accept_lengths=accept_lengths, mean_tokens_per_step=n / max(steps, 1), seconds=total,
                     tokens_per_second=produced / total if total > 0 else 0.0, produced=produced,
-                    h2d_bytes=int(prompt.numel()) * 4, d2h_bytes=d2h)
+                    finish_reason=reason, h2d_bytes=int(prompt.numel()) * 4, d2h_bytes=d2h)
 
     # ------------------------------------------------------------------ host views
     def read_ctl(self) -> List[int]:
@@ -340,9 +365,11 @@ def spec_step(dec: SpecDecoder):
 
 def generate_step(prompt: torch.Tensor, base_model: Model, draft_model: Model, prefill_step_size: int = 512,
                   k: int = 8, depth: int = 5, verify_num_tokens: int = 31, max_tokens: int = 128, tokenizer=None,
-                  N: int = 20, use_graph: bool = True, verbose: bool = True):
+                  N: int = 20, use_graph: bool = True, verbose: bool = True, eos_token_id: Optional[int] = None,
+                  clip: bool = False):
     """Greedy tree-speculative generation (``mlx_eagle.py:503-606``), same arguments as the reference
-    (``verify_num_tokens`` is limited to 31 here).  Builds a ``SpecDecoder`` for the request, captures
+    (``verify_num_tokens`` is limited to 31 here) plus the two stop rules of ``SpecDecoder.generate``
+    (``eos_token_id``, ``clip``).  Builds a ``SpecDecoder`` for the request, captures
     its step graph and calls ``SpecDecoder.generate``; prints the reference's three summary lines.
     Returns the result dict of ``generate`` plus the decoder under ``"decoder"``."""
     rows = prompt.numel() + max_tokens + 8 * (depth + 2) + verify_num_tokens + 128
@@ -350,7 +377,8 @@ def generate_step(prompt: torch.Tensor, base_model: Model, draft_model: Model, p
     dec = SpecDecoder(base_model, draft_model, depth, verify_num_tokens, rows,
                       max_out_tokens=max_tokens + 128, max_steps=N + 8, k=k)
     dec.warmup(capture=use_graph)
-    stats = dec.generate(prompt, max_tokens=max_tokens, N=N, prefill_step_size=prefill_step_size)
+    stats = dec.generate(prompt, max_tokens=max_tokens, N=N, prefill_step_size=prefill_step_size,
+                         eos_token_id=eos_token_id, clip=clip)
     if verbose:
         if tokenizer is not None:
             print(tokenizer.decode(stats["tokens"]))
@@ -375,14 +403,16 @@ def parse_args(argv=None):
     p.add_argument("--max-tokens", type=int, default=300)
     p.add_argument("--max-generation-steps", "-N", type=int, default=300)
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--eos-token-id", type=int, default=None, help="stop at the first generated token with this id")
+    p.add_argument("--clip", action="store_true", help="cut the output to exactly --max-tokens tokens")
     return p.parse_args(argv)
 
 
 def main(argv=None):
     args = parse_args(argv)
     dev = torch.device("cuda", torch.cuda.current_device())
-    draft = Model.random_init(shape_preset(args.draft_model), args.seed + 1, dev)
-    base = Model.random_init(shape_preset(args.base_model), args.seed + 2, dev)
+    draft = Model.random_init(shape_preset(args.draft_model), args.seed + 1, dev).relayout()
+    base = Model.random_init(shape_preset(args.base_model), args.seed + 2, dev).relayout()
     if "," in args.prompt or not args.prompt.isdigit():
         ids = torch.tensor([int(t) for t in args.prompt.split(",")], dtype=torch.int32)
     else:
@@ -390,7 +420,8 @@ def main(argv=None):
         ids = torch.randint(0, min(draft.args.vocab_size, base.args.vocab_size), (int(args.prompt),), generator=g,
                             dtype=torch.int32)
     generate_step(ids, base, draft, k=8, depth=args.depth, verify_num_tokens=args.verify_num_tokens,
-                  max_tokens=args.max_tokens, prefill_step_size=512, N=args.max_generation_steps)
+                  max_tokens=args.max_tokens, prefill_step_size=512, N=args.max_generation_steps,
+                  eos_token_id=args.eos_token_id, clip=args.clip)
 
 
 if __name__ == "__main__":

@@ -67,9 +67,11 @@ def spec_step(y, base_model, draft_model, base_cache, draft_cache, accept_length
 
 
 def generate_step(prompt, base_model: OracleModel, draft_model: OracleModel, prefill_step_size=512, k=8, depth=5,
-                  verify_num_tokens=15, max_tokens=128, N=20, cache_rows=None):
+                  verify_num_tokens=15, max_tokens=128, N=20, cache_rows=None, eos_token_id=None, clip=False):
     """Returns ``dict(tokens, accept_lengths, steps, seconds, tokens_per_second)``; timer starts after
-    prompt ingestion (``mlx_eagle.py:541``)."""
+    prompt ingestion (``mlx_eagle.py:541``).  ``eos_token_id`` / ``clip`` are the two stop rules the
+    product adds to the reference loop (stop after the first end-of-sequence token; cut to exactly
+    ``max_tokens``), restated here so the GPU loop can be checked against them."""
     y = np.asarray(prompt).reshape(-1)
     rows = cache_rows or (y.size + max_tokens + 8 * (depth + 2) + verify_num_tokens + 128)
     base_cache = make_prompt_cache(base_model, rows)
@@ -85,8 +87,10 @@ def generate_step(prompt, base_model: OracleModel, draft_model: OracleModel, pre
     n, accept_length, accept_lengths = 0, 0, []
     tic = time.perf_counter()
     steps = 0
+    finish = "steps"
+    stop_n = 0 if (eos_token_id is not None and tokens[0] == eos_token_id) else None
     for _ in range(N):
-        if n >= max_tokens:
+        if n >= max_tokens or stop_n is not None:
             break
         tpi, mi, dt, logits, base_offset, draft_offset = spec_step(
             y, base_model, draft_model, base_cache, draft_cache, accept_length, k, depth, verify_num_tokens)
@@ -105,8 +109,17 @@ def generate_step(prompt, base_model: OracleModel, draft_model: OracleModel, pre
         y = np.concatenate([accepted_tokens.astype(np.int64), [next_token]])
         tokens.extend(int(t) for t in y)
         accept_lengths.append(int(accept_length))
+        if eos_token_id is not None and eos_token_id in [int(t) for t in y]:
+            stop_n = n + [int(t) for t in y].index(eos_token_id) + 1
         n += 1 + accept_length
         steps += 1
     total = time.perf_counter() - tic
-    return dict(tokens=tokens, generated=n, accept_lengths=accept_lengths, steps=steps, seconds=total,
+    if stop_n is not None:
+        n, finish = stop_n, "eos"
+    if n >= max_tokens:
+        finish = "eos" if (finish == "eos" and n <= max_tokens) else "length"
+        if clip:
+            n = max_tokens
+    tokens = tokens[: 1 + n]
+    return dict(tokens=tokens, generated=n, finish_reason=finish, accept_lengths=accept_lengths, steps=steps, seconds=total,
                 tokens_per_second=n / total if total > 0 else 0.0, base_cache=base_cache, draft_cache=draft_cache)

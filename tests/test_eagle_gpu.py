@@ -79,3 +79,55 @@ def test_bad_configurations_are_rejected(be, models):
         be.SpecDecoder(base, draft, depth=0, verify_num_tokens=15, cache_rows=256)     # README: depth 0 needs T=7
     with pytest.raises(be._lib.B200Error):
         be.SpecDecoder(base, draft, depth=3, verify_num_tokens=15, cache_rows=256, k=4)
+
+
+def test_eos_stop_clipping_and_final_token_match_the_oracle_loop(be, models):
+    """The stop rules a serving loop needs on top of the reference's: stop at an end-of-sequence token (found on
+    the device), cut to exactly max_tokens, keep the last token (``mlx_eagle.py:544-546,573,596-601``)."""
+    args, base, draft, states = models
+    rng = np.random.default_rng(7)
+    prompt = rng.integers(0, args.vocab_size, 33)
+    ob, od = model_ref.OracleModel(args, states[0]), model_ref.OracleModel(args, states[1])
+    free = eagle_ref.generate_step(prompt, ob, od, depth=3, verify_num_tokens=15, max_tokens=40, N=40)
+    # an "end of sequence" that the free-running generation produces in the middle of a multi-token step
+    steps_tok = []
+    n = 1
+    for a in free["accept_lengths"]:
+        steps_tok.append(free["tokens"][n:n + a + 1])
+        n += a + 1
+    pick = next((st for st in steps_tok[2:] if len(st) > 1), steps_tok[3])
+    eos = pick[min(1, len(pick) - 1)]
+    if eos in free["tokens"][:free["tokens"].index(eos)]:
+        pytest.skip("token repeats earlier")
+    ref = eagle_ref.generate_step(prompt, ob, od, depth=3, verify_num_tokens=15, max_tokens=40, N=40, eos_token_id=eos)
+    res = be.generate_step(torch.from_numpy(prompt), base, draft, depth=3, verify_num_tokens=15, max_tokens=40, N=40,
+                           verbose=False, eos_token_id=eos)
+    assert res["finish_reason"] == ref["finish_reason"] == "eos"
+    assert res["tokens"] == ref["tokens"] and res["tokens"][-1] == eos and res["tokens"].count(eos) == 1
+    assert res["generated"] == ref["generated"] == len(res["tokens"]) - 1
+    # exact clipping: 17 tokens, not a whole number of steps
+    ref = eagle_ref.generate_step(prompt, ob, od, depth=3, verify_num_tokens=15, max_tokens=17, N=40, clip=True)
+    res = be.generate_step(torch.from_numpy(prompt), base, draft, depth=3, verify_num_tokens=15, max_tokens=17, N=40,
+                           verbose=False, clip=True)
+    assert res["tokens"] == ref["tokens"] == free["tokens"][:18] and res["generated"] == 17
+    assert res["finish_reason"] == ref["finish_reason"] == "length"
+    # the first token itself is the end of sequence: no step runs
+    res = be.generate_step(torch.from_numpy(prompt), base, draft, depth=3, verify_num_tokens=15, max_tokens=17, N=40,
+                           verbose=False, eos_token_id=free["tokens"][0])
+    assert res["tokens"] == [free["tokens"][0]] and res["generated"] == 0 and res["steps_launched"] == 0
+
+
+def test_step_log_does_not_overflow_when_replayed_past_its_capacity(be, models):
+    """Replaying more steps than the step log holds must not write past it (the counters keep counting)."""
+    args, base, draft, _ = models
+    dec = be.SpecDecoder(base, draft, depth=3, verify_num_tokens=15, cache_rows=512, max_out_tokens=64, max_steps=6)
+    big = torch.full((2 * 6 + 64,), -7, dtype=torch.int32, device=dec.device)
+    dec.step_log = big[:12]                      # the log, followed by a canary in the same allocation
+    dec.prefill(torch.arange(3, 20, dtype=torch.int32))
+    dec.step_log.fill_(-7)
+    for _ in range(9):
+        dec.step()
+    torch.cuda.synchronize()
+    assert int(dec.ctl[4]) == 9                  # CTL_STEP
+    assert bool((big[12:] == -7).all())          # nothing written behind the log
+    assert bool((big[:12:2] >= 0).all())         # the six logged steps are there

@@ -96,3 +96,18 @@ def test_random_draft_still_yields_the_targets_greedy_tokens(tiny):
     plain, _ = _plain_greedy(base, prompt, len(res["tokens"]))
     assert res["tokens"][:6] == plain[:6]
     assert res["generated"] == sum(1 + a for a in res["accept_lengths"])
+
+
+def test_stop_rules_of_the_oracle_loop(tiny):
+    """End-of-sequence stop and exact clipping, as restated for the product's loop: prefixes of the free run."""
+    args, base, _ = tiny
+    rng = np.random.default_rng(2)
+    prompt = rng.integers(0, args.vocab_size, 10)
+    free = eagle_ref.generate_step(prompt, base, base, depth=2, verify_num_tokens=7, max_tokens=16, N=8)
+    clipped = eagle_ref.generate_step(prompt, base, base, depth=2, verify_num_tokens=7, max_tokens=5, N=8, clip=True)
+    assert clipped["tokens"] == free["tokens"][:6] and clipped["generated"] == 5 and clipped["finish_reason"] == "length"
+    eos = free["tokens"][4]
+    first = free["tokens"].index(eos)
+    stopped = eagle_ref.generate_step(prompt, base, base, depth=2, verify_num_tokens=7, max_tokens=16, N=8, eos_token_id=eos)
+    assert stopped["tokens"] == free["tokens"][:first + 1] and stopped["finish_reason"] == "eos"
+    assert stopped["generated"] == first

@@ -57,7 +57,14 @@ def test_nothing_is_allocated_and_oversize_is_refused(be, cuda):
     assert limit == 4 << 20
     # more than 32 rows, or a shape whose scratch need exceeds the built-in array: refused, nothing launched
     assert lib.b200_qmm_noalloc(None, None, None, None, None, None, 33, 4608, 3584, 64, 0, None) == -1
+    # 32 x 4608 x 3584: the gate/up pair of that shape would want 5.6 MiB, but this entry point only runs the
+    # plain product, whose split needs 3.9 MiB: accepted, same bits as the ordinary entry point
     assert lib.b200_qmm_workspace_bytes(32, 4608, 3584) > limit
     x2, _, _, _, (x2d, wq2d, s2d, b2d) = _problem(be, cuda, 4608, 3584, 32, 4)
-    rc, _ = _noalloc(be, cuda, x2d, wq2d, s2d, b2d, 4608, 3584, 32)
+    rc, y2 = _noalloc(be, cuda, x2d, wq2d, s2d, b2d, 4608, 3584, 32)
+    assert rc == 0
+    assert torch.equal(y2, be.qmm_kernel.matmul(x2d, wq2d, s2d, b2d, 64)[0])
+    # 32 x 3584 x 18944: the plain product's own split wants 5.3 MiB: refused
+    x3, _, _, _, (x3d, wq3d, s3d, b3d) = _problem(be, cuda, 3584, 18944, 32, 5)
+    rc, _ = _noalloc(be, cuda, x3d, wq3d, s3d, b3d, 3584, 18944, 32)
     assert rc == -6
