@@ -276,7 +276,10 @@ typedef struct b200_forward_desc {
      * be zeroed (with no launch in flight anywhere) before the next pass. */
     int tp_world, tp_rank;
     int head_rows;
-    int reserved;
+    int grid_ctas;          /* CTAs of the persistent kernel: 0 = one per SM.  A small model (a draft whose layer is
+                             * a few MB) is bound by the latency of its device-wide phase boundaries, not by
+                             * bandwidth: fewer CTAs make every boundary cheaper and 16 to 64 SMs already pull 2 to
+                             * 6.5 TB/s.  Size the workspace with the same value. */
     void* tp_peers[8];
 } b200_forward_desc;
 

@@ -1802,16 +1802,14 @@ struct WsLayout {
     int nkb, qrp;
 };
 
-int g_fwd_grid = 0;
-int fwd_grid() {
-    if (g_fwd_grid == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;
-        g_fwd_grid = n;
-    }
-    return g_fwd_grid;
+// CTAs of a launch: one per SM of the current device, or the descriptor's smaller request.
+int fwd_grid(const b200_forward_desc* d) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+        n = 148;
+    if (d->grid_ctas > 0 && d->grid_ctas < n) n = d->grid_ctas;
+    return n;
 }
 
 
@@ -1832,11 +1830,13 @@ bool fwd_shape_ok(const b200_forward_desc* d) {
     } else if (d->tp_world < 0) {
         return false;
     }
+    if (d->grid_ctas < 0) return false;
     return true;
 }
 
-WsLayout fwd_layout(const b200_forward_desc* d, PhasePlan (&plan)[5]) {
-    const int grid = fwd_grid();
+WsLayout fwd_layout(const b200_forward_desc* d, PhasePlan (&plan)[5], int* grid_out = nullptr) {
+    const int grid = fwd_grid(d);
+    if (grid_out) *grid_out = grid;
     const int mp = ((d->M + 7) / 8) * 8;
     const int nqkv = (d->n_heads + 2 * d->n_kv_heads) * d->head_dim;
     const int mt = mp / 8;
@@ -1903,7 +1903,7 @@ int make_kv_map(CUtensorMap* map, void* cache, int layers, int hkv, int cap, int
 }
 
 template <int MT, int HD, bool TP>
-int launch_forward(const FwdParams& p, cudaStream_t stream) {
+int launch_forward(const FwdParams& p, int grid, cudaStream_t stream) {
     auto kern = forward_kernel<MT, HD, TP>;
     bool attr_set = false;
     if (!attr_set) {
@@ -1912,7 +1912,7 @@ int launch_forward(const FwdParams& p, cudaStream_t stream) {
         attr_set = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(fwd_grid());
+    cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kFwdThreads);
     cfg.dynamicSmemBytes = Geo<MT>::SMEM;
     cfg.stream = stream;
@@ -1926,10 +1926,10 @@ int launch_forward(const FwdParams& p, cudaStream_t stream) {
 }
 
 template <int MT>
-int launch_forward_hd(const FwdParams& p, cudaStream_t stream) {
+int launch_forward_hd(const FwdParams& p, int grid, cudaStream_t stream) {
     if (p.tp_world > 1)         // a shard: the variant with the exchange phases
-        return p.HD == 128 ? launch_forward<MT, 128, true>(p, stream) : launch_forward<MT, 64, true>(p, stream);
-    return p.HD == 128 ? launch_forward<MT, 128, false>(p, stream) : launch_forward<MT, 64, false>(p, stream);
+        return p.HD == 128 ? launch_forward<MT, 128, true>(p, grid, stream) : launch_forward<MT, 64, true>(p, grid, stream);
+    return p.HD == 128 ? launch_forward<MT, 128, false>(p, grid, stream) : launch_forward<MT, 64, false>(p, grid, stream);
 }
 
 }  // namespace
@@ -1962,7 +1962,8 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
     for (const void* q : al)
         if (!aligned16(q)) return B200_EALIGN;
     FwdParams p{};
-    const WsLayout w = fwd_layout(d, p.plan);
+    int grid = 0;
+    const WsLayout w = fwd_layout(d, p.plan, &grid);
     if (d->workspace_bytes < w.total) return B200_EWORKSPACE;
     p.M = d->M; p.mp = ((d->M + 7) / 8) * 8; p.rows_out = d->rows_out; p.H = d->hidden; p.I = d->intermediate; p.Hq = d->n_heads;
     p.Hkv = d->n_kv_heads; p.HD = d->head_dim; p.V = d->vocab; p.L = d->n_layers;
@@ -2014,10 +2015,10 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
     p.timeline_pitch = d->timeline ? d->timeline_pitch : 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch ((d->M + 7) / 8) {
-        case 1: return launch_forward_hd<1>(p, st);
-        case 2: return launch_forward_hd<2>(p, st);
-        case 3: return launch_forward_hd<3>(p, st);
-        default: return launch_forward_hd<4>(p, st);
+        case 1: return launch_forward_hd<1>(p, grid, st);
+        case 2: return launch_forward_hd<2>(p, grid, st);
+        case 3: return launch_forward_hd<3>(p, grid, st);
+        default: return launch_forward_hd<4>(p, grid, st);
     }
 }
 

@@ -142,7 +142,7 @@ class SpecDecoder:
                               p(self.topk_cs_index), p(f.tokens), p(f.pos), p(f.mask), p(f.prefix), st),
            "b200_tree_expand")
 
-    def _finalize_and_verify(self):
+    def _finalize(self):
         L, p, ck = _lib.lib(), _lib.ptr, _lib.check
         st = _lib.stream_ptr(self.device)
         f = self.base.fwd
@@ -150,8 +150,19 @@ class SpecDecoder:
                                 p(self.ctl), p(self.y), p(f.tokens), p(f.pos), p(f.mask), p(f.prefix),
                                 p(self.tree_position_ids), p(self.mask_index), p(self.draft_tokens),
                                 p(self.retrieve), p(self.tree_info), st), "b200_tree_finalize")
+
+    def _finalize_and_verify(self):
+        self._finalize()
         self.base_logits = self.base.forward_device(self.T + 1, self.base_cache, 0, self.T + 1)
         return self.base_logits
+
+    def draft_tree_step(self):
+        """The draft side of a step alone (``mlx_eagle.py:400-440`` up to the selected tree): catch-up pass, root
+        expansion, ``depth`` tree levels, selection of the ``verify_num_tokens`` best nodes with their masks,
+        depths and root-to-leaf paths.  No target pass, nothing accepted: the decode state does not advance, so the
+        call can be repeated (what the draft-only benchmark configuration times)."""
+        self._draft_tree()
+        self._finalize()
 
     def _accept(self):
         L, p, ck = _lib.lib(), _lib.ptr, _lib.check

@@ -284,6 +284,7 @@ class Model:
         self.timeline = None
         self.attn_split_blocks = 0                       # 0 = library default; < 0 = always split the keys across CTAs
         self.phase_mask = 0                              # profiling: run only some phase kinds (0 = all)
+        self.grid_ctas = 0                               # CTAs of the persistent kernel (0 = one per SM)
         self.fwd = FwdInputs(self.device)
 
     # ------------------------------------------------------------------ construction
@@ -495,7 +496,8 @@ class Model:
         d.kv_cache = p(cache.data)
         if self.tp is not None:
             d.head_rows = self.vocab_local
-        key = (cache.rows,)
+        d.grid_ctas = self.grid_ctas
+        key = (cache.rows, self.grid_ctas)
         if self._fwd_ws is None or self._fwd_ws_key != key:
             d32 = _lib.ForwardDesc.from_buffer_copy(d)
             d32.M, d32.rows_out, d32.write_off, d32.tail = MAX_ROWS, MAX_ROWS, 0, MAX_TAIL

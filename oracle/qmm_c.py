@@ -19,6 +19,8 @@ def lib():
         _lib.oracle_f64_to_f16.restype = ctypes.c_uint16
         _lib.oracle_f64_to_f16.argtypes = [ctypes.c_double]
         _lib.oracle_num_threads.restype = ctypes.c_int
+        _lib.oracle_set_num_threads.restype = None
+        _lib.oracle_set_num_threads.argtypes = [ctypes.c_int]
     return _lib
 
 
@@ -47,3 +49,12 @@ def qmm(x, wq, scales, biases, group_size=64, bias=None, nthreads=0):
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def use_all_cores() -> int:
+    """Run later matmuls on every core this process may use, even when a launcher exported
+    ``OMP_NUM_THREADS=1``; returns the thread count."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_num_threads(n)
+    return num_threads()

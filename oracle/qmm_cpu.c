@@ -177,3 +177,13 @@ int oracle_num_threads(void) {
     return 1;
 #endif
 }
+
+/* Thread count of later calls, whatever OMP_NUM_THREADS said at start-up (launchers such as
+ * torch.distributed.run set it to 1 for every rank). */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
