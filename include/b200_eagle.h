@@ -281,6 +281,11 @@ typedef struct b200_forward_desc {
                              * bandwidth: fewer CTAs make every boundary cheaper and 16 to 64 SMs already pull 2 to
                              * 6.5 TB/s.  Size the workspace with the same value. */
     void* tp_peers[8];
+    int scales_in_fast_range;   /* non-zero: EVERY group scale of every matrix of layer_table and of lm_head_tiled has its
+                                 * fp16 exponent field in 1..10 (2^-14 <= |scale| < 2^-4, never zero or subnormal): the
+                                 * kernel then expands the nibbles with a shorter instruction sequence that gives the
+                                 * same bits.  0 is always safe. */
+    int reserved;
 } b200_forward_desc;
 
 size_t b200_forward_workspace_bytes(const b200_forward_desc* desc);

@@ -61,7 +61,8 @@ constexpr int kMaxSsqParts = 512;             // one part per 16 columns of h: h
 constexpr int kCsPitch = 64;                  // cos/sin table: cs[token][i], i < head_dim/2 <= 64
 
 // sync words (ints) at the head of the workspace
-constexpr int kSyncBar = 0, kSyncExit = 1, kSyncErr = 2;
+constexpr int kSyncExit = 1, kSyncErr = 2, kSyncBar = 8;   // exit count, error code, then kBarLanes arrival counters
+constexpr int kBarLanes = 8;
 
 enum { EPI_QKV = 0, EPI_SILU = 1, EPI_RESID = 2, EPI_HEAD = 3, EPI_TP = 4 };
 enum { K_EMBED = 0, K_A = 1, K_B1 = 2, K_B2 = 3, K_C = 4, K_D = 5, K_E = 6, K_HEAD = 7, K_R = 8 };
@@ -123,6 +124,7 @@ struct FwdParams {
     int attn_fused_max;            // single-phase attention while the cache spans at most this many key blocks
     unsigned phase_mask;           // bit per phase kind (K_*): kinds to run; all ones normally
     uint32_t grid_wait_limit, tp_wait_limit;   // polls before a wait on other CTAs / other GPUs gives up
+    int fast_scales;               // every group scale of every matrix has its fp16 exponent field in 1..10
     alignas(64) CUtensorMap kvmap; // the whole KV cache as a 2-D fp16 tensor [rows][head_dim], 64 x 64 boxes, 128-byte swizzle
     long long* timeline;           // optional [CTAs][timeline_pitch][8] timer stamps per barrier: arrive, leave, then
                                    // six stamps inside the matmul phase that ends at that barrier
@@ -167,6 +169,8 @@ struct Ctx {
     uint32_t pos;       // ring stages produced (producer warp) / consumed (consumer warps)
     uint32_t apos;      // attention key blocks produced / assigned so far
     uint32_t ause;      // key blocks this consumer warp has taken from its slot so far
+    uint64_t* rbar;     // the producer warp has left the per-token 1/rms of the phase's input in s_rstd
+    uint32_t ruse;      // phases that used rbar so far (both sides count)
     int ans;            // number of key-block slots (attention geometry)
     uint32_t epoch;     // barriers (device-wide or all-GPU) before the current phase
     uint32_t lbar;      // of those, the device-wide ones (the local counter's target is lbar * CTAs)
@@ -216,54 +220,63 @@ __device__ __forceinline__ void raise_error(const FwdParams& p, Ctx& c, int code
     atomicCAS(p.sync + kSyncErr, 0, code);
 }
 
-// Device-wide barrier, consumer side: every consumer thread calls it; thread 0 arrives for the CTA
-// and polls.  The counter only grows during a launch (target = epoch * CTAs); the last CTA to
-// leave the kernel resets it.
+// Device-wide barrier.  Arrival: after the consumer warps of the CTA have met, one thread makes the CTA's
+// writes visible and adds one to one of kBarLanes arrival counters (CTA b uses counter b % kBarLanes).
+// Departure: warp 0 polls for the CTA (lanes 0..kBarLanes-1 read one counter each with an acquire load: one
+// 32-byte sector per poll) and releases the other consumer warps through the CTA's named barrier; the producer
+// warp polls the same counters itself when it first needs the previous phase's output, so the activation
+// copies of the next phase are issued the moment the barrier opens, not after a relay through shared memory
+// (measured: a 0.5B-shape pass of 120 barriers went from 929 to 835 us).  The counters only grow during a
+// launch (counter j must reach barriers * CTAs that use j); the last CTA to leave the kernel resets them.
+// Every poll loop is bounded.
+__device__ __forceinline__ bool grid_poll(const FwdParams& p, uint32_t nbar, int lane, uint32_t limit, volatile int* abort_flag) {
+    const int mine = lane < kBarLanes ? ((int)gridDim.x + kBarLanes - 1 - lane) / kBarLanes : 0;   // CTAs on counter `lane`
+    const int target = (int)nbar * mine;
+    const int* ctr = p.sync + kSyncBar + (lane < kBarLanes ? lane : 0);
+    for (uint32_t i = 0; i < limit; i++) {
+        const bool ok = lane >= kBarLanes || ld_acquire(ctr) >= target;
+        if (__all_sync(0xffffffffu, ok)) return true;
+        if ((i & 63u) == 63u && *abort_flag) return false;
+    }
+    return false;
+}
+
 __device__ void grid_barrier(const FwdParams& p, Ctx& c) {
     c.epoch++;
     c.lbar++;
     consumer_sync(kNCons);
+    long long* tl = nullptr;
     if (threadIdx.x == 0 && !*c.abort_flag) {
-        long long* tl = nullptr;
         if (p.timeline != nullptr && (int)c.epoch <= p.timeline_pitch) {
             tl = p.timeline + ((size_t)blockIdx.x * p.timeline_pitch + (c.epoch - 1)) * 8;
             tl[0] = global_ns();
         }
         __threadfence();               // cumulative: covers the CTA's writes ordered before the bar.sync
         fence_proxy_async_all();
-        atomicAdd(p.sync + kSyncBar, 1);
-        const int target = (int)(c.lbar * gridDim.x);
-        bool ok = false;
-        const volatile int* bar = p.sync + kSyncBar;
-        for (uint32_t i = 0; i < p.grid_wait_limit; i++) {
-            if (*bar >= target) { ok = true; break; }
-        }
-        if (!ok) raise_error(p, c, 10);
-        __threadfence();
-        *c.s_epoch = c.epoch;          // the producer warp watches this word instead of the global counter
-        if (tl != nullptr) {
-            tl[1] = global_ns();
-            tl[7] = clock64();         // same instant in SM cycles, the origin of the next phase's stamps
-        }
+        atomicAdd(p.sync + kSyncBar + (blockIdx.x % kBarLanes), 1);
+    }
+    // warp 0 polls for the CTA (every warp polling for itself was measured slower: 9 x 148 pollers on one sector)
+    if (c.warp == 0 && !*c.abort_flag) {
+        if (!grid_poll(p, c.lbar, c.lane, p.grid_wait_limit, c.abort_flag) && c.lane == 0 && !*c.abort_flag) raise_error(p, c, 10);
     }
     consumer_sync(kNCons);
+    if (tl != nullptr) {
+        tl[1] = global_ns();
+        tl[7] = clock64();             // same instant in SM cycles, the origin of the next phase's stamps
+    }
 }
 
 // Producer side: the whole warp calls it before the first activation copy of a phase; it only
-// observes the counter.  Returns false on timeout / abort.
-__device__ bool producer_grid_wait(const FwdParams& p, Ctx& c, uint32_t need_epoch) {
-    int ok = 1;
-    if (need_epoch > 0 && c.lane == 0) {
-        ok = 0;
-        for (uint32_t i = 0; i < (p.grid_wait_limit << 4) && !*c.abort_flag; i++) {
-            if (*c.s_epoch >= need_epoch) { ok = 1; break; }
-        }
-        if (!ok && !*c.abort_flag) raise_error(p, c, 11);
-        __threadfence();
+// observes the counters.  Returns false on timeout / abort.
+__device__ bool producer_grid_wait(const FwdParams& p, Ctx& c, uint32_t need_lbar) {
+    bool ok = true;
+    if (need_lbar > 0) {
+        ok = !*c.abort_flag && grid_poll(p, need_lbar, c.lane, p.grid_wait_limit << 4, c.abort_flag);
+        if (!ok && c.lane == 0 && !*c.abort_flag) raise_error(p, c, 11);
+        __syncwarp();
     }
-    ok = __shfl_sync(0xffffffffu, ok, 0);
     fence_proxy_async_all();       // activations were written through the generic proxy by other CTAs
-    return ok != 0;
+    return ok;
 }
 
 // The ring memory has two geometries: NST matmul stages, or `ans` slots of one 64-key K/V block each
@@ -414,11 +427,50 @@ __device__ __forceinline__ void tp_reduce_phase(const FwdParams& p, Ctx& c, cons
 // streaming layout for TPI <= 4), then the same for up_proj in dual mode, then the activations of
 // the stage's K range (one bulk copy per token row).
 
+// rstd[m] = rsqrt(mean(h[m]^2) + eps) from the per-16-column sums of squares the producer of h left in p.ssq, by
+// the PRODUCER warp, once per phase, right after it has issued the phase's first activation copies: the loads
+// (one 128-byte line per part) overlap the weight stream, and the consumers find the result in shared memory
+// when they reach their first epilogue (they wait, bounded, on rbar).  Fixed summation order.
+__device__ __forceinline__ void producer_rstd(const FwdParams& p, Ctx& c, int rows) {
+    const int parts = p.H / 16;
+    const int nq = rows <= 8 ? 2 : (rows <= 16 ? 4 : 8);         // token quads (float4 of a part's line)
+    const int np = 32 / nq;                                       // parts read side by side
+    const int tq = c.lane % nq, pq = c.lane / nq;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int base = 0; base < parts; base += 8 * np) {
+        float4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {                             // eight independent loads in flight per lane
+            const int part = base + i * np + pq;
+            v[i] = part < parts ? __ldcg(reinterpret_cast<const float4*>(p.ssq + part * kSsqPitch) + tq)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) { acc.x += v[i].x; acc.y += v[i].y; acc.z += v[i].z; acc.w += v[i].w; }
+    }
+    for (int o = nq; o < 32; o <<= 1) {
+        acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
+        acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
+        acc.z += __shfl_xor_sync(0xffffffffu, acc.z, o);
+        acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
+    }
+    if (pq == 0) {
+        const float hh = (float)p.H;
+        const int m = tq * 4;
+        if (m < rows) c.s_rstd[m] = rsqrtf(acc.x / hh + p.eps);
+        if (m + 1 < rows) c.s_rstd[m + 1] = rsqrtf(acc.y / hh + p.eps);
+        if (m + 2 < rows) c.s_rstd[m + 2] = rsqrtf(acc.z / hh + p.eps);
+        if (m + 3 < rows) c.s_rstd[m + 3] = rsqrtf(acc.w / hh + p.eps);
+    }
+    __syncwarp();
+    if (c.lane == 0) mbar_arrive(smem_u32(c.rbar));              // release: orders the stores above
+}
+
 // Streams the weight records (and activation rows) of this CTA's items into the ring.
-// `need_epoch`: grid barriers that must have completed before the activations may be read.
+// `need_epoch`: device-wide barriers that must have completed before the activations may be read.
 template <int MT>
 __device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QDesc& d, uint32_t need_epoch,
-                                            const bool dual) {
+                                            const bool dual, const bool need_rstd) {
     using G = Geo<MT>;
     const int lane = c.lane;
     const int kw = d.pl.kw, U = d.pl.U;
@@ -449,6 +501,10 @@ __device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QD
             if (i < npend) issue_x(pend_slot[i], pend_k0[i], pend_recs[i]);
         npend = 0;
         ready = true;
+        if (need_rstd) {
+            producer_rstd(p, c, d.xrows);
+            c.ruse++;
+        }
         return true;
     };
 
@@ -522,32 +578,7 @@ __device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QD
     }
 }
 
-// rstd[m] = rsqrt(mean(h[m]^2) + eps) from the per-tile sums of squares the producer of h left in
-// p.ssq; all consumer threads, right after the grid barrier (overlaps the wait for the activations).
-__device__ __forceinline__ void compute_rstd(const FwdParams& p, Ctx& c, int rows) {
-    const int parts = p.H / 16;
-    const int l16 = threadIdx.x & 15;
-    for (int m0 = 0; m0 < rows; m0 += 16) {
-        const int m = m0 + (threadIdx.x >> 4);
-        float ss = 0.f;
-        for (int base = 0; base < parts; base += 256) {
-            float v[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) {                 // sixteen independent loads in flight per thread
-                const int part = base + i * 16 + l16;
-                v[i] = (m < rows && part < parts) ? __ldcg(p.ssq + part * kSsqPitch + m) : 0.f;
-            }
-#pragma unroll
-            for (int i = 0; i < 16; i++) ss += v[i];
-        }
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (l16 == 0 && m < rows) c.s_rstd[m] = rsqrtf(ss / (float)p.H + p.eps);
-    }
-    consumer_sync(kNCons);
-}
-
-template <int MT, bool DUAL, bool TP>
+template <int MT, bool DUAL, bool TP, bool FAST>
 __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QDesc& d, const int EPI) {
     using G = Geo<MT>;
     constexpr int S = DUAL ? 2 : 1;
@@ -567,8 +598,9 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
     const int nchunks_total = d.K / kChunkK;
     const int nitems = d.pl.row_items * d.pl.splits;
     const bool need_rstd = (EPI != EPI_RESID && !(TP && EPI == EPI_TP));
-    bool rstd_done = !need_rstd;
+    constexpr bool fast = FAST;                   // every scale of the model is in the range of dequant_pack_fast
     stamp(p, c, 2);
+    bool rstd_done = !need_rstd;
 
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
         const int row_item = item % d.pl.row_items;
@@ -620,8 +652,13 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
                             const __half2 p0 = u32_as_h2((j < 2) ? sb[s][0].x : sb[s][0].y);   // {scale, bias}
                             const __half2 p1 = u32_as_h2((j < 2) ? sb[s][1].x : sb[s][1].y);
                             uint32_t d0[4], d1[4];
-                            dequant_pack(comp(w[s][0], j), __low2half2(p0), __high2half2(p0), d0);
-                            dequant_pack(comp(w[s][1], j), __low2half2(p1), __high2half2(p1), d1);
+                            if (fast) {
+                                dequant_pack_fast(comp(w[s][0], j), scale_times_2_20(__low2half2(p0)), __high2half2(p0), d0);
+                                dequant_pack_fast(comp(w[s][1], j), scale_times_2_20(__low2half2(p1)), __high2half2(p1), d1);
+                            } else {
+                                dequant_pack(comp(w[s][0], j), __low2half2(p0), __high2half2(p0), d0);
+                                dequant_pack(comp(w[s][1], j), __low2half2(p1), __high2half2(p1), d1);
+                            }
 #pragma unroll
                             for (int mt = 0; mt < MT; mt++) {
                                 mma_m16n8k16(acc[s][mt], d0[0], d1[0], d0[1], d1[1], xb[mt].x, xb[mt].y);
@@ -636,8 +673,10 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
         }
 
         stamp(p, c, 5);
-        if (!rstd_done) {             // the per-token 1/rms of the input, needed by the epilogue only
-            compute_rstd(p, c, d.xrows);
+        if (!rstd_done) {             // the per-token 1/rms of the input (needed by the epilogue only): from the producer warp
+            bool rok = !*c.abort_flag && fwd_wait(smem_u32(c.rbar), c.ruse & 1u);
+            if (!__all_sync(0xffffffffu, rok) && lane == 0 && !*c.abort_flag) raise_error(p, c, 13);
+            c.ruse++;
             rstd_done = true;
         }
         stamp(p, c, 3);
@@ -1601,6 +1640,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
     c.empty = c.full + G::NST;
     c.afull = c.empty + G::NST;
     c.aempty = c.afull + kASlotsMax;
+    c.rbar = c.aempty + kASlotsMax;
+    c.ruse = 0;
     c.apos = 0;
     c.ause = 0;
     c.ans = AGeo<MT, HD>::NS;
@@ -1638,6 +1679,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             mbar_init(smem_u32(c.afull + s), 1);
             mbar_init(smem_u32(c.aempty + s), 1);
         }
+        mbar_init(smem_u32(c.rbar), 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
@@ -1709,16 +1751,18 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             }
             tp_wn = d.wn;
             if (producer) {
-                qmm_produce<MT>(p, c, d, c.epoch, kind == K_D);
-            } else if (kind == K_D) {
-                qmm_consume<MT, true, false>(p, c, d, EPI_SILU);
+                qmm_produce<MT>(p, c, d, c.lbar, kind == K_D, epi != EPI_RESID && epi != EPI_TP);
+            } else if (p.fast_scales) {          // uniform: chosen once per launch by the host
+                if (kind == K_D) qmm_consume<MT, true, false, true>(p, c, d, EPI_SILU);
+                else qmm_consume<MT, false, TP, true>(p, c, d, epi);
             } else {
-                qmm_consume<MT, false, TP>(p, c, d, epi);
+                if (kind == K_D) qmm_consume<MT, true, false, false>(p, c, d, EPI_SILU);
+                else qmm_consume<MT, false, TP, false>(p, c, d, epi);
             }
         }
         const bool exchange = TP && (kind == K_C || kind == K_E);
         if (kind != K_HEAD) {
-            if (producer) c.epoch++;
+            if (producer) { c.epoch++; if (!exchange) c.lbar++; }
             else if (exchange) tp_all_barrier(p, c);
             else grid_barrier(p, c);
         }
@@ -1726,6 +1770,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             // the partial products of all GPUs -> h, h*w, sums of squares (every GPU computes all of it)
             if (producer) {
                 c.epoch++;
+                c.lbar++;
             } else {
                 tp_reduce_phase(p, c, tp_wn);
                 grid_barrier(p, c);
@@ -1741,7 +1786,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
         __threadfence();
         const int old = atomicAdd(p.sync + kSyncExit, 1);
         if (old == (int)gridDim.x - 1) {
-            p.sync[kSyncBar] = 0;
+            for (int j = 0; j < kBarLanes; j++) p.sync[kSyncBar + j] = 0;
             p.sync[kSyncExit] = 0;
             if (TP)                        // every CTA read the old count before its first barrier
                 *reinterpret_cast<volatile unsigned*>(p.tp_peers[p.tp_rank] + kTpFwdCount) = c.tp_seq0 + c.tpx;
@@ -2010,6 +2055,7 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
     p.phase_mask = d->phase_mask ? (unsigned)d->phase_mask : 0xffu;
     p.grid_wait_limit = g_wait_limit ? (g_wait_limit < (1u << 27) ? g_wait_limit : (1u << 27)) : kGridWaitLimit;
     p.tp_wait_limit = g_wait_limit ? g_wait_limit : kTpWaitLimit;
+    p.fast_scales = d->scales_in_fast_range ? 1 : 0;
     p.attn_fused_max = d->attn_split_blocks > 0 ? d->attn_split_blocks - 1 : (d->attn_split_blocks < 0 ? 0 : 32);
     p.timeline = static_cast<long long*>(d->timeline);
     p.timeline_pitch = d->timeline ? d->timeline_pitch : 0;

@@ -194,10 +194,15 @@ class QLinear:
         self.in_features = wq.shape[1] * 8
         self.group_size, self.bits = 64, 4
         self.tiled = None
+        self.scales_fast = False
 
     def relayout(self, keep_rowmajor: bool = False):
         """Build the streaming layout of this layer's weights; drop the row-major tensors unless asked."""
         self._nbytes = self.nbytes()
+        # the persistent kernel expands nibbles with a shorter, bit-identical sequence when every scale's fp16
+        # exponent field is in 1..10 (2^-14 <= |s| < 2^-4); recorded here, while the scales are still at hand
+        e = (self.scales.view(torch.int16).to(torch.int32) >> 10) & 31
+        self.scales_fast = bool(((e >= 1) & (e <= 10)).all())
         self.tiled = qk.relayout(self.weight, self.scales, self.biases)
         if not keep_rowmajor:
             self.weight = self.scales = self.biases = None
@@ -285,6 +290,8 @@ class Model:
         self.attn_split_blocks = 0                       # 0 = library default; < 0 = always split the keys across CTAs
         self.phase_mask = 0                              # profiling: run only some phase kinds (0 = all)
         self.grid_ctas = 0                               # CTAs of the persistent kernel (0 = one per SM)
+        self.fast_dequant = True                         # allow the short nibble expansion when every scale permits it
+        self._scales_fast = None
         self.fwd = FwdInputs(self.device)
 
     # ------------------------------------------------------------------ construction
@@ -497,6 +504,10 @@ class Model:
         if self.tp is not None:
             d.head_rows = self.vocab_local
         d.grid_ctas = self.grid_ctas
+        if self._scales_fast is None:
+            self._scales_fast = all(lw[k].scales_fast for lw in self.layers for k in ("qkv", "o", "gate", "up", "down")) \
+                and self.lm_head.scales_fast
+        d.scales_in_fast_range = 1 if (self._scales_fast and self.fast_dequant) else 0
         key = (cache.rows, self.grid_ctas)
         if self._fwd_ws is None or self._fwd_ws_key != key:
             d32 = _lib.ForwardDesc.from_buffer_copy(d)

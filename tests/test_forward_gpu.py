@@ -154,3 +154,29 @@ def test_forward_rejects_bad_descriptors(be, pair):
     bad = be._lib.ForwardDesc.from_buffer_copy(d)
     bad.h = d.h + 2
     assert lib.b200_forward(ctypes.byref(bad), None) == -2
+
+
+def test_short_nibble_expansion_gives_the_same_bits_and_is_refused_for_out_of_range_scales(be, cuda):
+    """The kernel's shorter expansion (nibble as an fp16 subnormal times scale * 2^20) must equal the long one bit
+    for bit whenever it is allowed, and must not be chosen when a scale is zero, subnormal or >= 2^-4."""
+    args = be.shape_preset("tiny-qwen2")
+    rng = np.random.default_rng(8)
+    prompt = torch.from_numpy(rng.integers(0, args.vocab_size, 40))
+    m = be.Model.random_init(args, seed=5, device=cuda, gen_device="cpu").relayout()
+    outs = []
+    for fast in (True, False):
+        m.fast_dequant = fast
+        outs.append(m(prompt[None], cache=m.make_cache(128))[0].clone())
+    assert m._scales_fast is True                       # N(0, 0.02) weights: scales around 1e-2
+    m.check_fused_error()
+    assert torch.equal(outs[0], outs[1])
+    # one zero scale, one large scale: the model must fall back to the long expansion and still match the oracle
+    m2 = be.Model.random_init(args, seed=5, device=cuda, gen_device="cpu")
+    m2.layers[0]["gate"].scales[3, 1] = 0.0
+    m2.layers[1]["down"].scales[7, 0] = 0.125
+    om = model_ref.OracleModel(args, m2.state_numpy())
+    m2.relayout()
+    got = m2(prompt[None], cache=m2.make_cache(128))[0].cpu().numpy()
+    assert m2._scales_fast is False
+    want = om(prompt.numpy(), model_ref.make_prompt_cache(om, 128))
+    _close(got, want, 2.0 ** -6, 2e-2)
