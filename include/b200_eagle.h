@@ -161,6 +161,14 @@ int b200_embed_gather(const int* tokens, const uint32_t* wq, const void* scales,
 int b200_rms_norm(const void* x, const void* w, void* y, const int* row_index, int M, int H, float eps,
                   void* stream);
 
+/* Element-wise halves of the fused matmul epilogues, for prompt ingestion (mlx_eagle.py:522-535), whose matmuls run
+ * 128 token rows at a time through b200_qmm_umma (plain epilogue): h = fp16(h + y) (the residual add of
+ * mlx_llama.py:246,248) and out = silu(gate) * up with every op result rounded to fp16 (mlx_llama.py:215), the same
+ * rounding points as B200_EPI_RESIDUAL / B200_EPI_SILU_MUL.  n = element count, a multiple of 8; fp16 device arrays,
+ * 16-byte aligned. */
+int b200_add_f16(void* h, const void* y, size_t n, void* stream);
+int b200_silu_mul_f16(const void* gate, const void* up, void* out, size_t n, void* stream);
+
 /* Tensor-parallel residual epilogue: h[M,N] = fp16(h + fp16(sum)) with `sum` the all-reduced fp32 partial
  * products of a row-parallel layer (o_proj / down_proj of mlx_llama.py:246,248 sharded along K).  No
  * counterpart in the reference, which runs on one device. */

@@ -118,6 +118,10 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_tp_argmax_combine.argtypes = [vp, i32, ctypes.c_uint, i32, i32, ctypes.POINTER(ctypes.c_void_p), vp]
     l.b200_forward.restype = i32
     l.b200_forward.argtypes = [ctypes.POINTER(ForwardDesc), vp]
+    l.b200_add_f16.restype = i32
+    l.b200_add_f16.argtypes = [vp, vp, sz, vp]
+    l.b200_silu_mul_f16.restype = i32
+    l.b200_silu_mul_f16.argtypes = [vp, vp, vp, sz, vp]
     l.b200_residual_add_f32.restype = i32
     l.b200_residual_add_f32.argtypes = [vp, vp, i32, i32, vp]
     l.b200_argmax_key_shift.restype = i32

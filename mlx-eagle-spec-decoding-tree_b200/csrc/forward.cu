@@ -749,18 +749,42 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
                     float a0[8], a1[8];
 #pragma unroll
                     for (int e = 0; e < 8; e++) a0[e] = a1[e] = 0.f;
+                    // residual and norm weights of the epilogue: issued now, so that their latency runs with the
+                    // partial sums' (h is read and written by this thread only)
+                    uint4 rv = make_uint4(0, 0, 0, 0), wv = make_uint4(0, 0, 0, 0);
+                    if (valid && EPI == EPI_RESID && !(TP && EPI == EPI_TP)) {
+                        rv = __ldcg(reinterpret_cast<const uint4*>(p.h + (size_t)tok * d.N + n0));
+                        wv = *reinterpret_cast<const uint4*>(d.wn + n0);
+                    }
                     if (valid) {
-                        for (int sp = 0; sp < d.pl.splits; sp++) {
-                            const float* src = p.partial + ((size_t)sp * d.pl.row_items + row_item) * MP * TW + (size_t)tok * TW + c0;
-                            const float4 u0 = __ldcg(reinterpret_cast<const float4*>(src));
-                            const float4 u1 = __ldcg(reinterpret_cast<const float4*>(src) + 1);
-                            a0[0] += u0.x; a0[1] += u0.y; a0[2] += u0.z; a0[3] += u0.w;
-                            a0[4] += u1.x; a0[5] += u1.y; a0[6] += u1.z; a0[7] += u1.w;
-                            if (DUAL) {
-                                const float4 v0 = __ldcg(reinterpret_cast<const float4*>(src + R));
-                                const float4 v1 = __ldcg(reinterpret_cast<const float4*>(src + R) + 1);
-                                a1[0] += v0.x; a1[1] += v0.y; a1[2] += v0.z; a1[3] += v0.w;
-                                a1[4] += v1.x; a1[5] += v1.y; a1[6] += v1.z; a1[7] += v1.w;
+                        // four splits' loads in flight at a time (a load from L2 takes the better part of a
+                        // microsecond); added in split order, so the result does not depend on the batching
+                        for (int sp0 = 0; sp0 < d.pl.splits; sp0 += 4) {
+                            float4 u0[4], u1[4], v0[4], v1[4];
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {          // past the last split: the last one again (weight 0 below)
+                                const int sp = min(sp0 + j, d.pl.splits - 1);
+                                const float* src = p.partial + ((size_t)sp * d.pl.row_items + row_item) * MP * TW + (size_t)tok * TW + c0;
+                                u0[j] = __ldcg(reinterpret_cast<const float4*>(src));
+                                u1[j] = __ldcg(reinterpret_cast<const float4*>(src) + 1);
+                                if (DUAL) {
+                                    v0[j] = __ldcg(reinterpret_cast<const float4*>(src + R));
+                                    v1[j] = __ldcg(reinterpret_cast<const float4*>(src + R) + 1);
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const float m = (sp0 + j < d.pl.splits) ? 1.f : 0.f;     // fma(1, x, a) == a + x
+                                a0[0] = fmaf(m, u0[j].x, a0[0]); a0[1] = fmaf(m, u0[j].y, a0[1]);
+                                a0[2] = fmaf(m, u0[j].z, a0[2]); a0[3] = fmaf(m, u0[j].w, a0[3]);
+                                a0[4] = fmaf(m, u1[j].x, a0[4]); a0[5] = fmaf(m, u1[j].y, a0[5]);
+                                a0[6] = fmaf(m, u1[j].z, a0[6]); a0[7] = fmaf(m, u1[j].w, a0[7]);
+                                if (DUAL) {
+                                    a1[0] = fmaf(m, v0[j].x, a1[0]); a1[1] = fmaf(m, v0[j].y, a1[1]);
+                                    a1[2] = fmaf(m, v0[j].z, a1[2]); a1[3] = fmaf(m, v0[j].w, a1[3]);
+                                    a1[4] = fmaf(m, v1[j].x, a1[4]); a1[5] = fmaf(m, v1[j].y, a1[5]);
+                                    a1[6] = fmaf(m, v1[j].z, a1[6]); a1[7] = fmaf(m, v1[j].w, a1[7]);
+                                }
                             }
                         }
                     }
@@ -774,8 +798,6 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
                     } else if (EPI == EPI_RESID) {
                         float ss = 0.f;
                         if (valid) {
-                            const uint4 rv = __ldcg(reinterpret_cast<const uint4*>(p.h + (size_t)tok * d.N + n0));
-                            const uint4 wv = *reinterpret_cast<const uint4*>(d.wn + n0);
                             const __half* rh = reinterpret_cast<const __half*>(&rv);
                             const __half* wh = reinterpret_cast<const __half*>(&wv);
                             __align__(16) __half hw[8];

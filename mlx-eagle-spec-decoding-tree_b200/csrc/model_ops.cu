@@ -120,6 +120,42 @@ __global__ void residual_add_f32_kernel(__half* __restrict__ h, const float* __r
     hp[1] = __hadd2(hp[1], __floats2half2_rn(s.z, s.w));
 }
 
+// ---- element-wise halves of the fused matmul epilogues, for prompt ingestion through the large-M matmul (whose own
+// epilogue is plain): the same rounding points as B200_EPI_RESIDUAL and B200_EPI_SILU_MUL.
+__global__ void add_f16_kernel(__half* __restrict__ h, const __half* __restrict__ y, size_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= n) return;
+    uint4 a = *reinterpret_cast<const uint4*>(h + i);
+    const uint4 b = *reinterpret_cast<const uint4*>(y + i);
+    __half2* ah = reinterpret_cast<__half2*>(&a);
+    const __half2* bh = reinterpret_cast<const __half2*>(&b);
+#pragma unroll
+    for (int e = 0; e < 4; e++) ah[e] = __hadd2(ah[e], bh[e]);
+    *reinterpret_cast<uint4*>(h + i) = a;
+}
+
+__global__ void silu_mul_f16_kernel(const __half* __restrict__ gate, const __half* __restrict__ up, __half* __restrict__ out,
+                                    size_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= n) return;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gate + i);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(up + i);
+    const __half* g = reinterpret_cast<const __half*>(&g4);
+    const __half* u = reinterpret_cast<const __half*>(&u4);
+    __align__(16) __half o[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) {                 // every op result fp16, as in the fused epilogue (mlx_llama.py:215)
+        const float gf = __half2float(g[e]);
+        const __half sig = __float2half_rn(1.0f / (1.0f + expf(-gf)));
+        o[e] = __hmul(__hmul(g[e], sig), u[e]);
+    }
+    *reinterpret_cast<uint4*>(out + i) = *reinterpret_cast<const uint4*>(o);
+}
+
 // Stand-alone operator with the reference's tensor layout: in/out (B, H, L, D), offsets (B, L).
 __global__ void rope_positions_kernel(const __half* __restrict__ in, const int* __restrict__ offsets,
                                       const float* __restrict__ inv_freq, float scaling,
@@ -179,6 +215,23 @@ int b200_residual_add_f32(void* h, const float* sum, int M, int N, void* stream)
     const int n = M * N;
     b200::launch_kernel(b200::residual_add_f32_kernel, dim3((n / 4 + 255) / 256), dim3(256), 0,
                         static_cast<cudaStream_t>(stream), static_cast<__half*>(h), sum, n);
+    return b200::check_launch();
+}
+
+int b200_add_f16(void* h, const void* y, size_t n, void* stream) {
+    if (!h || !y || n < 8 || (n % 8) != 0) return B200_EINVAL;
+    if (!b200::aligned16(h) || !b200::aligned16(y)) return B200_EALIGN;
+    b200::launch_kernel(b200::add_f16_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                        static_cast<__half*>(h), static_cast<const __half*>(y), n);
+    return b200::check_launch();
+}
+
+int b200_silu_mul_f16(const void* gate, const void* up, void* out, size_t n, void* stream) {
+    if (!gate || !up || !out || n < 8 || (n % 8) != 0) return B200_EINVAL;
+    if (!b200::aligned16(gate) || !b200::aligned16(up) || !b200::aligned16(out)) return B200_EALIGN;
+    b200::launch_kernel(b200::silu_mul_f16_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0,
+                        static_cast<cudaStream_t>(stream), static_cast<const __half*>(gate), static_cast<const __half*>(up),
+                        static_cast<__half*>(out), n);
     return b200::check_launch();
 }
 

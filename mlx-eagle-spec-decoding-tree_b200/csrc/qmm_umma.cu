@@ -12,10 +12,11 @@
 //                    (exact q*s+b, rounded once to fp16, like every other kernel of this library) and writes
 //                    the fp16 pairs with tcgen05.st into its own lane of a 128-lane x 64-column tile in tensor
 //                    memory (lane = weight row, column = two k values): the A operand never touches shared
-//                    memory.  The group also moves the chunk's activations to the slot that goes with the tile;
+//                    memory;
 //   MMA warp         one thread issues 8 tcgen05.mma (128 x N x 16, N = 16 .. 128 tokens; A from tensor memory,
-//                    B = activations from shared memory) per chunk into a TMEM accumulator and commits to the
-//                    mbarriers that free the tile and publish the accumulator;
+//                    B = the chunk's activations, read in place from the packed stage) per chunk into a TMEM
+//                    accumulator and commits to the mbarriers that free the tile, free the packed stage (together
+//                    with the eight warps that read its packs) and publish the accumulator;
 //   epilogue         the dequant warps read the accumulator (tcgen05.ld, one weight row per thread) and store fp16.
 //
 // The activations come in the tensor cores' canonical K-major layout without swizzle ([chunk][token group of 8]
@@ -56,12 +57,11 @@ constexpr uint32_t kUmmaWaitPolls = 1u << 24;    // x <= 32 ns each (short suspe
 template <int NT>                                // token columns of the MMA: 16 or 32
 struct UGeo {
     static constexpr int XBYTES = (NT / 8) * kSBO;                   // activations of one chunk, same layout
-    static constexpr int PSTAGE = 2 * kRunBytes + XBYTES;            // packed stage
-    static constexpr int TSTAGE = XBYTES;                            // the activations that go with a tile in tensor memory
-    static constexpr int NP = NT <= 32 ? 8 : (NT == 64 ? 4 : 2);      // packed stages
-    static constexpr int NTS = NT <= 64 ? kAStages : 2;              // tile stages (tensor-memory tiles + activation slots)
+    static constexpr int PSTAGE = 2 * kRunBytes + XBYTES;            // packed stage: two record runs + the chunk's activations
+    static constexpr int NP = NT <= 32 ? 8 : (NT == 64 ? 6 : 4);      // packed stages (the MMAs read the activations in place)
+    static constexpr int NTS = NT <= 64 ? kAStages : 2;              // tile stages (tensor-memory tiles)
     static constexpr int ACC = NT < 32 ? 32 : NT;                    // columns of one accumulator
-    static constexpr int BAR_OFF = NP * PSTAGE + NTS * TSTAGE;
+    static constexpr int BAR_OFF = NP * PSTAGE;
     static constexpr int SMEM = BAR_OFF + 256 + 1024;                // + barriers, + alignment slack
 };
 
@@ -105,7 +105,6 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* packed = smem;
-    unsigned char* tiles = smem + G::NP * G::PSTAGE;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G::BAR_OFF);
     uint64_t* pfull = bars;                          // packed stage landed            (producer -> dequant warps)
     uint64_t* pempty = pfull + G::NP;        // packed stage read              (8 dequant warps -> producer)
@@ -125,7 +124,7 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
         s_abort = 0;
         for (int s = 0; s < G::NP; s++) {
             mbar_init(smem_u32(pfull + s), 1);
-            mbar_init(smem_u32(pempty + s), kGroupWarps);
+            mbar_init(smem_u32(pempty + s), kGroupWarps + 1);   // the eight warps that read the packs + the MMAs that read the activations
         }
         for (int s = 0; s < G::NTS; s++) {
             mbar_init(smem_u32(tready + s), kGroupWarps);
@@ -191,7 +190,10 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                     const uint32_t a0 = tmem + ts * kAColumns;        // the tile: lane = weight row, column = two k values
-                    const uint32_t b0 = smem_u32(tiles + ts * G::TSTAGE);
+                    const uint32_t ps = n % G::NP;                    // the chunk's packed stage still holds its activations
+                    ok = uwait(smem_u32(pfull + ps), (n / G::NP) & 1u);   // (observed here too: the MMAs read what the copy wrote)
+                    if (!ok) break;
+                    const uint32_t b0 = smem_u32(packed + ps * G::PSTAGE + 2 * kRunBytes);
 #pragma unroll
                     for (int ks = 0; ks < kChunkK / 16; ks++) {
                         const uint64_t db = umma_desc(b0 + ks * 2 * kLBO);
@@ -202,9 +204,12 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
                             "r"(a0 + ks * 8), "l"(db), "r"(idesc), "r"(accumulate)
                             : "memory");
                     }
-                    // the tile (and its activations) may be rewritten once these MMAs have read it
+                    // the tile and the stage's activations may be rewritten once these MMAs have read them
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
                                      smem_u32(tfree + ts))
+                                 : "memory");
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
+                                     smem_u32(pempty + ps))
                                  : "memory");
                 }
                 if (ok)
@@ -230,10 +235,6 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const unsigned char* stage = packed + ps * G::PSTAGE;
-                unsigned char* xslot = tiles + ts * G::TSTAGE;
-                // the chunk's activations move to the slot of the tile (the MMAs read them; the packed stage is freed now)
-                for (int i = wl * 32 + lane; i < G::XBYTES / 16; i += kGroupWarps * 32)
-                    *reinterpret_cast<uint4*>(xslot + i * 16) = *reinterpret_cast<const uint4*>(stage + 2 * kRunBytes + i * 16);
                 // Thread = weight row 32 * (wl % 4) + lane of the item (the tensor-memory lane this warp may write);
                 // warps 0-3 of the group take the k groups 4j+0, 4j+1, warps 4-7 the k groups 4j+2, 4j+3.  A row's 16
                 // packs are 64 contiguous bytes of its record: pack j of k group 4j+t at byte 16 t + 4 j.
@@ -261,7 +262,6 @@ __global__ void __launch_bounds__(kUThreads, 1) qmm_umma_kernel(const __grid_con
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-                fence_proxy_async();                  // generic-proxy stores -> visible to the tensor cores' reads
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(smem_u32(pempty + ps));

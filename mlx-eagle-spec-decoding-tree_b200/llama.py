@@ -31,6 +31,7 @@ from .quantize import quantize
 
 MAX_ROWS = 32          # tokens per forward pass (tree size + 1 <= 32)
 MAX_TAIL = 64          # uncommitted cache rows a query can address through its bit mask
+PREFILL_ROWS = 128     # prompt tokens per pass of the large-M (tcgen05) matmul path
 
 
 @dataclass
@@ -291,6 +292,10 @@ class Model:
         self.phase_mask = 0                              # profiling: run only some phase kinds (0 = all)
         self.grid_ctas = 0                               # CTAs of the persistent kernel (0 = one per SM)
         self.fast_dequant = True                         # allow the short nibble expansion when every scale permits it
+        self.prefill_large_m = True                      # prompts: 128 rows per weight read through b200_qmm_umma
+        self._pf = None                                  # buffers of that path, made on first use
+        self.prefill_graphs = True                       # replay full 128-row chunks from a CUDA graph
+        self._pf_graphs = {}
         self._scales_fast = None
         self.fwd = FwdInputs(self.device)
 
@@ -623,6 +628,112 @@ class Model:
         vl = self.vocab_local                      # a tensor-parallel shard produces its slice of the vocabulary
         return self.logits[:rows] if vl == a.vocab_size else self.logits.view(-1)[: rows * vl].view(rows, vl)
 
+    # ------------------------------------------------------------------ prompt ingestion, 128 rows per weight read
+    def can_prefill_large_m(self) -> bool:
+        """True when a causal prompt can go through ``b200_qmm_umma`` 128 rows at a time: weights in the
+        streaming layout, every matrix height and width a multiple of 128, no tensor-parallel shard."""
+        if not self.prefill_large_m or self.tp is not None or os.environ.get("B200_PREFILL_LARGE_M", "1") == "0":
+            return False
+        a = self.args
+        lins = [lw[k] for lw in self.layers for k in ("qkv", "o", "gate", "up", "down")] + [self.lm_head]
+        if any(q.tiled is None for q in lins):
+            return False
+        return all(q.out_features % 128 == 0 and q.in_features % 128 == 0 for q in lins) and a.head_dim in (64, 128)
+
+    def _prefill_large_m(self, tokens: torch.Tensor, cache: KVCache, off: int, all_logits: bool, head: bool = True):
+        """One causal pass of up to 128 prompt tokens starting at cache row ``off`` (``mlx_eagle.py:522-535``
+        ingests the prompt in chunks; ``mlx_llama.py:231-249`` is the layer).  Every matmul reads its weights
+        once for the whole chunk (``b200_qmm_umma``, tcgen05); the element-wise steps around it keep the rounding
+        points of the 32-row path's fused epilogues (norm -> fp16, product -> fp16, + bias, + residual in fp16,
+        SiLU(gate) * up with fp16 results); attention runs in blocks of 32 query rows, each seeing all earlier
+        rows as committed prefix and its own rows causally.  Returns fp16 logits ``(L, V)`` or ``(1, V)`` (``None`` with ``head=False``: cache rows only)."""
+        a, L, ck, p = self.args, _lib.lib(), _lib.check, _lib.ptr
+        st = _lib.stream_ptr(self.device)
+        n = tokens.numel()
+        H, I, hd = a.hidden_size, a.intermediate_size, a.head_dim
+        Hq, Hkv = a.num_attention_heads, a.num_key_value_heads
+        nqkv = self.nq + 2 * self.nkv
+        if self._pf is None:
+            f16 = dict(dtype=torch.float16, device=self.device)
+            R = PREFILL_ROWS
+            self._pf = dict(h=torch.zeros(R, H, **f16), xn=torch.zeros(R, H, **f16), qkv=torch.zeros(R, nqkv, **f16),
+                            attn=torch.zeros(R, self.nq, **f16), g=torch.zeros(R, I, **f16), u=torch.zeros(R, I, **f16),
+                            y=torch.zeros(R, H, **f16), tok=torch.zeros(R, dtype=torch.int32, device=self.device),
+                            pos=torch.zeros(R, dtype=torch.int32, device=self.device),
+                            prefix=torch.zeros(R // MAX_ROWS + 1, dtype=torch.int32, device=self.device),
+                            mask=torch.tensor([(2 << m) - 1 for m in range(MAX_ROWS)], dtype=torch.int64).to(self.device),
+                            logits=None)
+        b = self._pf
+        b["tok"][:n].copy_(tokens)
+        b["pos"][:n].copy_(off + torch.arange(n, dtype=torch.int32))
+        nblk = (n + MAX_ROWS - 1) // MAX_ROWS
+        b["prefix"][: nblk + 1].copy_(off + MAX_ROWS * torch.arange(nblk + 1, dtype=torch.int32))
+        if n < PREFILL_ROWS or not self.prefill_graphs:
+            return self._prefill_body(n, cache, all_logits, head)
+        # a full chunk is ~25 launches per layer: replayed from a CUDA graph (inputs live in device buffers), or
+        # the host's launch time, not the GPU, would bound prompt ingestion
+        key = (cache.data.data_ptr(), cache.rows, all_logits, head)
+        entry = self._pf_graphs.get(key)
+        if entry is None:
+            out = self._prefill_body(n, cache, all_logits, head)        # eager once: sizes workspaces, sets attributes
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self._prefill_body(n, cache, all_logits, head)
+            self._pf_graphs[key] = (graph, out)
+            # the eager pass already produced this chunk's result: nothing to replay now
+            return out
+        entry[0].replay()
+        return entry[1]
+
+    def _prefill_body(self, n: int, cache: KVCache, all_logits: bool, head: bool):
+        a, L, ck, p = self.args, _lib.lib(), _lib.check, _lib.ptr
+        st = _lib.stream_ptr(self.device)
+        H, I, hd = a.hidden_size, a.intermediate_size, a.head_dim
+        Hq, Hkv = a.num_attention_heads, a.num_key_value_heads
+        nqkv = self.nq + 2 * self.nkv
+        b = self._pf
+        nblk = (n + MAX_ROWS - 1) // MAX_ROWS
+        aws = self._attention_workspace(cache)
+        eps = float(a.rms_norm_eps)
+        h, xn, qkv, attn, g, u, y = (b[k][:n] for k in ("h", "xn", "qkv", "attn", "g", "u", "y"))
+        ck(L.b200_embed_gather(p(b["tok"]), p(self.embed.weight), p(self.embed.scales), p(self.embed.biases), p(h), n, H,
+                               a.vocab_size, st), "b200_embed_gather")
+        for li, lw in enumerate(self.layers):
+            kc, vc = cache.layer(li)
+            ck(L.b200_rms_norm(p(h), p(lw["input_norm"]), p(xn), None, n, H, eps, st), "b200_rms_norm")
+            qk.matmul_umma(xn, lw["qkv"].tiled, nqkv, bias=lw["qkv"].bias, out=qkv)
+            ck(L.b200_rope_kv_append(p(qkv), p(b["pos"]), p(self.inv_freqs), self.rope_scaling_factor, p(kc), p(vc),
+                                     p(b["prefix"]), 0, n, Hq, Hkv, hd, cache.rows, st), "b200_rope_kv_append")
+            for j in range(nblk):
+                r0 = j * MAX_ROWS
+                m = min(MAX_ROWS, n - r0)
+                ck(L.b200_tree_attention(ctypes.c_void_p(qkv.data_ptr() + r0 * nqkv * 2), nqkv, p(kc), p(vc), p(b["mask"]),
+                                         ctypes.c_void_p(b["prefix"].data_ptr() + 4 * j), m,
+                                         ctypes.c_void_p(attn.data_ptr() + r0 * self.nq * 2), m, Hq, Hkv, hd, cache.rows,
+                                         cache.rows, self.scale, p(aws), aws.numel(), st), "b200_tree_attention")
+            qk.matmul_umma(attn, lw["o"].tiled, H, out=y)
+            ck(L.b200_add_f16(p(h), p(y), n * H, st), "b200_add_f16")
+            ck(L.b200_rms_norm(p(h), p(lw["post_norm"]), p(xn), None, n, H, eps, st), "b200_rms_norm")
+            qk.matmul_umma(xn, lw["gate"].tiled, I, out=g)
+            qk.matmul_umma(xn, lw["up"].tiled, I, out=u)
+            ck(L.b200_silu_mul_f16(p(g), p(u), p(g), n * I, st), "b200_silu_mul_f16")
+            qk.matmul_umma(g, lw["down"].tiled, H, out=y)
+            ck(L.b200_add_f16(p(h), p(y), n * H, st), "b200_add_f16")
+        V = self.lm_head.out_features
+        if not head:
+            return None
+        if all_logits:
+            if b["logits"] is None:
+                b["logits"] = torch.zeros(PREFILL_ROWS, V, dtype=torch.float16, device=self.device)
+            ck(L.b200_rms_norm(p(h), p(self.norm), p(xn), None, n, H, eps, st), "final norm")
+            qk.matmul_umma(xn, self.lm_head.tiled, V, out=b["logits"][:n])
+            return b["logits"][:n]
+        ck(L.b200_rms_norm(ctypes.c_void_p(h.data_ptr() + (n - 1) * H * 2), p(self.norm), p(self.xn), None, 1, H, eps, st),
+           "final norm")
+        self._linear(self.xn, self.lm_head, self.logits, 1, qk.EPI_NONE)
+        return self.logits[:1]
+
     # ------------------------------------------------------------------ reference-style call
     def __call__(self, inputs: torch.Tensor, cache: Optional[KVCache] = None, mask: Optional[torch.Tensor] = None,
                  position_ids: Optional[Union[torch.Tensor, int]] = None, flat_rope: bool = False,
@@ -641,6 +752,20 @@ class Model:
         if Ltot > MAX_ROWS and (mask is not None or position_ids is not None):
             raise _lib.B200Error("explicit masks / positions are limited to 32 tokens per call")
         outs = []
+        if Ltot > MAX_ROWS and self.can_prefill_large_m():
+            for c0 in range(0, Ltot, PREFILL_ROWS):
+                chunk = inputs[c0:c0 + PREFILL_ROWS]
+                off = cache.offset
+                if off + chunk.numel() > cache.rows:
+                    raise _lib.B200Error("KV cache is full")
+                last = c0 + PREFILL_ROWS >= Ltot
+                if logits_last_only and not last:
+                    self._prefill_large_m(chunk, cache, off, all_logits=False, head=False)
+                else:
+                    lg = self._prefill_large_m(chunk, cache, off, all_logits=not logits_last_only)
+                    outs = [lg.clone()] if logits_last_only else outs + [lg.clone()]
+                cache.offset = off + chunk.numel()
+            return torch.cat(outs, 0).unsqueeze(0)
         for c0 in range(0, Ltot, MAX_ROWS):
             chunk = inputs[c0:c0 + MAX_ROWS]
             L = chunk.numel()

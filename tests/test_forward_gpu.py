@@ -161,7 +161,7 @@ def test_short_nibble_expansion_gives_the_same_bits_and_is_refused_for_out_of_ra
     for bit whenever it is allowed, and must not be chosen when a scale is zero, subnormal or >= 2^-4."""
     args = be.shape_preset("tiny-qwen2")
     rng = np.random.default_rng(8)
-    prompt = torch.from_numpy(rng.integers(0, args.vocab_size, 40))
+    prompt = torch.from_numpy(rng.integers(0, args.vocab_size, 29))          # one pass of the persistent kernel
     m = be.Model.random_init(args, seed=5, device=cuda, gen_device="cpu").relayout()
     outs = []
     for fast in (True, False):
@@ -180,3 +180,31 @@ def test_short_nibble_expansion_gives_the_same_bits_and_is_refused_for_out_of_ra
     assert m2._scales_fast is False
     want = om(prompt.numpy(), model_ref.make_prompt_cache(om, 128))
     _close(got, want, 2.0 ** -6, 2e-2)
+
+
+def test_prompt_through_the_large_m_path_matches_the_oracle_and_the_32_row_passes(pair):
+    """A 300-token prompt goes through b200_qmm_umma 128 rows at a time (mlx_eagle.py:522-535): logits and every
+    K/V row against the CPU oracle, and against the same prompt ingested 32 rows at a time."""
+    args, m, om = pair
+    rng = np.random.default_rng(11)
+    prompt = rng.integers(0, args.vocab_size, 300)
+    assert m.can_prefill_large_m()
+    cache = m.make_cache(384)
+    logits = m(torch.from_numpy(prompt)[None], cache=cache)[0].cpu().numpy()
+    assert cache.offset == 300
+    oc = model_ref.make_prompt_cache(om, 384)
+    want = om(prompt, oc)
+    _close(logits, want, 2.0 ** -6, 2e-2)
+    for li, c in enumerate(oc):
+        _close(cache.data[li, 0, :, :300].cpu().numpy(), c.keys[0, :, :300], 2.0 ** -6, 2e-2)
+        _close(cache.data[li, 1, :, :300].cpu().numpy(), c.values[0, :, :300], 2.0 ** -6, 2e-2)
+    m.prefill_large_m = False
+    try:
+        cache2 = m.make_cache(384)
+        small = m(torch.from_numpy(prompt)[None], cache=cache2)[0].cpu().numpy()
+    finally:
+        m.prefill_large_m = True
+    m.check_fused_error()
+    _close(logits, small, 2.0 ** -6, 2e-2)
+    last = m(torch.from_numpy(prompt)[None], cache=m.make_cache(384), logits_last_only=True)[0].cpu().numpy()
+    _close(last[0], want[-1], 2.0 ** -6, 2e-2)
