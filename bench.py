@@ -372,10 +372,16 @@ def tensor_parallel_numbers(torch, dist, be, workload, rank, world, dev, K, warm
     kernels with NCCL all-reduces.  Returns a dict of numbers (the same on every rank)."""
     tname, dname, prompt_len, depth, verify = TP_WORKLOADS[workload]
     tshape, dshape = be.shape_preset(tname), be.shape_preset(dname)
-    draft = be.Model.random_init(dshape, seed=1000, device=dev).relayout()          # same weights on every rank
+    shard_draft = os.environ.get("B200_TP_DRAFT", "replicated") == "sharded"
+    if shard_draft:          # the draft's layers are cut like the target's; its vocabulary projection stays whole
+        draft = be.Model.random_init_shard(dshape, 1000, dev, rank, world, shard_head=False).relayout()
+        draft.tp.open_exchange(dshape.hidden_size)
+    else:
+        draft = be.Model.random_init(dshape, seed=1000, device=dev).relayout()      # same weights on every rank
     base = be.Model.random_init_shard(tshape, 2000, dev, rank, world).relayout()
     base.tp.open_exchange(tshape.hidden_size)
-    assert base.can_fuse()
+    base.tp_two_shot = draft.tp_two_shot = int(os.environ.get("B200_TP_TWO_SHOT", "0"))      # 0 = library default
+    assert base.can_fuse() and draft.can_fuse()
     rows = ((prompt_len + 8 * (warmup + K + depth + 8) + verify + 128 + 63) // 64) * 64
     dec = be.SpecDecoder(base, draft, depth, verify, cache_rows=rows, max_out_tokens=8 * (warmup + K) + 512,
                          max_steps=warmup + K + 64)
@@ -442,9 +448,12 @@ def tensor_parallel_numbers(torch, dist, be, workload, rank, world, dev, K, warm
     out = dict(tname=tname, dname=dname, prompt_len=prompt_len, depth=depth, verify=verify, sec=sec, produced=produced,
                mean_accept=mean_accept, clocks=clocks, res=res, e2e_sec=e2e_sec, alg=alg, fsec=fsec, nccl_sec=nccl_sec,
                dsec=dsec, step_bytes=step_bytes, prefix_now=prefix_now, launches=dec.kernel_launches_per_step * K,
-               head_dim=tshape.head_dim)
+               head_dim=tshape.head_dim, draft_mode="layers cut across the GPUs, whole vocabulary projection" if shard_draft
+               else "replicated")
     dist.barrier()
     base.tp.close_exchange()
+    if shard_draft:
+        draft.tp.close_exchange()
     del dec, base, draft
     torch.cuda.empty_cache()
     return out
@@ -476,13 +485,13 @@ def run_tensor_parallel(args, rank, world, local_rank):
             "config": {"workload": f"spec-decode {r['tname']}-shape target cut over {world} GPUs + replicated {r['dname']}-shape "
                                    f"draft, prompt {r['prompt_len']}, depth {r['depth']}, verify {r['verify']}, greedy",
                        "parallelism": f"tp{world} target (all-reduce inside the persistent kernel over peer memory), "
-                                      "replicated draft and tree logic",
+                                      f"draft {r['draft_mode']}, replicated tree logic",
                        "l2": "inputs larger than L2 (weights streamed every step)", "mean_accept_length": r["mean_accept"],
                        "weight_bytes_per_step_per_gpu": r["step_bytes"],
                        "step_weight_stream_frac_of_peak": r["step_bytes"] / (sec / K) / 1e9 / peak,
                        "target_pass_ms": {"persistent_kernel_peer_memory_allreduce": 1e3 * r["fsec"],
                                           "per_op_kernels_nccl_allreduce_eager": 1e3 * r["nccl_sec"]},
-                       "draft_pass_ms": 1e3 * r["dsec"]},
+                       "draft_pass_ms": 1e3 * r["dsec"], "draft": r["draft_mode"]},
             "clocks": r["clocks"],
             "e2e": {"value": res["produced"] / r["e2e_sec"], "unit": UNIT,
                     "h2d_bytes_per_step": res["h2d_bytes"] / e2e_steps, "d2h_bytes_per_step": res["d2h_bytes"] / e2e_steps,
@@ -806,7 +815,7 @@ def main():
                   "mean_accept_length": r["mean_accept"],
                   "target_pass_ms": {"persistent_kernel_peer_memory_allreduce": 1e3 * r["fsec"],
                                      "per_op_kernels_nccl_allreduce_eager": 1e3 * r["nccl_sec"]},
-                  "draft_pass_ms": 1e3 * r["dsec"]}
+                  "draft_pass_ms": 1e3 * r["dsec"], "draft": r["draft_mode"]}
         except Exception as e:                             # the attachment must not take the headline down with it
             tp = {"error": f"{type(e).__name__}: {e}"}
         if line is not None:

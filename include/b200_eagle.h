@@ -293,7 +293,12 @@ typedef struct b200_forward_desc {
                                  * fp16 exponent field in 1..10 (2^-14 <= |scale| < 2^-4, never zero or subnormal): the
                                  * kernel then expands the nibbles with a shorter instruction sequence that gives the
                                  * same bits.  0 is always safe. */
-    int reserved;
+    int tp_two_shot;            /* exchange of the row-parallel layers: 0 = every GPU reads all ranks' partial products
+                                 * in full (one all-GPU barrier per exchange; the default: fastest measured at 2 and 4
+                                 * GPUs); 1 = two-step form: each GPU reduces its slice of the columns and stores the
+                                 * result to every GPU (a second all-GPU barrier; needs hidden % (16 * tp_world) == 0).
+                                 * Same bits either way.  The same value on every rank; zero the exchange buffers when
+                                 * switching. */
 } b200_forward_desc;
 
 size_t b200_forward_workspace_bytes(const b200_forward_desc* desc);

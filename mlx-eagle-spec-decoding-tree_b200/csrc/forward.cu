@@ -119,6 +119,7 @@ struct FwdParams {
     // residual.  tp_peers[r] = rank r's exchange buffer as mapped into this process.
     // The count of exchanges done by earlier launches lives in the buffer (flags only ever grow).
     int tp_world, tp_rank;
+    int tp_two_shot;               // reduce-scatter + all-gather through the exchange buffers instead of reading every peer in full
     unsigned char* tp_peers[kMaxTp];
     int head_rows;                 // rows of the vocabulary projection held here (a vocabulary shard under TP)
     int attn_fused_max;            // single-phase attention while the cache spans at most this many key blocks
@@ -318,11 +319,14 @@ __device__ __forceinline__ float4 ld_sys_f4(const float* q) {
     return v;
 }
 
-// Barrier over all CTAs of all GPUs of the group, after a phase that wrote partial products: thread 0 of
-// every CTA makes the CTA's writes visible system-wide, adds one to the arrival counter in every GPU's
-// exchange buffer (its own included) and waits (bounded) until its own GPU's counter shows the arrivals of
-// all CTAs of all GPUs for this exchange.  Counters only grow (compared modulo 2^32).
-__device__ void tp_all_barrier(const FwdParams& p, Ctx& c) {
+// Barrier over all CTAs of all GPUs of the group.  Thread 0 of every CTA makes the CTA's writes visible
+// system-wide; then, with the two-step exchange, it takes a ticket on its own GPU's CTA
+// counter, and the CTA that takes the last ticket adds one to the GPU-level arrival counter in every GPU's
+// exchange buffer (its own included, release at system scope): ONE remote atomic per peer and barrier instead of
+// one per CTA; with the one-step exchange every CTA adds one to every GPU's counter itself.  Every CTA then waits
+// (bounded) until its own GPU's counter shows all arrivals.  `nbar` = all-GPU barriers completed since
+// the buffers were last zeroed (the same on every GPU); counters only grow (compared modulo 2^32).
+__device__ void tp_all_barrier(const FwdParams& p, Ctx& c, uint32_t nbar) {
     c.epoch++;
     consumer_sync(kNCons);
     if (threadIdx.x == 0 && !*c.abort_flag) {
@@ -333,20 +337,36 @@ __device__ void tp_all_barrier(const FwdParams& p, Ctx& c) {
         }
         __threadfence_system();
         fence_proxy_async_all();
-        for (int r = 0; r < p.tp_world; r++) {
-            const int q = (p.tp_rank + r) % p.tp_world;          // own counter first
-            unsigned* cnt = reinterpret_cast<unsigned*>(p.tp_peers[q] + kTpFwdArrive);
-            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(cnt) : "memory");   // ordered by the fence above
+        unsigned char* own = p.tp_peers[p.tp_rank];
+        unsigned target;
+        if (p.tp_two_shot) {
+            // two-step exchange: one remote atomic per GPU and barrier (the last CTA's), not one per CTA
+            const unsigned ticket = atomicAdd(reinterpret_cast<unsigned*>(own + kTpFwdLocal), 1u);
+            if (ticket + 1u == (nbar + 1u) * gridDim.x) {      // the last CTA of this GPU: tell every GPU
+                __threadfence_system();                        // the other CTAs' writes, ordered before their tickets
+                for (int r = 0; r < p.tp_world; r++) {
+                    const int q = (p.tp_rank + r) % p.tp_world;    // own counter first
+                    unsigned* cnt = reinterpret_cast<unsigned*>(p.tp_peers[q] + kTpFwdArrive);
+                    asm volatile("red.release.sys.global.add.u32 [%0], 1;\n" ::"l"(cnt) : "memory");
+                }
+            }
+            target = (nbar + 1u) * (unsigned)p.tp_world;
+        } else {
+            // one-step exchange: every CTA adds one to every GPU's counter directly (one hop less on the critical path)
+            for (int r = 0; r < p.tp_world; r++) {
+                const int q = (p.tp_rank + r) % p.tp_world;
+                unsigned* cnt = reinterpret_cast<unsigned*>(p.tp_peers[q] + kTpFwdArrive);
+                asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(cnt) : "memory");   // ordered by the fence above
+            }
+            target = (nbar + 1u) * (unsigned)p.tp_world * gridDim.x;
         }
-        const unsigned target = (c.tp_seq0 + c.tpx + 1) * (unsigned)p.tp_world * gridDim.x;
-        const unsigned* mine = reinterpret_cast<const unsigned*>(p.tp_peers[p.tp_rank] + kTpFwdArrive);
+        const unsigned* mine = reinterpret_cast<const unsigned*>(own + kTpFwdArrive);
         bool ok = false;
         for (uint32_t i = 0; i < p.tp_wait_limit; i++) {
             if ((int)(ld_acquire_sys(mine) - target) >= 0) { ok = true; break; }
         }
         if (!ok) raise_error(p, c, 12);
         __threadfence();
-        *c.s_epoch = c.epoch;
         if (tl != nullptr) {
             tl[1] = global_ns();
             tl[7] = clock64();
@@ -412,9 +432,93 @@ __device__ __noinline__ void tp_reduce_rows(const FwdParams& p, const __half* wn
     }
 }
 
+// Two-step variant, on request (the one-step form makes every GPU read (N-1) whole partial buffers per exchange;
+// measured on 4 GPUs the second all-GPU barrier of this form costs more than the reads it saves, so it is not the default).
+// Shot one: GPU r adds, for ITS slice of H / N columns only, the partial products of all ranks (rank order) and
+// the residual, and stores the fp16 result into the gather area of every GPU's exchange buffer (plain stores,
+// the peers' over NVLink).  After another all-GPU barrier, shot two: every GPU turns the gathered rows into h,
+// h*w and the sums of squares, exactly like the single-GPU epilogue; all GPUs hold bit-identical hidden states.
+__device__ __forceinline__ __half* tp_gather_of(const FwdParams& p, int rank, uint32_t x) {
+    return reinterpret_cast<__half*>(p.tp_peers[rank] + kTpHeader + (size_t)2 * 32 * p.H * sizeof(float)) + (size_t)(x & 1u) * 32 * p.H;
+}
+
+__device__ __noinline__ void tp_reduce_scatter(const FwdParams& p, uint32_t xchg) {
+    const int W = p.H / p.tp_world;                    // columns this GPU reduces (a multiple of 16)
+    const int upt = W / 4;
+    const int units = p.M * upt;
+    const int stride = gridDim.x * kNCons;
+    for (int i = blockIdx.x * kNCons + threadIdx.x; i < units; i += stride) {
+        const int tok = i / upt;
+        const int n0 = p.tp_rank * W + (i - tok * upt) * 4;
+        float4 u[kMaxTp];
+#pragma unroll
+        for (int r = 0; r < kMaxTp; r++)               // all ranks' loads in flight together
+            if (r < p.tp_world) u[r] = ld_sys_f4(tp_partial_of(p, r, xchg) + (size_t)tok * p.H + n0);
+        const uint2 rv = __ldcg(reinterpret_cast<const uint2*>(p.h + (size_t)tok * p.H + n0));
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < kMaxTp; r++) {             // rank order: the sum does not depend on who computes it
+            if (r < p.tp_world) { a[0] += u[r].x; a[1] += u[r].y; a[2] += u[r].z; a[3] += u[r].w; }
+        }
+        const __half* rh = reinterpret_cast<const __half*>(&rv);
+        __align__(8) __half out[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) out[e] = __hadd(rh[e], __float2half_rn(a[e]));
+        const uint2 ov = *reinterpret_cast<const uint2*>(out);
+#pragma unroll
+        for (int r = 0; r < kMaxTp; r++) {
+            if (r < p.tp_world) {
+                uint2* dst = reinterpret_cast<uint2*>(tp_gather_of(p, r, xchg) + (size_t)tok * p.H + n0);
+                asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};\n" ::"l"(dst), "r"(ov.x), "r"(ov.y) : "memory");
+            }
+        }
+    }
+}
+
+__device__ __noinline__ void tp_finalize_rows(const FwdParams& p, const __half* wn, uint32_t xchg) {
+    const int upt = p.H / 4;
+    const int units = p.M * upt;
+    const int units32 = (units + 31) & ~31;
+    const int stride = gridDim.x * kNCons;
+    const __half* gathered = tp_gather_of(p, p.tp_rank, xchg);
+    for (int i = blockIdx.x * kNCons + threadIdx.x; i < units32; i += stride) {
+        const bool valid = i < units;
+        const int tok = valid ? i / upt : 0;
+        const int n0 = valid ? (i - tok * upt) * 4 : 0;
+        float ss = 0.f;
+        if (valid) {
+            uint2 hv;
+            asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];\n" : "=r"(hv.x), "=r"(hv.y)
+                         : "l"(gathered + (size_t)tok * p.H + n0) : "memory");
+            const uint2 wv = *reinterpret_cast<const uint2*>(wn + n0);
+            const __half* hh = reinterpret_cast<const __half*>(&hv);
+            const __half* wh = reinterpret_cast<const __half*>(&wv);
+            __align__(8) __half hw[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float fv = __half2float(hh[e]);
+                ss += fv * fv;
+                hw[e] = __hmul(hh[e], wh[e]);
+            }
+            *reinterpret_cast<uint2*>(p.h + (size_t)tok * p.H + n0) = hv;
+            *reinterpret_cast<uint2*>(p.hw + xt_index(tok, n0, p.mp)) = *reinterpret_cast<const uint2*>(hw);
+        }
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);              // the four 4-column quarters of a 16-column part
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        if (valid && (threadIdx.x & 3) == 0) p.ssq[(n0 >> 4) * kSsqPitch + tok] = ss;
+    }
+}
+
 __device__ __forceinline__ void tp_reduce_phase(const FwdParams& p, Ctx& c, const __half* wn) {
+    const uint32_t xchg = c.tp_seq0 + c.tpx;
     consumer_sync(kNCons);
-    if (!*c.abort_flag) tp_reduce_rows(p, wn, c.tp_seq0 + c.tpx);
+    if (p.tp_two_shot) {
+        if (!*c.abort_flag) tp_reduce_scatter(p, xchg);
+        tp_all_barrier(p, c, xchg * 2u + 1u);
+        if (!*c.abort_flag) tp_finalize_rows(p, wn, xchg);
+    } else if (!*c.abort_flag) {
+        tp_reduce_rows(p, wn, xchg);
+    }
     c.tpx++;
 }
 
@@ -489,16 +593,20 @@ __device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QD
     uint32_t pend_slot[G::NST];
     int pend_k0[G::NST], pend_recs[G::NST];
 
-    auto issue_x = [&](uint32_t slot, int k0, int recs) {       // one run: `recs` chunks x MP padded rows
-        if (lane == 0)
-            bulk_copy_g2s(smem_u32(c.ring + slot * G::STAGE + kWArea), d.x + (size_t)(k0 >> 7) * G::MP * kXRowH,
-                          (uint32_t)(recs * G::MP * kXRow), smem_u32(c.full + slot));
-    };
+    // A bulk copy occupies the issuing warp for ~0.3 us whatever its size, but the lanes of ONE instruction issue
+    // side by side: all copies of a stage (weights and activations) therefore go out in a single instruction.
+    const uint64_t xpolicy = make_evict_normal_policy();
+    auto x_src = [&](int k0) { return reinterpret_cast<const unsigned char*>(d.x + (size_t)(k0 >> 7) * G::MP * kXRowH); };
     auto flush = [&]() -> bool {
         if (!producer_grid_wait(p, c, need_epoch)) return false;
+        uint32_t my_slot = 0;
+        int my_k0 = 0, my_recs = 0;
 #pragma unroll
         for (int i = 0; i < G::NST; i++)
-            if (i < npend) issue_x(pend_slot[i], pend_k0[i], pend_recs[i]);
+            if (lane == i) { my_slot = pend_slot[i]; my_k0 = pend_k0[i]; my_recs = pend_recs[i]; }
+        if (lane < npend)          // the activation runs of the stages queued before the barrier opened
+            bulk_copy_g2s_hint(smem_u32(c.ring + my_slot * G::STAGE + kWArea), x_src(my_k0), (uint32_t)(my_recs * G::MP * kXRow),
+                               smem_u32(c.full + my_slot), xpolicy);
         npend = 0;
         ready = true;
         if (need_rstd) {
@@ -543,29 +651,40 @@ __device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QD
             __syncwarp();
             unsigned char* stage = c.ring + slot * G::STAGE;
             const size_t ch0 = (size_t)(c_begin + st * CPS);
+            const int k0 = (c_begin + st * CPS) * kChunkK;
+            // lanes 0 .. ncw-1: the weight runs; lane ncw: the activation run (once the previous phase's output is visible)
+            int ncw;
+            uint32_t cdst = 0, cbytes = 0;
+            const unsigned char* csrc = nullptr;
             if (TPI >= 4) {
                 // whole 64-row blocks: the stage's chunks of a block are one contiguous run
                 const int nb = TPI / 4;
-                if (lane < nb * nmat) {
+                ncw = nb * nmat;
+                if (lane < ncw) {
                     const int mtx = lane / nb, b = lane - mtx * nb;
                     const unsigned char* wbase = mtx ? d.w1 : d.w0;
-                    bulk_copy_g2s_hint(smem_u32(stage + mtx * up_off + b * CPS * 4 * kRec),
-                                       wbase + ((size_t)(b ? blk1 : blk0) * nchunks_total + ch0) * 4 * kRec,
-                                       (uint32_t)(recs * 4 * kRec), fbar, wpolicy);
+                    cdst = smem_u32(stage + mtx * up_off + b * CPS * 4 * kRec);
+                    csrc = wbase + ((size_t)(b ? blk1 : blk0) * nchunks_total + ch0) * 4 * kRec;
+                    cbytes = (uint32_t)(recs * 4 * kRec);
                 }
             } else {
-                for (int idx = lane; idx < recs * nmat; idx += 32) {     // part of a block: one copy per chunk
-                    const int mtx = idx / recs, cc = idx - mtx * recs;
+                ncw = recs * nmat;                                        // part of a block: one copy per chunk (<= 16)
+                if (lane < ncw) {
+                    const int mtx = lane / recs, cc = lane - mtx * recs;
                     const unsigned char* wbase = mtx ? d.w1 : d.w0;
-                    bulk_copy_g2s_hint(smem_u32(stage + mtx * up_off + cc * chunk_bytes),
-                                       wbase + (((size_t)blk0 * nchunks_total + ch0 + cc) * 4 + (t0 & 3)) * kRec,
-                                       (uint32_t)chunk_bytes, fbar, wpolicy);
+                    cdst = smem_u32(stage + mtx * up_off + cc * chunk_bytes);
+                    csrc = wbase + (((size_t)blk0 * nchunks_total + ch0 + cc) * 4 + (t0 & 3)) * kRec;
+                    cbytes = (uint32_t)chunk_bytes;
                 }
             }
-            const int k0 = (c_begin + st * CPS) * kChunkK;
-            if (ready) {
-                issue_x(slot, k0, recs);
-            } else {
+            const bool xlane = ready && lane == ncw;
+            if (xlane) {
+                cdst = smem_u32(stage + kWArea);
+                csrc = x_src(k0);
+                cbytes = (uint32_t)(recs * G::MP * kXRow);
+            }
+            if (lane < ncw || xlane) bulk_copy_g2s_hint(cdst, csrc, cbytes, fbar, xlane ? xpolicy : wpolicy);
+            if (!ready) {
 #pragma unroll
                 for (int i = 0; i < G::NST; i++)
                     if (i == npend) { pend_slot[i] = slot; pend_k0[i] = k0; pend_recs[i] = recs; }
@@ -1785,13 +1904,13 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
         const bool exchange = TP && (kind == K_C || kind == K_E);
         if (kind != K_HEAD) {
             if (producer) { c.epoch++; if (!exchange) c.lbar++; }
-            else if (exchange) tp_all_barrier(p, c);
+            else if (exchange) tp_all_barrier(p, c, (c.tp_seq0 + c.tpx) * (p.tp_two_shot ? 2u : 1u));
             else grid_barrier(p, c);
         }
         if (exchange) {
             // the partial products of all GPUs -> h, h*w, sums of squares (every GPU computes all of it)
             if (producer) {
-                c.epoch++;
+                c.epoch += p.tp_two_shot ? 2 : 1;
                 c.lbar++;
             } else {
                 tp_reduce_phase(p, c, tp_wn);
@@ -2008,7 +2127,7 @@ using namespace b200;
 
 size_t b200_forward_tp_buffer_bytes(int hidden) {
     if (hidden < 128 || (hidden % 128) != 0) return 0;
-    return (size_t)kTpHeader + (size_t)2 * 32 * hidden * sizeof(float);
+    return (size_t)kTpHeader + (size_t)2 * 32 * hidden * sizeof(float) + (size_t)2 * 32 * hidden * sizeof(__half);
 }
 
 size_t b200_forward_workspace_bytes(const b200_forward_desc* d) {
@@ -2067,6 +2186,8 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
     p.head_rows = d->head_rows > 0 ? d->head_rows : d->vocab;
     p.tp_world = d->tp_world > 1 ? d->tp_world : 1;
     p.tp_rank = d->tp_world > 1 ? d->tp_rank : 0;
+    p.tp_two_shot = (p.tp_world > 1 && (p.H % (16 * p.tp_world)) == 0 &&
+                     d->tp_two_shot > 0) ? 1 : 0;
     if (p.tp_world > 1) {
         for (int r = 0; r < p.tp_world; r++) {
             if (!d->tp_peers[r]) return B200_EINVAL;

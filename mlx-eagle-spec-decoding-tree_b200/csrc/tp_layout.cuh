@@ -1,6 +1,7 @@
 // Layout of a tensor-parallel exchange buffer (one per GPU, mapped by every process of the group).
 // Header: flag lines and counters of the two users, then the key slots of the argmax combine; after the
-// header two buffers of [32][hidden] fp32 partial products, used in turn.
+// header two buffers of [32][hidden] fp32 partial products, used in turn, then two gather areas of [32][hidden] fp16
+// (the reduced hidden states of the two-shot exchange), used in turn.
 #pragma once
 
 namespace b200 {
@@ -9,6 +10,7 @@ constexpr int kMaxTp = 8;             // GPUs of one tensor-parallel group
 constexpr int kTpFlagStride = 64;     // one line per peer: peer r raises the word at r * 64
 constexpr int kTpFwdArrive = 0;       // persistent forward kernel: arrivals of all CTAs of all GPUs (remote atomics)
 constexpr int kTpFwdCount = 512;      //   exchanges completed by earlier launches (local word)
+constexpr int kTpFwdLocal = 768;      //   tickets of this GPU's own CTAs for the all-GPU barrier (local atomics)
 constexpr int kTpKeyFlags = 1024;     // argmax combine: flags written by the peers
 constexpr int kTpKeyCount = 1536;     //   combines completed so far (local word)
 constexpr int kTpKeyErr = 1540;       //   non-zero after a combine whose wait for a peer gave up

@@ -292,6 +292,7 @@ class Model:
         self.phase_mask = 0                              # profiling: run only some phase kinds (0 = all)
         self.grid_ctas = 0                               # CTAs of the persistent kernel (0 = one per SM)
         self.fast_dequant = True                         # allow the short nibble expansion when every scale permits it
+        self.tp_two_shot = 0                             # tensor-parallel exchange: 0 one-step (default), 1 two-step form
         self.prefill_large_m = True                      # prompts: 128 rows per weight read through b200_qmm_umma
         self._pf = None                                  # buffers of that path, made on first use
         self.prefill_graphs = True                       # replay full 128-row chunks from a CUDA graph
@@ -335,11 +336,14 @@ class Model:
         return Model(args, layers, embed, norm_w(), lm_head, device)
 
     @staticmethod
-    def random_init_shard(args: ModelArgs, seed: int, device, rank: int, world: int, group=None) -> "Model":
+    def random_init_shard(args: ModelArgs, seed: int, device, rank: int, world: int, group=None,
+                          shard_head: bool = True) -> "Model":
         """A tensor-parallel shard drawn directly at shard shapes, for models too large to build whole on one
         GPU.  Every rank must pass the same seed: embeddings and norms then agree across ranks (which the
         replicated hidden state needs); the shards' own weights are the same random numbers on every rank,
-        which changes nothing about the work done.  Not a shard of ``random_init(args, seed)``."""
+        which changes nothing about the work done.  Not a shard of ``random_init(args, seed)``.
+        ``shard_head=False`` keeps the whole vocabulary projection on every GPU (a tensor-parallel DRAFT: its logits
+        feed the tree kernels, which want every vocabulary row; only the layers are cut)."""
         import dataclasses
         a = args
         hd = a.head_dim
@@ -350,15 +354,16 @@ class Model:
         largs = dataclasses.replace(a, num_attention_heads=a.num_attention_heads // world,
                                     num_key_value_heads=a.num_key_value_heads // world,
                                     intermediate_size=a.intermediate_size // world)
-        m = Model.random_init(largs, seed, device, head_rows=a.vocab_size // world)
+        m = Model.random_init(largs, seed, device, head_rows=a.vocab_size // world if shard_head else None)
         m.tp = TensorParallel(rank, world, group)
-        m.vocab_offset = rank * (a.vocab_size // world)
+        m.vocab_offset = rank * (a.vocab_size // world) if shard_head else 0
         m.part32 = torch.zeros(MAX_ROWS, a.hidden_size, dtype=torch.float32, device=m.device)
         return m
 
-    def shard(self, rank: int, world: int, group=None) -> "Model":
+    def shard(self, rank: int, world: int, group=None, shard_head: bool = True) -> "Model":
         """This model's shard ``rank`` of ``world`` for tensor-parallel execution (call before ``relayout``).
-        Heads, kv heads, MLP rows and vocabulary rows are cut evenly; embeddings and norms are replicated."""
+        Heads, kv heads, MLP rows and vocabulary rows are cut evenly; embeddings and norms are replicated.
+        ``shard_head=False`` leaves the vocabulary projection whole on every GPU (for a tensor-parallel draft)."""
         a = self.args
         if any(v % world for v in (a.num_attention_heads, a.num_key_value_heads, a.vocab_size)) or \
                 (a.intermediate_size // world) % 128 or (self.nq // world) % 128 or (a.vocab_size // world) % 8:
@@ -382,10 +387,10 @@ class Model:
         import dataclasses
         largs = dataclasses.replace(a, num_attention_heads=a.num_attention_heads // world,
                                     num_key_value_heads=a.num_key_value_heads // world, intermediate_size=I)
-        head = _rows(self.lm_head, rank * V, (rank + 1) * V)
+        head = _rows(self.lm_head, rank * V, (rank + 1) * V) if shard_head else (None if self.lm_head is self.embed else self.lm_head)
         m = Model(largs, layers, self.embed, self.norm, head, self.device)
         m.tp = TensorParallel(rank, world, group)
-        m.vocab_offset = rank * V
+        m.vocab_offset = rank * V if shard_head else 0
         m.part32 = torch.zeros(MAX_ROWS, a.hidden_size, dtype=torch.float32, device=self.device)
         return m
 
@@ -527,6 +532,7 @@ class Model:
         d.attn_split_blocks = self.attn_split_blocks
         if self.tp is not None:
             d.tp_world, d.tp_rank, d.head_rows = self.tp.world, self.tp.rank, self.vocab_local
+            d.tp_two_shot = self.tp_two_shot
             for r, q in enumerate(self.tp.peers):
                 d.tp_peers[r] = q
         if self.timeline is not None:
@@ -540,7 +546,7 @@ class Model:
         (``self.timeline`` int64 ``[SMs, barriers + 1, 8]``; the last entry holds the end of the kernel)."""
         if on:
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-            per_layer = 6 if self.tp is None else 8          # a shard has two more barriers per layer
+            per_layer = 6 if self.tp is None else 10         # a shard has two to four more barriers per layer
             self.timeline = torch.zeros(sms, per_layer * self.args.num_hidden_layers + 2, 8, dtype=torch.int64,
                                         device=self.device)
         else:

@@ -56,6 +56,26 @@ def _rank(rank, world, port, out):
     again = shard(prompt[None], cache=shard.make_cache(128))[0].float().cpu()
     shard.check_fused_error()
     assert torch.equal(again, fused)
+    # the two-step exchange (each GPU reduces its slice of the columns and stores it to every GPU), forced on two GPUs:
+    # same sums in the same rank order, so the same bits as the one-step exchange
+    shard.tp.reset_exchange()
+    shard.tp_two_shot = 1
+    two = shard(prompt[None], cache=shard.make_cache(128))[0].float().cpu()
+    shard.check_fused_error()
+    assert torch.equal(two, fused)
+    # a tensor-parallel DRAFT next to the tensor-parallel target: layers cut, vocabulary projection whole
+    draft2 = be.Model.random_init(args, seed=12, device=dev, gen_device="cpu")
+    draft2.norm.mul_(8.0)
+    dshard = draft2.shard(rank, world, shard_head=False).relayout()
+    dshard.tp.open_exchange(args.hidden_size)
+    assert dshard.can_fuse() and dshard.vocab_local == args.vocab_size
+    res3 = be.generate_step(prompt, shard, dshard, depth=3, verify_num_tokens=15, max_tokens=40, N=40, verbose=False)
+    shard.check_fused_error()
+    dshard.check_fused_error()
+    gold = g["random_draft_d3_t15"]
+    assert res3["tokens"] == gold["tokens"] and res3["accept_lengths"] == gold["accept_lengths"]
+    dist.barrier()
+    dshard.tp.close_exchange()
     shard.tp.close_exchange()
     dist.destroy_process_group()
 
