@@ -198,7 +198,7 @@ def roofline_block(torch, model, cache, rows, prefix, name, reps=20):
             "algorithmic_bytes_per_launch": alg, "us_per_launch": 1e6 * sec, "launches_timed": reps}
 
 
-def qmm_sweep(torch, be, dev, launches=100, sets=32):
+def qmm_sweep(torch, be, dev, launches=100, sets=32, rows=(1, 8, 16, 24, 32)):
     """The operator half of the metric: y = x . dequant(W)^T at N 8192, K 2048 (W ~ N(0, 0.02), 4 bit, group 64,
     x ~ N(0, 1) fp16) for 1, 8, 16, 24, 32 rows.  Every launch reads another of `sets` weight sets (302 MB in
     all, more than the 126 MB L2), each launch is timed by its own pair of CUDA events, the median of `launches`
@@ -217,7 +217,7 @@ def qmm_sweep(torch, be, dev, launches=100, sets=32):
         plain.append((wq, s, b))
         tiled.append(qk.relayout(wq, s, b))
     out = []
-    for m in (1, 8, 16, 24, 32):
+    for m in rows:
         x = torch.randn(m, K, generator=g, device=dev).half()
         y = torch.empty(m, N, dtype=torch.float16, device=dev)
         alg = _qmm_bytes(m, N, K)
@@ -587,13 +587,13 @@ def parity_check(be, base, draft, depth, verify, prompt_len, steps=3):
                     "retrieve paths, accept length, tokens, counters bit-identical"}
 
 
-def timed_blocks(torch, dist, world, dec, K, snapshot):
+def timed_blocks(torch, dist, world, dec, K, snapshot, min_seconds=MIN_TIMED_SECONDS):
     """Replays the K-step block from the same decode state until MIN_TIMED_SECONDS have been timed (at least 3
     blocks); CUDA events around each block, barrier + synchronize on both sides.  Returns the per-block seconds
     and the tokens one block produces."""
     ctl0, y0 = snapshot
     secs, produced = [], None
-    while len(secs) < 3 or (sum(secs) < MIN_TIMED_SECONDS and len(secs) < 400):
+    while len(secs) < 3 or (sum(secs) < min_seconds and len(secs) < 400):
         dec.ctl.copy_(ctl0)
         dec.y.copy_(y0)
         torch.cuda.synchronize()
@@ -631,6 +631,10 @@ def main():
     ap.add_argument("--operator-sweep", action="store_true",
                     help="only time the two matmul operators (mma.sync streaming kernel, tcgen05 kernel) at big layer shapes")
     ap.add_argument("--qmm-sweep", action="store_true", help="only the 8192 x 2048 operator sweep at 1..32 rows")
+    ap.add_argument("--rows", type=int, default=0, help="with --qmm-sweep: only this row count (profiling)")
+    ap.add_argument("--launches", type=int, default=100, help="with --qmm-sweep: timed launches per kernel and row count")
+    ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
+                    help="repeat the block of --steps steps until this much time has been measured (0: three blocks; profiling)")
     ap.add_argument("--workload", default="c3", choices=["streams"] + sorted(STREAM_WORKLOADS) + sorted(TP_WORKLOADS),
                     help="c3 (= streams, the default): one independent request stream per GPU; c2: draft-only tree build; c4: "
                          "Llama-3-8B/3.2-1B shapes, prompt 1024; tp70b / tp7b: one stream with the target cut across all ranks")
@@ -659,7 +663,8 @@ def main():
         print(json.dumps({"operator_sweep": operator_sweep(torch, be, dev, reps=max(1, min(args.steps, 20)))}))
         return
     if args.qmm_sweep:
-        print(json.dumps({"qmm_sweep": qmm_sweep(torch, be, dev)}))
+        print(json.dumps({"qmm_sweep": qmm_sweep(torch, be, dev, launches=args.launches,
+                                                 rows=(args.rows,) if args.rows else (1, 8, 16, 24, 32))}))
         return
     tname, dname, PROMPT, DEPTH, VERIFY, metric = STREAM_WORKLOADS[args.workload]
     warmup = max(args.warmup, 3)
@@ -716,7 +721,7 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     torch.cuda.nvtx.range_push("timed_steps")
-    secs, produced = timed_blocks(torch, dist, world, dec, K, snapshot)
+    secs, produced = timed_blocks(torch, dist, world, dec, K, snapshot, args.min_seconds)
     torch.cuda.nvtx.range_pop()
     if not sampler.rows:
         for _ in range(K):                                  # keep the GPU busy while one direct query runs

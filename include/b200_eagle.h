@@ -133,13 +133,15 @@ size_t b200_qmm_tiled_workspace_bytes(int M, int N, int K);
 int b200_qmm_tiled(const void* x, const void* wt, const void* wt2, const void* bias, const void* extra, void* y,
                    int M, int N, int K, int epilogue, void* workspace, size_t workspace_bytes, void* stream);
 
-/* The same product (plain epilogue: y = fp16(acc) [+ bias, in fp16]) on the tcgen05 tensor cores: the
- * dequantised fp16 weights (exact q*s+b, rounded once) go through shared memory as 128-row tiles, one thread per
- * CTA issues tcgen05.mma with the accumulator in tensor memory.  Same streaming weight layout; M <= 128 (one
- * weight read serves up to 128 token rows: the shape of prompt ingestion),
- * N % 128 == 0, K % 128 == 0.  workspace: b200_qmm_umma_workspace_bytes bytes (the activations re-laid for the
- * tensor cores + an error word, int 0 of the workspace, non-zero if a bounded wait gave up; zero it before
- * the first use).  Replaces qmm_kernel.py:79-124 like b200_qmm. */
+/* The same product (plain epilogue: y = fp16(acc) [+ bias, in fp16]) on the tcgen05 tensor cores: sixteen warps
+ * expand the packed records (exact q*s+b, rounded once) and write the fp16 weights with tcgen05.st straight into
+ * 128-row tiles in tensor memory (the weights never pass through shared memory as fp16), one thread per CTA issues
+ * tcgen05.mma (weights from tensor memory, activations read in place from the bulk-copied stage in shared memory)
+ * with the accumulator in tensor memory.  Same streaming weight layout; M <= 128 (one weight read serves up to 128
+ * token rows: the shape of prompt ingestion), N % 128 == 0, K % 128 == 0.  workspace: b200_qmm_umma_workspace_bytes
+ * bytes (the activations in the tensor cores' K-major core-matrix order, written by a relayout kernel that this call
+ * launches first, + an error word, int 0 of the workspace, non-zero if a bounded wait gave up; zero it before the
+ * first use).  Replaces qmm_kernel.py:79-124 like b200_qmm. */
 size_t b200_qmm_umma_workspace_bytes(int M, int K);
 int b200_qmm_umma(const void* x, const void* w_tiled, const void* bias, void* y, int M, int N, int K,
                   void* workspace, size_t workspace_bytes, void* stream);

@@ -4,11 +4,11 @@ Drop-in for the hot path of 0seba/mlx-eagle-spec-decoding-tree: the operator
 modules keep the reference's names and call signatures, the work is done by
 ``libb200eagle.so`` (hand-written CUDA behind a C ABI, see ``include/b200_eagle.h``).
 """
-from . import _lib, quantize, qmm_kernel, llama, eagle, rope  # noqa: F401
+from . import _lib, quantize, qmm_kernel, llama, eagle, rope, load  # noqa: F401
 from .qmm_kernel import matmul  # noqa: F401
 from .rope import rope_positions  # noqa: F401
 from .llama import Model, ModelArgs, KVCache, shape_preset  # noqa: F401
 from .eagle import SpecDecoder, generate_step, spec_step  # noqa: F401
 
 __all__ = ["matmul", "rope_positions", "Model", "ModelArgs", "KVCache", "shape_preset", "SpecDecoder",
-           "generate_step", "spec_step", "qmm_kernel", "quantize", "llama", "eagle", "rope"]
+           "generate_step", "spec_step", "qmm_kernel", "quantize", "llama", "eagle", "rope", "load"]

@@ -798,7 +798,6 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
             c.ruse++;
             rstd_done = true;
         }
-        stamp(p, c, 3);
         // ---- K-parts of a tile -> its first warp, through shared memory, in part order
         if (kw > 1) {
             float4* sc = reinterpret_cast<float4*>(c.scratch);
@@ -1033,6 +1032,7 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
                 }
             }
         }
+        stamp(p, c, 3);                // epilogue of the item issued
     }
 }
 

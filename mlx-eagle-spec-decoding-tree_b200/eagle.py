@@ -402,13 +402,14 @@ def generate_step(prompt: torch.Tensor, base_model: Model, draft_model: Model, p
 
 
 def parse_args(argv=None):
-    """CLI flags of ``mlx_eagle.py:620-681``; model names are shape presets (random-init weights),
-    since no checkpoint or tokenizer can be downloaded here, and the prompt is a token count."""
+    """CLI flags of ``mlx_eagle.py:620-681``; a model is a local checkpoint directory or a shape preset
+    (random-init weights: nothing can be downloaded where this was written)."""
     p = argparse.ArgumentParser(description="Tree speculative decoding on B200 with seeded random-init models.")
     p.add_argument("--draft-model", type=str, default="qwen2-0.5b")
     p.add_argument("--base-model", type=str, default="qwen2-7b")
     p.add_argument("--prompt", type=str, required=True,
-                   help="number of seeded random prompt tokens, or comma-separated token ids")
+                   help="text (with a checkpoint that has a tokenizer), comma-separated token ids, or a number of seeded "
+                        "random prompt tokens")
     p.add_argument("--depth", type=int, default=1)
     p.add_argument("--verify-num-tokens", type=int, default=15, help="7, 15, 23 or 31")
     p.add_argument("--max-tokens", type=int, default=300)
@@ -420,19 +421,39 @@ def parse_args(argv=None):
 
 
 def main(argv=None):
+    """``python -m`` entry with the reference's flags (``mlx_eagle.py:683-756``).  ``--draft-model`` / ``--base-model``
+    name either a local MLX-format 4-bit checkpoint directory (``load.load``, the counterpart of ``mlx_utils.load``)
+    or a shape preset with seeded random-init weights; ``--prompt`` is text (needs the checkpoint's tokenizer),
+    comma-separated token ids, or a count of seeded random tokens."""
+    import os
+    from . import load as _load
     args = parse_args(argv)
     dev = torch.device("cuda", torch.cuda.current_device())
-    draft = Model.random_init(shape_preset(args.draft_model), args.seed + 1, dev).relayout()
-    base = Model.random_init(shape_preset(args.base_model), args.seed + 2, dev).relayout()
-    if "," in args.prompt or not args.prompt.isdigit():
-        ids = torch.tensor([int(t) for t in args.prompt.split(",")], dtype=torch.int32)
-    else:
+
+    def get(name, seed):
+        if os.path.isdir(name):
+            m, tok = _load.load(name, dev)
+            return m.relayout(), tok
+        return Model.random_init(shape_preset(name), seed, dev).relayout(), None
+
+    draft, _ = get(args.draft_model, args.seed + 1)
+    base, tokenizer = get(args.base_model, args.seed + 2)
+    if args.prompt.isdigit():
         g = torch.Generator().manual_seed(args.seed)
         ids = torch.randint(0, min(draft.args.vocab_size, base.args.vocab_size), (int(args.prompt),), generator=g,
                             dtype=torch.int32)
+    elif all(t.strip().lstrip("-").isdigit() for t in args.prompt.split(",")):
+        ids = torch.tensor([int(t) for t in args.prompt.split(",")], dtype=torch.int32)
+    elif tokenizer is not None:
+        ids = torch.tensor(tokenizer.encode(args.prompt), dtype=torch.int32)
+    else:
+        raise SystemExit("a text prompt needs a checkpoint directory with tokenizer files as --base-model")
+    eos = args.eos_token_id
+    if eos is None and tokenizer is not None and getattr(tokenizer, "eos_token_id", None) is not None:
+        eos = int(tokenizer.eos_token_id)
     generate_step(ids, base, draft, k=8, depth=args.depth, verify_num_tokens=args.verify_num_tokens,
                   max_tokens=args.max_tokens, prefill_step_size=512, N=args.max_generation_steps,
-                  eos_token_id=args.eos_token_id, clip=args.clip)
+                  eos_token_id=eos, clip=args.clip, tokenizer=tokenizer)
 
 
 if __name__ == "__main__":
