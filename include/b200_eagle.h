@@ -332,6 +332,14 @@ int b200_tp_argmax_combine(unsigned long long* best_key, int R, unsigned int ind
                            int tp_rank, void* const* tp_peers, void* stream);
 int b200_forward(const b200_forward_desc* desc, void* stream);
 
+/* Measurement aid, not part of the model interface: overrides the work split the planner would choose for the
+ * matmul phases of later b200_forward calls.  spec = "A=kw:cps:splits,C=...,D=...,E=...,H=..." (A q|k|v, C o_proj,
+ * D gate/up, E down_proj, H vocabulary projection; kw = K-parts inside a CTA, 1/2/4/8; cps = 128-column chunks of K
+ * per ring stage; splits = split of K across CTAs); values that do not fit the shape are ignored; NULL or ""
+ * restores the planner.  The workspace size depends on the split: query b200_forward_workspace_bytes again after a
+ * hint.  The same string is read once from the environment variable B200_FWD_PLAN.  No counterpart in the reference. */
+void b200_forward_plan_hint(const char* spec);
+
 /* ------------------------------------------------------------------------------------------
  * Draft tree, acceptance and compaction.  One request; k = 8 children per node.
  * ctl is int32[16]: [0] committed length of the target cache, [1] of the draft cache, [2] accept

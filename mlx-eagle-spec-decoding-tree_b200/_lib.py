@@ -98,6 +98,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_logits_argmax.argtypes = [vp, i32, i32, vp, vp]
     l.b200_tree_accept.restype = i32
     l.b200_tree_accept.argtypes = [i32] + [vp] * 10
+    l.b200_forward_plan_hint.restype = None
+    l.b200_forward_plan_hint.argtypes = [ctypes.c_char_p]
     l.b200_forward_workspace_bytes.restype = sz
     l.b200_forward_workspace_bytes.argtypes = [ctypes.POINTER(ForwardDesc)]
     l.b200_forward_tp_buffer_bytes.restype = sz

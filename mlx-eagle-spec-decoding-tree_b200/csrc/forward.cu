@@ -31,6 +31,11 @@
 // cluster multicast.
 #include <cuda.h>
 
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
 #include "pipeline.cuh"
 #include "tp_layout.cuh"
 #include "qmm_common.cuh"
@@ -82,7 +87,7 @@ struct LayerPtrs {                 // one entry per layer, in device memory (8 p
 
 struct PhasePlan {
     int row_items, splits, chunks_per_split;   // items along N, split-K ways across CTAs
-    int kw, U;                                 // K-parts per tile inside a CTA (8/kw tiles per item), records per warp and stage
+    int kw, cps;                               // K-parts per tile inside a CTA (8/kw tiles per item), chunks of K per ring stage
 };
 
 struct FwdParams {
@@ -527,9 +532,11 @@ __device__ __forceinline__ void tp_reduce_phase(const FwdParams& p, Ctx& c, cons
 // consumer warps are arranged as TPI tiles x kw K-parts: warp (j, i) owns tile j of the item and, in
 // every ring stage, the chunks i, i+kw, ... of that stage.  The K-parts of a tile are added in
 // shared memory in part order, so small matrices need no split-K through global memory.  A stage
-// holds CPS = kw*U chunks: for every chunk the TPI records of the item's tiles (contiguous in the
-// streaming layout for TPI <= 4), then the same for up_proj in dual mode, then the activations of
-// the stage's K range (one bulk copy per token row).
+// holds CPS chunks (the planner takes as many as fit: narrow items leave most of the stage to the
+// activations, so that a whole K of a few thousand is in flight when the barrier opens): for every chunk
+// the TPI records of the item's tiles (contiguous in the streaming layout for TPI <= 4), then the same
+// for up_proj in dual mode, then, right behind the weights, the activations of the stage's K range
+// (one bulk copy: they are contiguous in the chunk-major layout).
 
 // rstd[m] = rsqrt(mean(h[m]^2) + eps) from the per-16-column sums of squares the producer of h left in p.ssq, by
 // the PRODUCER warp, once per phase, right after it has issued the phase's first activation copies: the loads
@@ -577,10 +584,11 @@ __device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QD
                                             const bool dual, const bool need_rstd) {
     using G = Geo<MT>;
     const int lane = c.lane;
-    const int kw = d.pl.kw, U = d.pl.U;
-    const int TPI = kWN / kw, CPS = kw * U;
+    const int kw = d.pl.kw;
+    const int TPI = kWN / kw, CPS = d.pl.cps;
     const int chunk_bytes = TPI * kRec;
     const int up_off = CPS * chunk_bytes;
+    const int x_off = (dual ? 2 : 1) * up_off;            // the activations follow the weights of the stage
     const int nchunks_total = d.K / kChunkK;
     const int nblocks = (d.N + 63) / 64;
     const int nitems = d.pl.row_items * d.pl.splits;
@@ -605,7 +613,7 @@ __device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QD
         for (int i = 0; i < G::NST; i++)
             if (lane == i) { my_slot = pend_slot[i]; my_k0 = pend_k0[i]; my_recs = pend_recs[i]; }
         if (lane < npend)          // the activation runs of the stages queued before the barrier opened
-            bulk_copy_g2s_hint(smem_u32(c.ring + my_slot * G::STAGE + kWArea), x_src(my_k0), (uint32_t)(my_recs * G::MP * kXRow),
+            bulk_copy_g2s_hint(smem_u32(c.ring + my_slot * G::STAGE + x_off), x_src(my_k0), (uint32_t)(my_recs * G::MP * kXRow),
                                smem_u32(c.full + my_slot), xpolicy);
         npend = 0;
         ready = true;
@@ -679,7 +687,7 @@ __device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QD
             }
             const bool xlane = ready && lane == ncw;
             if (xlane) {
-                cdst = smem_u32(stage + kWArea);
+                cdst = smem_u32(stage + x_off);
                 csrc = x_src(k0);
                 cbytes = (uint32_t)(recs * G::MP * kXRow);
             }
@@ -704,12 +712,13 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
     constexpr int MP = MT * 8;
     const int lane = c.lane, warp = c.warp;
     const int g = lane >> 2, t = lane & 3;
-    const int kw = d.pl.kw, U = d.pl.U;
-    const int TPI = kWN / kw, CPS = kw * U;
+    const int kw = d.pl.kw;
+    const int TPI = kWN / kw, CPS = d.pl.cps;
     const int R = TPI * 16;                      // output rows (of each matrix) per item
     const int TW = S * R;
     const int chunk_bytes = TPI * kRec;
     const int up_off = CPS * chunk_bytes;
+    const int x_off = S * up_off;
     const int tj = warp / kw, ki = warp - tj * kw;    // tile of the item, K-part
     // record of (chunk cc of the stage, tile tj): whole blocks arrive as [block][chunk][4 tiles], parts of a block as [chunk][tiles]
     const int rec_base = (TPI >= 4) ? ((tj >> 2) * CPS * 4 * kRec + (tj & 3) * kRec) : tj * kRec;
@@ -748,8 +757,10 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
             if (ok) {
                 const unsigned char* stage = c.ring + slot * G::STAGE;
                 const int nrec = min(CPS, n - st * CPS);
-                for (int cc = ki; cc < nrec; cc += kw) {
-                    const unsigned char* xrow = stage + kWArea + (cc * MP + g) * kXRow + t * 16;
+                // K-part ki owns the chunks of the ITEM whose index is ki modulo kw (stages need not hold a multiple of kw)
+                const int first = (ki - st * CPS) & (kw - 1);       // kw is a power of two
+                for (int cc = first; cc < nrec; cc += kw) {
+                    const unsigned char* xrow = stage + x_off + (cc * MP + g) * kXRow + t * 16;
                     uint4 w[S][2];
                     uint2 sb[S][2];
 #pragma unroll
@@ -1940,41 +1951,84 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
 // spends about half a microsecond per record while all warps of an SM stream, a shared-memory
 // K reduction costs a few tenths, a split through global memory four to five (partial sums out,
 // ticket, partial sums back in).
-PhasePlan make_plan(int N, int K, int grid, int mt, bool dual) {
+// Tuning hook (b200_forward_plan_hint, or the environment variable B200_FWD_PLAN read at the first launch):
+// "A=kw:cps:splits,D=..." (phases A C D E, H = vocabulary projection) replaces the planner's choice for a
+// phase wherever the values are feasible for the shape.  For measuring plans on the GPU, not an interface of the model.
+struct PlanOverride { int kw, cps, splits; };
+PlanOverride g_plan_override[5];
+bool g_plan_override_init = false;
+void parse_plan_hint(const char* e) {
+    for (auto& o : g_plan_override) o = PlanOverride{0, 0, 0};
+    g_plan_override_init = true;
+    if (e == nullptr) return;
+    const char* names = "ACDEH";
+    while (*e) {
+        const char* f = std::strchr(names, *e);
+        int kw = 0, cps = 0, sp = 0;
+        if (f && e[1] == '=' && std::sscanf(e + 2, "%d:%d:%d", &kw, &cps, &sp) == 3) g_plan_override[f - names] = PlanOverride{kw, cps, sp};
+        const char* nx = std::strchr(e, ',');
+        if (!nx) break;
+        e = nx + 1;
+    }
+}
+const PlanOverride* plan_override(int which) {
+    if (!g_plan_override_init) parse_plan_hint(std::getenv("B200_FWD_PLAN"));
+    return g_plan_override[which].kw > 0 ? &g_plan_override[which] : nullptr;
+}
+
+// Chooses, per phase, the K-parts inside a CTA (kw), the chunks of K per ring stage (cps) and the split of K
+// across CTAs.  A stage holds cps x (the item's records [x2 in dual mode] + the activations of a chunk); narrow
+// items (few tiles) therefore take many chunks per stage, and a K of a few thousand is wholly in flight when
+// the barrier before the phase opens.  The cost model is in microseconds, fitted to phase timelines on B200:
+// a record costs a warp ~0.19 us (two warps per scheduler), the first stage lands ~1.1 us after the barrier,
+// every further generation of the three-stage ring another ~1 us unless the arithmetic hides it, adding the
+// K-parts through shared memory 0.4 us, a split through global memory (partial sums out, ticket, partial sums
+// in) ~3 us on the last CTA; an SM takes ~55 KB per us through its ring (weights from HBM and activations from
+// L2 together), which is what keeps wide-K phases on split-K: without it every CTA re-reads all of x.
+constexpr double kRingBytesPerUs = 55e3;
+PhasePlan make_plan(int N, int K, int grid, int mt, bool dual, int which, bool hinted = true) {
     const int nchunks = K / kChunkK;
     const int tiles = (N + 15) / 16;
-    const int cps_max = mt == 1 ? 8 : (mt == 2 ? 4 : 2);
-    const int umax = dual ? 2 : 4;                      // weight area: 32 records = 16 pairs per stage
+    const int nmat = dual ? 2 : 1;
+    const int stage_bytes = kWArea + (mt == 1 ? 8 : (mt == 2 ? 4 : 2)) * mt * 8 * kXRow;   // Geo<MT>::STAGE
+    const double t_rec = 0.19 * (mt == 1 ? 0.85 : (mt == 2 ? 1.0 : (mt == 3 ? 1.3 : 1.6)));
     PhasePlan best{};
     double best_cost = 1e30;
+    const PlanOverride* ov = hinted ? plan_override(which) : nullptr;
     for (int kw = 1; kw <= 8; kw *= 2) {
-        if (kw > cps_max || kw > nchunks) continue;
+        if (kw > nchunks) continue;
         if (dual && mt >= 3 && kw > 1) continue;        // the K-part scratch holds 8 warps x 2 matrices x 2 token tiles
+        if (ov && kw != ov->kw) continue;
         const int tpi = kWN / kw;
         const int row_items = (tiles + tpi - 1) / tpi;
-        int U = cps_max / kw;
-        if (U > umax) U = umax;
+        int fit = stage_bytes / (nmat * tpi * kRec + mt * 8 * kXRow);
+        if (tpi < 4) fit = std::min(fit, 31 / nmat);     // parts of a block: one bulk copy per chunk and matrix, <= 31 lanes
+        if (fit < kw) continue;                          // every K-part needs a chunk of the stage
         const int max_splits = row_items < kMaxCounters ? (nchunks + 3) / 4 : 1;
         for (int splits = 1; splits <= max_splits; splits++) {
-            const int cps = (nchunks + splits - 1) / splits;
-            const int eff = (nchunks + cps - 1) / cps;
+            if (ov && splits != ov->splits) continue;
+            const int per_split = (nchunks + splits - 1) / splits;
+            const int eff = (nchunks + per_split - 1) / per_split;
             if (eff != splits) continue;
             const long long items = (long long)row_items * splits;
             const long long rounds = (items + grid - 1) / grid;
-            const int rec_per_warp = ((cps + kw - 1) / kw) * (dual ? 2 : 1);
-            // bulk copies cost ~0.03 us each to issue (lanes issue in parallel): whole blocks come as one run per
-            // stage, parts of a block chunk by chunk; measured: a split through global memory adds 4-5 us
-            const int stages = (cps + kw * U - 1) / (kw * U);
-            const int ops_per_stage = 1 + (dual ? 2 : 1) * (tpi >= 4 ? tpi / 4 : kw * U);
-            const double cost = rounds * (0.5 * rec_per_warp + 0.03 * stages * ops_per_stage + (kw > 1 ? 0.3 : 0.0) +
-                                          (splits > 1 ? 4.5 : 0.0) + 1.0);
+            int stages = (per_split + fit - 1) / fit;
+            int cps = (per_split + stages - 1) / stages;                     // even stages
+            if (ov && ov->cps >= kw && ov->cps <= fit) { cps = ov->cps; stages = (per_split + cps - 1) / cps; }
+            const int rec_per_warp = ((per_split + kw - 1) / kw) * nmat;
+            const double compute = rec_per_warp * t_rec;
+            const double refill = ((stages + 2) / 3 - 1) * 1.0;
+            const double stream = (double)per_split * (nmat * tpi * kRec + mt * 8 * kXRow) / kRingBytesPerUs;
+            const double cost = rounds * (1.1 + std::max(std::max(compute, refill), stream) + 0.02 * stages + (kw > 1 ? 0.4 : 0.0) +
+                                          (splits > 1 ? 3.0 : 0.0) + 0.8);
             if (cost < best_cost - 1e-9) {
                 best_cost = cost;
-                best.row_items = row_items; best.splits = splits; best.chunks_per_split = cps; best.kw = kw; best.U = U;
+                best.row_items = row_items; best.splits = splits; best.chunks_per_split = per_split; best.kw = kw; best.cps = cps;
             }
             if (items >= 4LL * grid) break;             // more splits cannot help any more
         }
     }
+    if (ov && best_cost > 1e29) return make_plan(N, K, grid, mt, dual, which, false);    // the hint does not fit this shape
     return best;
 }
 
@@ -2026,20 +2080,20 @@ WsLayout fwd_layout(const b200_forward_desc* d, PhasePlan (&plan)[5], int* grid_
     const int mp = ((d->M + 7) / 8) * 8;
     const int nqkv = (d->n_heads + 2 * d->n_kv_heads) * d->head_dim;
     const int mt = mp / 8;
-    plan[PLAN_A] = make_plan(nqkv, d->hidden, grid, mt, false);
-    plan[PLAN_C] = make_plan(d->hidden, d->n_heads * d->head_dim, grid, mt, false);
-    plan[PLAN_D] = make_plan(d->intermediate, d->hidden, grid, mt, true);
-    plan[PLAN_E] = make_plan(d->hidden, d->intermediate, grid, mt, false);
+    plan[PLAN_A] = make_plan(nqkv, d->hidden, grid, mt, false, PLAN_A);
+    plan[PLAN_C] = make_plan(d->hidden, d->n_heads * d->head_dim, grid, mt, false, PLAN_C);
+    plan[PLAN_D] = make_plan(d->intermediate, d->hidden, grid, mt, true, PLAN_D);
+    plan[PLAN_E] = make_plan(d->hidden, d->intermediate, grid, mt, false, PLAN_E);
     const int head_rows = d->head_rows > 0 ? d->head_rows : d->vocab;
-    plan[PLAN_HEAD] = make_plan(head_rows, d->hidden, grid, mt, false);
+    plan[PLAN_HEAD] = make_plan(head_rows, d->hidden, grid, mt, false, PLAN_HEAD);
     // split-K scratch: sized for any row count up to 32, so one workspace serves every pass shape
     size_t pb = 0;
     for (int m = 1; m <= 4; m++) {
-        PhasePlan q[5] = {make_plan(nqkv, d->hidden, grid, m, false),
-                          make_plan(d->hidden, d->n_heads * d->head_dim, grid, m, false),
-                          make_plan(d->intermediate, d->hidden, grid, m, true),
-                          make_plan(d->hidden, d->intermediate, grid, m, false),
-                          make_plan(head_rows, d->hidden, grid, m, false)};
+        PhasePlan q[5] = {make_plan(nqkv, d->hidden, grid, m, false, PLAN_A),
+                          make_plan(d->hidden, d->n_heads * d->head_dim, grid, m, false, PLAN_C),
+                          make_plan(d->intermediate, d->hidden, grid, m, true, PLAN_D),
+                          make_plan(d->hidden, d->intermediate, grid, m, false, PLAN_E),
+                          make_plan(head_rows, d->hidden, grid, m, false, PLAN_HEAD)};
         for (int i = 0; i < 5; i++) pb = std::max(pb, partial_bytes(q[i], m * 8, i == PLAN_D));
     }
     WsLayout w{};
@@ -2129,6 +2183,8 @@ size_t b200_forward_tp_buffer_bytes(int hidden) {
     if (hidden < 128 || (hidden % 128) != 0) return 0;
     return (size_t)kTpHeader + (size_t)2 * 32 * hidden * sizeof(float) + (size_t)2 * 32 * hidden * sizeof(__half);
 }
+
+void b200_forward_plan_hint(const char* spec) { parse_plan_hint(spec); }
 
 size_t b200_forward_workspace_bytes(const b200_forward_desc* d) {
     if (!fwd_shape_ok(d)) return 0;
