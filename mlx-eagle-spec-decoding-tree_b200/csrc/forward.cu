@@ -221,6 +221,12 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                  : "r"(addr));
 }
 
+__device__ __forceinline__ int atom_add_acq_rel_gpu(int* addr, int v) {
+    int old;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;\n" : "=r"(old) : "l"(addr), "r"(v) : "memory");
+    return old;
+}
+
 __device__ __forceinline__ void raise_error(const FwdParams& p, Ctx& c, int code) {
     *c.abort_flag = 1;
     atomicCAS(p.sync + kSyncErr, 0, code);
@@ -858,12 +864,12 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
             }
             consumer_sync(kNCons);
             if (threadIdx.x == 0) {
-                __threadfence();
-                const int old = atomicAdd(p.counter + row_item, 1);
+                // one acquire-release ticket: releases this CTA's partial sums (ordered before it by the bar.sync
+                // above), and acquires the other splits' for the CTA that draws the last ticket
+                const int old = atom_add_acq_rel_gpu(p.counter + row_item, 1);
                 const int last = (old == d.pl.splits - 1);
                 *c.is_last = last;
                 if (last) p.counter[row_item] = 0;
-                __threadfence();
             }
             consumer_sync(kNCons);
             if (*c.is_last) {
