@@ -613,6 +613,65 @@ def timed_blocks(torch, dist, world, dec, K, snapshot, min_seconds=MIN_TIMED_SEC
     return secs, produced
 
 
+def batched_requests_numbers(torch, be, base, draft, depth, verify, prompt_len, K, warmup, dev, min_seconds):
+    """The same step for several requests at once on this GPU (``BatchSpecDecoder``: every pass is shared, so each
+    weight read serves all requests): as many requests as fit a 32-row pass, K-step blocks replayed from one decode
+    state like the headline, CUDA events; plus the public call from pinned host prompts.  Not the headline: the
+    workload of the metric is one request per GPU."""
+    R = min(4, 32 // (verify + 1), 32 // 8)
+    if R < 2:
+        return None
+    Kb = min(K, 100)
+    rows = min(2048, ((prompt_len + (depth + 2) * (warmup + Kb + 8) + verify + 192 + 63) // 64) * 64)
+    dec = be.BatchSpecDecoder(base, draft, depth, verify, cache_rows=rows, requests=R,
+                              max_out_tokens=(depth + 2) * (warmup + Kb) + 512, max_steps=warmup + Kb + 64)
+    dec.warmup(capture=True)
+    vocab = min(draft.args.vocab_size, base.args.vocab_size)
+    prompts = [torch.randint(0, vocab, (prompt_len,), generator=torch.Generator().manual_seed(4321 + r),
+                             dtype=torch.int32).pin_memory() for r in range(R)]
+    dec.prefill(prompts)
+    for _ in range(warmup):
+        dec.replay()
+    torch.cuda.synchronize()
+    ctl0 = dec.ctl.clone()
+    y0 = [s.y.clone() for s in dec.slots]
+    secs, produced = [], None
+    while len(secs) < 3 or (sum(secs) < min_seconds / 2 and len(secs) < 200):
+        dec.ctl.copy_(ctl0)
+        for s, y in zip(dec.slots, y0):
+            s.y.copy_(y)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(Kb):
+            dec.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        secs.append(e0.elapsed_time(e1) / 1e3)
+        produced = int((dec.ctl[:, 3] - ctl0[:, 3]).sum())
+    sec = statistics.median(secs)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    res = dec.generate(prompts, max_tokens=Kb, N=Kb)
+    torch.cuda.synchronize()
+    e2e_sec = time.perf_counter() - t0
+    e2e_tokens = sum(r["produced"] for r in res)
+    mt = (R * (verify + 1) + 7) // 8
+    target = roofline_block(torch, base, dec.slots[0].base_cache, min(32, R * (verify + 1)), prompt_len,
+                            f"forward_kernel<{mt},{base.args.head_dim}> at the rows of {R} requests (one cache: timing only)", reps=10)
+    out = {"requests_per_gpu": R, "tokens_per_second": produced / sec, "ms_per_step": 1e3 * sec / Kb, "steps": Kb,
+           "blocks": len(secs), "tokens_per_step": produced / Kb,
+           "e2e_tokens_per_second": e2e_tokens / e2e_sec,
+           "gpu_launches_per_step": dec.kernel_launches_per_step,
+           "target_pass_us_at_these_rows": target["us_per_launch"], "target_pass_frac_of_measured_peak": target["frac"],
+           "what": "BatchSpecDecoder: the requests share every draft and target pass (row groups of one launch, a KV slab "
+                   "and a committed length each); tree kernels, acceptance and compaction run per request; every request's "
+                   "tokens equal its single-request run (tests/test_batch_gpu.py)"}
+    del dec
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -807,6 +866,12 @@ def main():
                 "rest_ms": step_ms - line["roofline"]["us_per_launch"] / 1e3 - (DEPTH + 1) * dblk["us_per_launch"] / 1e3}
         if extras:
             line["qmm_sweep"] = qmm_sweep(torch, be, dev)
+        if extras and tname is not None and world == 1:
+            try:
+                line["config"]["batched_requests"] = batched_requests_numbers(
+                    torch, be, base, draft, DEPTH, VERIFY, PROMPT, K, warmup, dev, args.min_seconds)
+            except Exception as e:                         # the attachment must not take the headline down with it
+                line["config"]["batched_requests"] = {"error": f"{type(e).__name__}: {e}"}
     # ---- at N > 1: the tensor-parallel target on the same ranks (collective), attached to the line
     if world > 1 and extras and args.workload == "c3":
         tp = None

@@ -301,6 +301,14 @@ typedef struct b200_forward_desc {
                                  * result to every GPU (a second all-GPU barrier; needs hidden % (16 * tp_world) == 0).
                                  * Same bits either way.  The same value on every rank; zero the exchange buffers when
                                  * switching. */
+    int requests;               /* 0 or 1: one request.  2..4: the M rows are `requests` groups of M / requests rows, one
+                                 * group per request, so that several requests share every weight read (no counterpart in
+                                 * the reference, which decodes one request).  Request r then has its own committed length
+                                 * prefix[r], its own head-row offset row_index[r] (if row_index is given) and its own slab
+                                 * of kv_cache, laid out [requests][layers][2][kv heads][cache_rows][head_dim]; write_off
+                                 * and tail apply to each; attention never crosses requests; rows_out counts rows per
+                                 * request and logits is [requests * rows_out][vocab].  Needs cache_rows <= 2048 (single-
+                                 * phase attention) and tp_world <= 1. */
 } b200_forward_desc;
 
 size_t b200_forward_workspace_bytes(const b200_forward_desc* desc);

@@ -7,8 +7,8 @@ modules keep the reference's names and call signatures, the work is done by
 from . import _lib, quantize, qmm_kernel, llama, eagle, rope, load  # noqa: F401
 from .qmm_kernel import matmul  # noqa: F401
 from .rope import rope_positions  # noqa: F401
-from .llama import Model, ModelArgs, KVCache, shape_preset  # noqa: F401
-from .eagle import SpecDecoder, generate_step, spec_step  # noqa: F401
+from .llama import Model, ModelArgs, KVCache, BatchKVCache, shape_preset  # noqa: F401
+from .eagle import SpecDecoder, BatchSpecDecoder, generate_step, spec_step  # noqa: F401
 
-__all__ = ["matmul", "rope_positions", "Model", "ModelArgs", "KVCache", "shape_preset", "SpecDecoder",
+__all__ = ["matmul", "rope_positions", "Model", "ModelArgs", "KVCache", "shape_preset", "SpecDecoder", "BatchSpecDecoder", "BatchKVCache",
            "generate_step", "spec_step", "qmm_kernel", "quantize", "llama", "eagle", "rope", "load"]

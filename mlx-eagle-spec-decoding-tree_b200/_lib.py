@@ -146,7 +146,7 @@ class ForwardDesc(ctypes.Structure):
         + [("workspace_bytes", ctypes.c_size_t), ("timeline", ctypes.c_void_p), ("timeline_pitch", ctypes.c_int),
            ("phase_mask", ctypes.c_int), ("tp_world", ctypes.c_int), ("tp_rank", ctypes.c_int),
            ("head_rows", ctypes.c_int), ("grid_ctas", ctypes.c_int), ("tp_peers", ctypes.c_void_p * 8),
-           ("scales_in_fast_range", ctypes.c_int), ("tp_two_shot", ctypes.c_int)])
+           ("scales_in_fast_range", ctypes.c_int), ("tp_two_shot", ctypes.c_int), ("requests", ctypes.c_int)])
 
 
 def check(rc: int, what: str) -> None:

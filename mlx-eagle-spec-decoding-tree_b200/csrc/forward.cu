@@ -45,6 +45,7 @@ namespace {
 
 constexpr int kWN = 8;                        // consumer warps per CTA
 constexpr int kNCons = kWN * 32;
+constexpr int kMaxReq = 4;                   // requests that can share one pass
 constexpr int kFwdThreads = kNCons + 32;      // + one producer warp
 constexpr int kRec = 1152;                    // bytes per 16-row x 128-k weight record
 constexpr int kWArea = 8 * 4 * kRec;          // weight bytes of a ring stage: 8 (block, chunk) cells of 4 records
@@ -109,6 +110,12 @@ struct FwdParams {
     __half* kv;                    // [layers][2][Hkv][cap][HD]
     size_t kv_layer_stride, kv_half_stride;   // in halves
     int cap, write_off, tail;
+    // Several requests in one pass (nreq > 1): the M rows are nreq groups of mr rows; request r has its own
+    // committed length prefix[r], head-row offset row_index[r] and KV slab (kv + r * kv_req_stride); attention never
+    // crosses requests, every other phase just sees M rows.
+    int nreq, mr;
+    size_t kv_req_stride;          // in halves
+    int kv_req_rows;               // rows of the 2-D view of one request's slab (layers * 2 * Hkv * cap)
     int* sync;
     int* counter;
     float* ssq;
@@ -157,8 +164,18 @@ struct QDesc {
     PhasePlan pl;
     int xrows;                  // token rows of the pass
     int row_lo, row_cnt;        // token rows [row_lo, row_lo+row_cnt) are stored, as output rows 0.. (vocabulary projection)
+    int mr;                     // rows per request; 0 = one request.  Else request q = tok / mr stores its rows
+    const int* row_off;         //   [q*mr + row_off[q], +row_cnt) as output rows q*row_cnt .. (shared memory)
     bool y_tiled;               // output goes to the chunk-major padded layout (it is a later phase's matmul input)
 };
+
+// Output row of token row `tok` in a row-major result that keeps only selected rows, or -1.
+__device__ __forceinline__ int out_row(const QDesc& d, int tok) {
+    if (d.mr == 0) return (tok >= d.row_lo && tok < d.row_lo + d.row_cnt) ? tok - d.row_lo : -1;
+    const int q = tok / d.mr;
+    const int rel = tok - q * d.mr - d.row_off[q];
+    return (rel >= 0 && rel < d.row_cnt) ? q * d.row_cnt + rel : -1;
+}
 
 struct Ctx {
     unsigned char* ring;
@@ -169,6 +186,7 @@ struct Ctx {
     unsigned char* scratch;
     const LayerPtrs* ltab;        // the layer pointer table, copied to shared memory at kernel start
     volatile int* abort_flag;
+    const int* req_prefix;        // committed length of every request of the pass (shared memory)
     volatile uint32_t* s_epoch;   // grid barriers this CTA has seen complete (written by thread 0)
     int* is_last;
     float* s_rstd;
@@ -965,8 +983,9 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
                         }
                         if (d.y_tiled) {
                             *reinterpret_cast<uint4*>(d.y + xt_index(tok, n0, MP)) = *reinterpret_cast<const uint4*>(out);
-                        } else if (tok >= d.row_lo && tok < d.row_lo + d.row_cnt) {
-                            *reinterpret_cast<uint4*>(d.y + (size_t)(tok - d.row_lo) * d.N + n0) = *reinterpret_cast<const uint4*>(out);
+                        } else {
+                            const int orow = out_row(d, tok);
+                            if (orow >= 0) *reinterpret_cast<uint4*>(d.y + (size_t)orow * d.N + n0) = *reinterpret_cast<const uint4*>(out);
                         }
                     }
                 }
@@ -1043,8 +1062,12 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
                             o = __float2half_rn(acc[0][mt][i] * rs);
                             if (d.bias != nullptr) o = __hadd(o, d.bias[nn]);
                         }
-                        if (d.y_tiled) d.y[xt_index(tok, nn, MP)] = o;
-                        else if (tok >= d.row_lo && tok < d.row_lo + d.row_cnt) d.y[(size_t)(tok - d.row_lo) * d.N + nn] = o;
+                        if (d.y_tiled) {
+                            d.y[xt_index(tok, nn, MP)] = o;
+                        } else {
+                            const int orow = out_row(d, tok);
+                            if (orow >= 0) d.y[(size_t)orow * d.N + nn] = o;
+                        }
                     }
                 }
             }
@@ -1404,15 +1427,17 @@ __device__ __forceinline__ void attn_bp_produce(const FwdParams& p, Ctx& c, cons
     using A = AGeo<MT, HD>;
     const int lane = c.lane;
     const int Gq = p.Hq / p.Hkv;
-    const int ntiles = (p.M * Gq + 15) / 16;
-    const int nitems = p.Hkv * ntiles;
+    const int ntiles = (p.mr * Gq + 15) / 16;
+    const int nitems = p.nreq * p.Hkv * ntiles;           // item = (request, kv head, query tile)
     if ((int)blockIdx.x >= nitems) return;
     if (*c.abort_flag || !drain_stages<MT>(p, c)) return;
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-        const int hk = item / ntiles;
-        const int krow0 = ((layer * 2 + 0) * p.Hkv + hk) * p.cap;       // row of the cache viewed as [rows][HD]
-        const int vrow0 = ((layer * 2 + 1) * p.Hkv + hk) * p.cap;
-        for (int kb = 0; kb < a.nact; kb++, c.apos++) {
+        const int req = item / (p.Hkv * ntiles);
+        const int hk = (item / ntiles) % p.Hkv;
+        const int nact = p.nreq == 1 ? a.nact : min((c.req_prefix[req] + p.tail + kKeyBlock - 1) / kKeyBlock, p.nkb);
+        const int krow0 = req * p.kv_req_rows + ((layer * 2 + 0) * p.Hkv + hk) * p.cap;   // row of the cache viewed as [rows][HD]
+        const int vrow0 = req * p.kv_req_rows + ((layer * 2 + 1) * p.Hkv + hk) * p.cap;
+        for (int kb = 0; kb < nact; kb++, c.apos++) {
             const uint32_t slot = c.apos % A::NS, use = c.apos / A::NS;
             if (*c.abort_flag) return;
             if (use > 0 && !__all_sync(0xffffffffu, fwd_wait(smem_u32(c.aempty + slot), (use - 1) & 1u))) {
@@ -1444,20 +1469,25 @@ __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, cons
     const int lane = c.lane, warp = c.warp;
     const int g = lane >> 2, t = lane & 3;
     const int Gq = p.Hq / p.Hkv;
-    const int QR = p.M * Gq;
+    const int QR = p.mr * Gq;                      // query rows (token, head of the group) of one request and kv head
     const int ntiles = (QR + 15) / 16;
-    const int nitems = p.Hkv * ntiles;
-    const int prefix = a.prefix;
-    const int new0 = prefix + p.write_off;
+    const int nitems = p.nreq * p.Hkv * ntiles;
     __half* sq = reinterpret_cast<__half*>(c.scratch);
     __half* nkv = sq + 16 * KS;                    // [2][M][HD]: rotated k rows, then v rows, of this pass
     static_assert(16 * KS * 2 + 2 * 32 * HD * 2 <= kScratch, "query tile and new K/V rows must fit the scratch area");
     unsigned char* myslot = c.ring + (warp < NS ? warp : 0) * A::SLOT;
 
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-        const int hk = item / ntiles, rt = item - hk * ntiles;
+        const int req = item / (p.Hkv * ntiles);
+        const int hk = (item / ntiles) % p.Hkv, rt = item % ntiles;
+        const int prefix = p.nreq == 1 ? a.prefix : c.req_prefix[req];
+        const int nact = p.nreq == 1 ? a.nact : min((prefix + p.tail + kKeyBlock - 1) / kKeyBlock, p.nkb);
+        const int new0 = prefix + p.write_off;
+        const int mbase = req * p.mr;                      // first token row of the request
+        __half* const kc = a.kc + (size_t)req * p.kv_req_stride;
+        __half* const vc = a.vc + (size_t)req * p.kv_req_stride;
         const uint32_t n0 = c.apos;                        // first block of this item in the phase's block sequence
-        c.apos += a.nact;
+        c.apos += nact;
         stamp(p, c, 2);
         // ---- rotated queries of the tile -> padded tile in shared memory, by all threads
         {
@@ -1467,7 +1497,8 @@ __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, cons
                 const int r = rt * 16 + row;
                 uint4 o1 = make_uint4(0, 0, 0, 0), o2 = make_uint4(0, 0, 0, 0);
                 if (r < QR) {
-                    const int m = r / Gq, hh = hk * Gq + (r - m * Gq);
+                    const int ml = r / Gq, hh = hk * Gq + (r - ml * Gq);
+                    const int m = mbase + ml;
                     const __half* q = p.qkv + (size_t)m * p.NQKV + (size_t)hh * HD + cv * 8;
                     const uint4 x1v = __ldcg(reinterpret_cast<const uint4*>(q));
                     const uint4 x2v = __ldcg(reinterpret_cast<const uint4*>(q + HD / 2));
@@ -1496,18 +1527,18 @@ __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, cons
         //      tile's item of each kv head also appends them to the cache
         {
             const bool writer = (rt == 0);
-            for (int idx = threadIdx.x; idx < p.M * VPR; idx += kNCons) {
-                const int m = idx / VPR, cv = idx - m * VPR;
+            for (int idx = threadIdx.x; idx < p.mr * VPR; idx += kNCons) {
+                const int m = idx / VPR, cv = idx - m * VPR;          // m: row inside the request
                 const int key = new0 + m;
-                const __half* src = p.qkv + (size_t)m * p.NQKV;
+                const __half* src = p.qkv + (size_t)(mbase + m) * p.NQKV;
                 const uint4 vv = __ldcg(reinterpret_cast<const uint4*>(src + (size_t)(p.Hq + p.Hkv) * HD + (size_t)hk * HD + cv * 8));
-                *reinterpret_cast<uint4*>(nkv + (p.M + m) * HD + cv * 8) = vv;
-                if (writer && key < p.cap) *reinterpret_cast<uint4*>(a.vc + ((size_t)hk * p.cap + key) * HD + cv * 8) = vv;
+                *reinterpret_cast<uint4*>(nkv + (p.mr + m) * HD + cv * 8) = vv;
+                if (writer && key < p.cap) *reinterpret_cast<uint4*>(vc + ((size_t)hk * p.cap + key) * HD + cv * 8) = vv;
                 if (cv < VPR / 2) {
                     const __half* ksrc = src + (size_t)p.Hq * HD + (size_t)hk * HD;
                     const uint4 x1v = __ldcg(reinterpret_cast<const uint4*>(ksrc + cv * 8));
                     const uint4 x2v = __ldcg(reinterpret_cast<const uint4*>(ksrc + HD / 2 + cv * 8));
-                    const float4* csp = reinterpret_cast<const float4*>(p.cs + m * kCsPitch + cv * 8);
+                    const float4* csp = reinterpret_cast<const float4*>(p.cs + (mbase + m) * kCsPitch + cv * 8);
                     float4 cs4[4];
 #pragma unroll
                     for (int e = 0; e < 4; e++) cs4[e] = __ldcg(csp + e);
@@ -1525,7 +1556,7 @@ __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, cons
                     *reinterpret_cast<uint4*>(nkv + m * HD + cv * 8) = *reinterpret_cast<const uint4*>(k1);
                     *reinterpret_cast<uint4*>(nkv + m * HD + HD / 2 + cv * 8) = *reinterpret_cast<const uint4*>(k2);
                     if (writer && key < p.cap) {
-                        __half* kd = a.kc + ((size_t)hk * p.cap + key) * HD;
+                        __half* kd = kc + ((size_t)hk * p.cap + key) * HD;
                         *reinterpret_cast<uint4*>(kd + cv * 8) = *reinterpret_cast<const uint4*>(k1);
                         *reinterpret_cast<uint4*>(kd + HD / 2 + cv * 8) = *reinterpret_cast<const uint4*>(k2);
                     }
@@ -1538,7 +1569,7 @@ __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, cons
 
         const int r0 = rt * 16 + g, r1 = r0 + 8;
         const bool v0 = r0 < QR, v1 = r1 < QR;
-        const int m0 = v0 ? r0 / Gq : 0, m1 = v1 ? r1 / Gq : 0;
+        const int m0 = mbase + (v0 ? r0 / Gq : 0), m1 = mbase + (v1 ? r1 / Gq : 0);
         const unsigned long long mk0 = v0 ? p.mask[m0] : 0ull, mk1 = v1 ? p.mask[m1] : 0ull;
 
         float mrun0 = -INFINITY, mrun1 = -INFINITY, l0 = 0.f, l1 = 0.f;
@@ -1551,7 +1582,7 @@ __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, cons
         int nmine = 0;
         if (warp < NS) {
             const int kb_first = (int)((warp + NS - n0 % NS) % NS);
-            for (int kb = kb_first; kb < a.nact; kb += NS, c.ause++, nmine++) {
+            for (int kb = kb_first; kb < nact; kb += NS, c.ause++, nmine++) {
                 const int key0 = kb * kKeyBlock;
                 if (nmine > 0) {                           // the previous block of this warp is done: give its slot back
                     __syncwarp();
@@ -1567,14 +1598,14 @@ __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, cons
                 if (!ok) continue;
                 const uint32_t sk = smem_u32(myslot), sv = sk + NBX * kBox;
                 // this pass's own rows inside the block come from the rows prepared above
-                if (key0 + kKeyBlock > new0 && key0 < new0 + p.M) {
-                    for (int idx = lane; idx < p.M * VPR; idx += 32) {
+                if (key0 + kKeyBlock > new0 && key0 < new0 + p.mr) {
+                    for (int idx = lane; idx < p.mr * VPR; idx += 32) {
                         const int m = idx / VPR, cv = idx - m * VPR;
                         const int r = new0 + m - key0;
                         if (r < 0 || r >= kKeyBlock) continue;
                         *reinterpret_cast<uint4*>(myslot + swz(r, cv)) = *reinterpret_cast<const uint4*>(nkv + m * HD + cv * 8);
                         *reinterpret_cast<uint4*>(myslot + NBX * kBox + swz(r, cv)) =
-                            *reinterpret_cast<const uint4*>(nkv + (p.M + m) * HD + cv * 8);
+                            *reinterpret_cast<const uint4*>(nkv + (p.mr + m) * HD + cv * 8);
                     }
                     __syncwarp();
                 }
@@ -1699,7 +1730,7 @@ __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, cons
             constexpr int CPT = HD / 16;
             const int row = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * CPT;
             const int r = rt * 16 + row;
-            const int nw = a.nact < NS ? a.nact : NS;
+            const int nw = nact < NS ? nact : NS;
             if (r < QR) {
                 float mstar = -INFINITY;
                 for (int i = 0; i < nw; i++) {
@@ -1723,7 +1754,8 @@ __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, cons
                     }
                 }
                 const float inv = denom > 0.f ? 1.f / denom : 0.f;
-                const int m = r / Gq, hh = hk * Gq + (r - m * Gq);
+                const int ml = r / Gq, hh = hk * Gq + (r - ml * Gq);
+                const int m = mbase + ml;
                 __align__(16) __half out[CPT];
 #pragma unroll
                 for (int e = 0; e < CPT; e++) out[e] = __float2half_rn(acc[e] * inv);
@@ -1791,6 +1823,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
     __shared__ int s_abort, s_is_last;
     __shared__ uint32_t s_epoch;
     __shared__ float s_rstd[32];
+    __shared__ int s_prefix[kMaxReq], s_rowoff[kMaxReq];
 
     Ctx c;
     c.ring = smem;
@@ -1815,6 +1848,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
     c.s_epoch = &s_epoch;
     c.is_last = &s_is_last;
     c.s_rstd = s_rstd;
+    c.req_prefix = s_prefix;
 
     c.pos = 0;
     c.epoch = 0;
@@ -1824,6 +1858,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
     c.lane = threadIdx.x & 31;
     c.warp = threadIdx.x >> 5;
 
+    if ((int)threadIdx.x < p.nreq) {
+        s_prefix[threadIdx.x] = p.prefix[threadIdx.x];
+        s_rowoff[threadIdx.x] = p.row_index ? p.row_index[threadIdx.x] : 0;
+    }
     if (threadIdx.x == 0) {
         s_abort = 0;
         s_epoch = 0;
@@ -1886,6 +1924,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             QDesc d;
             d.xrows = p.M;
             d.row_lo = 0; d.row_cnt = p.M;
+            d.mr = 0; d.row_off = s_rowoff;
             d.y_tiled = false;
             d.w1 = nullptr; d.bias = nullptr; d.wn = nullptr;
             int epi = TP ? EPI_TP : EPI_RESID;
@@ -1904,6 +1943,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
                 d.N = p.H; d.K = p.I; d.pl = p.plan[PLAN_E];
             } else {                                   // K_HEAD, on the selected rows
                 d.row_lo = row_off; d.row_cnt = p.rows_out;       // all rows are multiplied, the selected ones stored
+                if (p.nreq > 1) d.mr = p.mr;                      // ... rows_out per request
                 d.x = p.hw; d.w0 = p.head_w; d.y = p.logits;
                 d.N = p.head_rows; d.K = p.H; d.pl = p.plan[PLAN_HEAD]; epi = EPI_HEAD;
             }
@@ -2068,7 +2108,8 @@ bool fwd_shape_ok(const b200_forward_desc* d) {
     if (d->n_heads < 1 || d->n_kv_heads < 1 || (d->n_heads % d->n_kv_heads) != 0) return false;
     if (((d->n_heads * d->head_dim) % 128) != 0) return false;
     if (d->vocab < 8 || (d->vocab % 8) != 0 || d->n_layers < 1 || d->n_layers > kMaxLayers) return false;
-    if (d->tail < 1 || d->tail > 64 || d->write_off < 0 || d->write_off + d->M > d->tail) return false;
+    if (d->tail < 1 || d->tail > 64 || d->write_off < 0) return false;
+    if (d->requests <= 1 && d->write_off + d->M > d->tail) return false;      // (several requests: checked below, per request)
     if (d->cache_rows < d->tail) return false;
     if (d->head_rows < 0 || (d->head_rows % 8) != 0 || d->head_rows > d->vocab) return false;
     if (d->tp_world > 1) {
@@ -2077,6 +2118,17 @@ bool fwd_shape_ok(const b200_forward_desc* d) {
         return false;
     }
     if (d->grid_ctas < 0) return false;
+    if (d->requests > 1) {
+        // several requests per pass: equal row groups, single-phase attention only (the cache must be short enough
+        // for it whatever the committed lengths are), no tensor-parallel shard
+        if (d->requests > kMaxReq || (d->M % d->requests) != 0 || d->tp_world > 1) return false;
+        if (d->write_off + d->M / d->requests > d->tail) return false;
+        const int fused_max = d->attn_split_blocks > 0 ? d->attn_split_blocks - 1 : (d->attn_split_blocks < 0 ? 0 : 32);
+        if ((d->cache_rows + kKeyBlock - 1) / kKeyBlock > fused_max) return false;
+        if (d->rows_out > d->M / d->requests) return false;
+    } else if (d->requests < 0) {
+        return false;
+    }
     return true;
 }
 
@@ -2232,6 +2284,10 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
     p.kv_half_stride = (size_t)d->n_kv_heads * d->cache_rows * d->head_dim;
     p.kv_layer_stride = 2 * p.kv_half_stride;
     p.cap = d->cache_rows; p.write_off = d->write_off; p.tail = d->tail;
+    p.nreq = d->requests > 1 ? d->requests : 1;
+    p.mr = d->M / p.nreq;
+    p.kv_req_stride = (size_t)d->n_layers * p.kv_layer_stride;
+    p.kv_req_rows = d->n_layers * 2 * d->n_kv_heads * d->cache_rows;
     char* ws = static_cast<char*>(d->workspace);
     p.sync = reinterpret_cast<int*>(ws + w.sync);
     p.counter = reinterpret_cast<int*>(ws + w.counter);
@@ -2242,7 +2298,7 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
     p.partial = reinterpret_cast<float*>(ws + w.partial);
     p.nkb = w.nkb; p.qrp = w.qrp;
     {
-        const int rc = make_kv_map(&p.kvmap, d->kv_cache, d->n_layers, d->n_kv_heads, d->cache_rows, d->head_dim);
+        const int rc = make_kv_map(&p.kvmap, d->kv_cache, d->n_layers * p.nreq, d->n_kv_heads, d->cache_rows, d->head_dim);
         if (rc != B200_OK) return rc;
     }
     p.head_rows = d->head_rows > 0 ? d->head_rows : d->vocab;

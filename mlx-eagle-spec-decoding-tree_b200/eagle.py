@@ -25,7 +25,7 @@ from typing import List, Optional
 import torch
 
 from . import _lib
-from .llama import KVCache, Model, ModelArgs, MAX_ROWS, shape_preset
+from .llama import KVCache, Model, ModelArgs, MAX_ROWS, MAX_REQUESTS, shape_preset
 
 K = 8                      # children per node (mlx_eagle.py:750)
 RETRIEVE_W = 9             # row width of the retrieve-index matrix (max depth 7 + 2)
@@ -37,7 +37,8 @@ class SpecDecoder:
     """Device-resident state and launch sequence of the speculative decoding loop."""
 
     def __init__(self, base_model: Model, draft_model: Model, depth: int, verify_num_tokens: int,
-                 cache_rows: int, max_out_tokens: int = 4096, max_steps: int = 4096, k: int = K):
+                 cache_rows: int, max_out_tokens: int = 4096, max_steps: int = 4096, k: int = K,
+                 base_cache: Optional[KVCache] = None, draft_cache: Optional[KVCache] = None, req: int = 0):
         if k != K:
             raise _lib.B200Error("k is fixed to 8, as in the reference (mlx_eagle.py:750)")
         if not (0 <= depth <= 6):
@@ -49,8 +50,10 @@ class SpecDecoder:
         self.depth, self.T = depth, T
         dev = base_model.device
         self.device = dev
-        self.base_cache = base_model.make_cache(cache_rows)
-        self.draft_cache = draft_model.make_cache(cache_rows)
+        # (a request of a BatchSpecDecoder gets its slabs of the shared caches and its row group ``req``)
+        self.base_cache = base_cache if base_cache is not None else base_model.make_cache(cache_rows)
+        self.draft_cache = draft_cache if draft_cache is not None else draft_model.make_cache(cache_rows)
+        self.req = req
         i32 = dict(dtype=torch.int32, device=dev)
         i64 = dict(dtype=torch.int64, device=dev)
         pool = K + K * K * max(depth, 1)
@@ -118,13 +121,22 @@ class SpecDecoder:
         return first
 
     # ------------------------------------------------------------------ one step, device only
-    def _draft_tree(self):
+    def _inputs(self, f, rows_per_request):
+        """This request's rows of a model's forward inputs (row group ``req``) and its committed-length word."""
+        o = self.req * rows_per_request
+        return f.tokens[o:], f.pos[o:], f.mask[o:], f.prefix[self.req:]
+
+    def _prep_catchup(self):
         L, p, ck = _lib.lib(), _lib.ptr, _lib.check
+        tok, pos, mask, prefix = self._inputs(self.draft.fwd, K)
+        ck(L.b200_prep_catchup(p(self.ctl), p(self.y), p(tok), p(pos), p(mask), p(prefix),
+                               p(self.sel_row), _lib.stream_ptr(self.device)), "b200_prep_catchup")
+
+    def _draft_tree(self):
         st = _lib.stream_ptr(self.device)
-        d, f = self.draft, self.draft.fwd
+        d = self.draft
         V = d.args.vocab_size
-        ck(L.b200_prep_catchup(p(self.ctl), p(self.y), p(f.tokens), p(f.pos), p(f.mask), p(f.prefix),
-                               p(self.sel_row), st), "b200_prep_catchup")
+        self._prep_catchup()
         logits = d.forward_device(K, self.draft_cache, 0, K, logits_rows=1, row_index=self.sel_row)
         self._expand(logits, 1, V, -1, st)
         for i in range(self.depth):
@@ -133,21 +145,21 @@ class SpecDecoder:
 
     def _expand(self, logits, R, V, level, st):
         L, p, ck = _lib.lib(), _lib.ptr, _lib.check
-        f = self.draft.fwd
+        tok, pos, mask, prefix = self._inputs(self.draft.fwd, K)
         ck(L.b200_logits_rowstats(p(logits), R, V, p(self.row_max), p(self.row_sum), st), "b200_logits_rowstats")
         ck(L.b200_logits_topk_candidates(p(logits), R, V, p(self.row_max), p(self.row_sum),
                                          0 if level < 0 else 1, p(self.cand), st), "b200_logits_topk_candidates")
         ck(L.b200_tree_expand(p(logits), V, level, p(self.cand), p(self.row_max), p(self.row_sum), p(self.ctl),
                               p(self.pool_scores), p(self.pool_tokens), p(self.pool_parents), p(self.cur_scores),
-                              p(self.topk_cs_index), p(f.tokens), p(f.pos), p(f.mask), p(f.prefix), st),
+                              p(self.topk_cs_index), p(tok), p(pos), p(mask), p(prefix), st),
            "b200_tree_expand")
 
     def _finalize(self):
         L, p, ck = _lib.lib(), _lib.ptr, _lib.check
         st = _lib.stream_ptr(self.device)
-        f = self.base.fwd
+        tok, pos, mask, prefix = self._inputs(self.base.fwd, self.T + 1)
         ck(L.b200_tree_finalize(self.depth, self.T, p(self.pool_scores), p(self.pool_tokens), p(self.pool_parents),
-                                p(self.ctl), p(self.y), p(f.tokens), p(f.pos), p(f.mask), p(f.prefix),
+                                p(self.ctl), p(self.y), p(tok), p(pos), p(mask), p(prefix),
                                 p(self.tree_position_ids), p(self.mask_index), p(self.draft_tokens),
                                 p(self.retrieve), p(self.tree_info), st), "b200_tree_finalize")
 
@@ -271,7 +283,10 @@ class SpecDecoder:
         total = time.perf_counter() - tic
         self.base.check_fused_error()
         self.draft.check_fused_error()
-        steps_run = i
+        return self._result(first, i, total, max_tokens, clip, int(prompt.numel()))
+
+    def _result(self, first: int, steps_run: int, total: float, max_tokens: int, clip: bool, prompt_len: int):
+        """The result dict of ``generate`` from the device-side logs after ``steps_run`` launched steps."""
         ctl = self.ctl.cpu().tolist()
         stop_n = ctl[CTL_STOP_N] if ctl[CTL_DONE] else None
         log = self.step_log[: 2 * steps_run].cpu().tolist()
@@ -295,7 +310,7 @@ class SpecDecoder:
         return dict(tokens=[first] + toks[:n], generated=n, steps=steps, steps_launched=steps_run,
                     accept_lengths=accept_lengths, mean_tokens_per_step=n / max(steps, 1), seconds=total,
                     tokens_per_second=produced / total if total > 0 else 0.0, produced=produced,
-                    finish_reason=reason, h2d_bytes=int(prompt.numel()) * 4, d2h_bytes=d2h)
+                    finish_reason=reason, h2d_bytes=prompt_len * 4, d2h_bytes=d2h)
 
     # ------------------------------------------------------------------ host views
     def read_ctl(self) -> List[int]:
@@ -309,6 +324,136 @@ class SpecDecoder:
 
 
 # ---------------------------------------------------------------------- reference-style functions
+class BatchSpecDecoder:
+    """Several requests decoded in lock step on one GPU: every draft pass and the target pass run ONCE for all of
+    them (request r owns row group r of the pass, its own slab of the KV caches and its own committed length), so
+    each weight read is shared; the tree kernels, the acceptance and the compaction run per request.  The reference
+    decodes one request (``mlx_eagle.py:503-606``); this is the same step for ``requests`` of them, and every request's
+    tokens are what ``SpecDecoder`` produces for it alone (up to the fp32 summation order of a wider pass).
+
+    ``requests * (verify_num_tokens + 1)`` and ``requests * 8`` rows must fit one pass (32 rows): 2 requests at 15
+    verify tokens, 4 at 7."""
+
+    def __init__(self, base_model: Model, draft_model: Model, depth: int, verify_num_tokens: int, cache_rows: int,
+                 requests: int, max_out_tokens: int = 4096, max_steps: int = 4096):
+        R, T = int(requests), verify_num_tokens
+        if not (1 <= R <= MAX_REQUESTS) or R * (T + 1) > MAX_ROWS or R * K > MAX_ROWS:
+            raise _lib.B200Error("requests x (verify_num_tokens + 1) rows must fit one 32-row pass")
+        if not (base_model.can_fuse() and draft_model.can_fuse()) or base_model.tp is not None:
+            raise _lib.B200Error("BatchSpecDecoder needs relayouted, unsharded models")
+        self.base, self.draft, self.depth, self.T, self.requests = base_model, draft_model, depth, T, R
+        self.device = base_model.device
+        self.base_cache = base_model.make_batch_cache(cache_rows, R)
+        self.draft_cache = draft_model.make_batch_cache(cache_rows, R)
+        self.ctl = torch.zeros(R, 16, dtype=torch.int32, device=self.device)
+        self.sel_rows = torch.zeros(R, dtype=torch.int32, device=self.device)
+        self.slots: List[SpecDecoder] = []
+        for r in range(R):
+            s = SpecDecoder(base_model, draft_model, depth, T, cache_rows, max_out_tokens, max_steps,
+                            base_cache=self.base_cache.slabs[r], draft_cache=self.draft_cache.slabs[r], req=r)
+            s.ctl = self.ctl[r]                       # one device array for all requests: one read-back per step
+            s.sel_row = self.sel_rows[r:r + 1]
+            self.slots.append(s)
+        self.max_steps = max_steps
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        one = self.slots[0].kernel_launches_per_step
+        fwd = (depth + 1) * draft_model.launches_per_forward + base_model.launches_per_forward
+        self.kernel_launches_per_step = fwd + R * (one - fwd)
+
+    def step(self):
+        """One speculative step of every request (no host synchronisation)."""
+        R, T, d, b = self.requests, self.T, self.draft, self.base
+        st = _lib.stream_ptr(self.device)
+        V = d.args.vocab_size
+        for s in self.slots:
+            s._prep_catchup()
+        logits = d.forward_device(K * R, self.draft_cache, 0, K, logits_rows=1, row_index=self.sel_rows, requests=R)
+        for r, s in enumerate(self.slots):
+            s._expand(logits[r:r + 1], 1, V, -1, st)
+        for i in range(self.depth):
+            logits = d.forward_device(K * R, self.draft_cache, K * i, K * (i + 1), requests=R)
+            for r, s in enumerate(self.slots):
+                s._expand(logits[r * K:(r + 1) * K], K, V, i, st)
+        for s in self.slots:
+            s._finalize()
+        bl = b.forward_device((T + 1) * R, self.base_cache, 0, T + 1, requests=R)
+        for r, s in enumerate(self.slots):
+            s.base_logits = bl[r * (T + 1):(r + 1) * (T + 1)]
+            s._accept()
+
+    def capture(self):
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.step()
+        self.graph = g
+        return g
+
+    def replay(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step()
+
+    def prefill(self, prompts, prefill_step_size: int = 512, eos_token_id: Optional[int] = None) -> List[int]:
+        """Feed every request's prompt to both models (one request at a time: prompts differ in length) and take
+        their first tokens."""
+        if len(prompts) != self.requests:
+            raise _lib.B200Error(f"need {self.requests} prompts")
+        return [s.prefill(pr, prefill_step_size, eos_token_id) for s, pr in zip(self.slots, prompts)]
+
+    def warmup(self, capture: bool = True):
+        g = torch.Generator().manual_seed(0)
+        v = min(self.base.args.vocab_size, self.draft.args.vocab_size)
+        self.prefill([torch.randint(0, v, (8,), generator=g, dtype=torch.int32) for _ in range(self.requests)])
+        self.step()
+        if capture:
+            self.capture()
+        torch.cuda.synchronize(self.device)
+
+    def generate(self, prompts, max_tokens: int = 128, N: int = 20, prefill_step_size: int = 512,
+                 eos_token_id: Optional[int] = None, clip: bool = False):
+        """Greedy tree-speculative generation for ``requests`` prompts at once.  Steps run until every request has
+        ``max_tokens`` tokens (or met ``eos_token_id``), at most ``N``; a request that finishes early keeps stepping
+        with the others and its surplus is dropped.  Returns one result dict per request (as ``SpecDecoder.generate``)
+        with the shared ``seconds``, plus ``"total_tokens_per_second"`` over all requests in each."""
+        s0 = self.slots[0]
+        longest = max(int(pr.numel()) for pr in prompts)
+        if N + 4 > self.max_steps or N * (self.depth + 2) + 8 * 4 > s0.out_tokens.numel():
+            raise _lib.B200Error("generate: N steps exceed the decoder's log capacity")
+        if longest + N * (self.depth + 2) + 8 * (self.depth + 2) + self.T + 64 > self.base_cache.rows:
+            raise _lib.B200Error("generate: prompt + N steps do not fit the KV cache")
+        firsts = self.prefill(prompts, prefill_step_size, eos_token_id)
+        torch.cuda.synchronize(self.device)
+        tic = time.perf_counter()
+        lead = 2
+        if not hasattr(self, "_pinned"):
+            self._pinned = [torch.zeros(self.requests, 16, dtype=torch.int32).pin_memory() for _ in range(4)]
+            self._events = [torch.cuda.Event() for _ in range(4)]
+        pinned, events = self._pinned, self._events
+        i = 0
+        while i < N:
+            self.replay()
+            pinned[i % 4].copy_(self.ctl, non_blocking=True)
+            events[i % 4].record()
+            i += 1
+            j = i - 1 - lead
+            if j >= 0:
+                events[j % 4].synchronize()
+                c = pinned[j % 4]
+                if all(int(c[r][CTL_NGEN]) >= max_tokens or int(c[r][CTL_DONE]) for r in range(self.requests)):
+                    break
+        torch.cuda.synchronize(self.device)
+        total = time.perf_counter() - tic
+        self.base.check_fused_error()
+        self.draft.check_fused_error()
+        out = [s._result(f, i, total, max_tokens, clip, int(pr.numel())) for s, f, pr in zip(self.slots, firsts, prompts)]
+        agg = sum(o["generated"] for o in out) / total if total > 0 else 0.0
+        for o in out:
+            o["total_tokens_per_second"] = agg
+        return out
+
+
 def post_process_draft_tree(tree_position_ids: torch.Tensor, total_tokens: int, mask_index: torch.Tensor) -> torch.Tensor:
     """Root-to-leaf index paths ``(leaf_num, max_depth)``, -1 padded (``mlx_eagle.py:254-295``).
 

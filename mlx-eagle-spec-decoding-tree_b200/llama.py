@@ -31,6 +31,7 @@ from .quantize import quantize
 
 MAX_ROWS = 32          # tokens per forward pass (tree size + 1 <= 32)
 MAX_TAIL = 64          # uncommitted cache rows a query can address through its bit mask
+MAX_REQUESTS = 4       # requests that can share one forward pass
 PREFILL_ROWS = 128     # prompt tokens per pass of the large-M (tcgen05) matmul path
 
 
@@ -226,7 +227,7 @@ class FwdInputs:
         self.tokens = torch.zeros(MAX_ROWS, dtype=torch.int32, device=device)
         self.pos = torch.zeros(MAX_ROWS, dtype=torch.int32, device=device)
         self.mask = torch.zeros(MAX_ROWS, dtype=torch.int64, device=device)   # uint64 bit masks
-        self.prefix = torch.zeros(1, dtype=torch.int32, device=device)
+        self.prefix = torch.zeros(MAX_REQUESTS, dtype=torch.int32, device=device)   # committed length per request
 
 
 class KVCache:
@@ -236,10 +237,11 @@ class KVCache:
     rewinds it directly (``mlx_eagle.py:376,405-406,593-594``), and so may callers here.
     """
 
-    def __init__(self, args: ModelArgs, rows: int, device):
+    def __init__(self, args: ModelArgs, rows: int, device, data: Optional[torch.Tensor] = None):
         self.rows = int(rows)
-        self.data = torch.zeros(args.num_hidden_layers, 2, args.num_key_value_heads, self.rows, args.head_dim,
-                                dtype=torch.float16, device=device)
+        self.data = data if data is not None else torch.zeros(
+            args.num_hidden_layers, 2, args.num_key_value_heads, self.rows, args.head_dim,
+            dtype=torch.float16, device=device)
         self.offset = 0
 
     def layer(self, i):
@@ -248,6 +250,18 @@ class KVCache:
     @property
     def state(self):
         return self.data[:, 0, :, : self.offset], self.data[:, 1, :, : self.offset]
+
+
+class BatchKVCache:
+    """The caches of several requests that share forward passes, in one allocation
+    ``[requests][layers][2][Hkv][rows][hd]`` (the layout ``b200_forward`` takes with ``requests > 1``).
+    ``slabs[r]`` is request r's cache as an ordinary :class:`KVCache` view (prompt ingestion, compaction)."""
+
+    def __init__(self, args: ModelArgs, rows: int, device, requests: int):
+        self.rows, self.requests = int(rows), int(requests)
+        self.data = torch.zeros(self.requests, args.num_hidden_layers, 2, args.num_key_value_heads, self.rows,
+                                args.head_dim, dtype=torch.float16, device=device)
+        self.slabs = [KVCache(args, rows, device, data=self.data[r]) for r in range(self.requests)]
 
 
 class Model:
@@ -439,6 +453,9 @@ class Model:
     def make_cache(self, rows: int) -> KVCache:
         return KVCache(self.args, rows, self.device)
 
+    def make_batch_cache(self, rows: int, requests: int) -> BatchKVCache:
+        return BatchKVCache(self.args, rows, self.device, requests)
+
     def relayout(self):
         """Re-lay-out every linear layer for the streaming kernel (one-off, at load time).  The
         embedding keeps its row-major form, which the token gather needs."""
@@ -486,7 +503,7 @@ class Model:
                 and self.nq % 128 == 0 and a.head_dim in (64, 128) and a.vocab_size % 8 == 0
                 and self.vocab_local % 8 == 0)
 
-    def _fused_desc(self, M, cache, write_off, tail, fwd, rows, row_index):
+    def _fused_desc(self, M, cache, write_off, tail, fwd, rows, row_index, requests=1):
         a = self.args
         p = lambda t: None if t is None else t.data_ptr()
         if self._layer_table is None:
@@ -511,6 +528,7 @@ class Model:
         d.h, d.hw, d.qkv, d.attn, d.act, d.logits = p(self.h), p(self.hw), p(self.qkv), p(self.xt_attn), \
             p(self.xt_act), p(self.logits)
         d.kv_cache = p(cache.data)
+        d.requests = requests
         if self.tp is not None:
             d.head_rows = self.vocab_local
         d.grid_ctas = self.grid_ctas
@@ -589,15 +607,26 @@ class Model:
         return self._attn_ws
 
     def forward_device(self, M: int, cache: KVCache, write_off: int, tail: int, fwd: Optional[FwdInputs] = None,
-                       logits_rows: Optional[int] = None, row_index: Optional[torch.Tensor] = None):
+                       logits_rows: Optional[int] = None, row_index: Optional[torch.Tensor] = None, requests: int = 1):
         """One forward pass of ``M`` tokens whose ids / positions / masks / committed length sit in
         ``fwd`` (device memory).  New K/V rows go to cache row ``prefix + write_off + m``; query m sees
         rows ``< prefix`` and tail row j iff bit j of ``fwd.mask[m]``.  Returns fp16 logits
         ``(logits_rows or M, V)`` (a view of an internal buffer); with ``row_index`` (device int) only
         rows ``row_index .. row_index+logits_rows-1`` of the hidden state reach the head."""
-        if not (1 <= M <= MAX_ROWS and 1 <= tail <= MAX_TAIL and write_off + M <= tail):
+        if not (1 <= M <= MAX_ROWS and 1 <= tail <= MAX_TAIL and write_off + M // requests <= tail):
             raise _lib.B200Error("forward_device: need 1 <= M <= 32, tail <= 64, write_off + M <= tail")
         fwd = fwd or self.fwd
+        if requests > 1:
+            # several requests share the pass (and every weight read): M = requests x rows of each; ``cache`` is a
+            # BatchKVCache, fwd.prefix / row_index hold one entry per request, logits come back as
+            # [requests * logits_rows][V]
+            if not (self.can_fuse() and isinstance(cache, BatchKVCache) and cache.requests == requests
+                    and M % requests == 0 and self.tp is None):
+                raise _lib.B200Error("forward_device: several requests need relayouted weights and a BatchKVCache")
+            rows = M // requests if logits_rows is None else logits_rows
+            desc = self._fused_desc(M, cache, write_off, tail, fwd, rows, row_index, requests)
+            _lib.check(_lib.lib().b200_forward(ctypes.byref(desc), _lib.stream_ptr(self.device)), "b200_forward")
+            return self.logits[: requests * rows]
         if self.can_fuse():
             rows = M if logits_rows is None else logits_rows
             desc = self._fused_desc(M, cache, write_off, tail, fwd, rows, row_index)

@@ -41,7 +41,7 @@ def lockstep(be, base, draft, depth, T, steps, prompt_len, seed, cache_rows=512,
         assert f.tokens[:K].cpu().tolist() == (y_host + [0] * K)[:K]
         assert f.pos[:K].cpu().tolist() == [draft_len + m for m in range(K)]
         assert _u64(f.mask[:K]) == [(2 << m) - 1 for m in range(K)]
-        assert int(f.prefix) == draft_len and int(dec.sel_row) == a_prev
+        assert int(f.prefix[0]) == draft_len and int(dec.sel_row) == a_prev
         logits = draft.forward_device(K, dec.draft_cache, 0, K, logits_rows=1, row_index=dec.sel_row).cpu().numpy()
         dec._expand(draft.logits[:1], 1, V, -1, st)
         # ---- root expansion (mlx_eagle.py:410-412)
@@ -49,7 +49,7 @@ def lockstep(be, base, draft, depth, T, steps, prompt_len, seed, cache_rows=512,
         off = draft_len + a_prev + 1
         assert dec.pool_tokens[:K].cpu().tolist() == ti.reshape(-1).tolist()
         assert np.array_equal(dec.pool_scores[:K].cpu().numpy(), tp.reshape(-1))
-        assert int(dec.ctl[5]) == off and int(f.prefix) == off
+        assert int(dec.ctl[5]) == off and int(f.prefix[0]) == off
         assert f.tokens[:K].cpu().tolist() == ti.reshape(-1).tolist()
         assert f.pos[:K].cpu().tolist() == [off] * K
         pool = tr.DraftPool(ti, tp, K)
@@ -82,7 +82,7 @@ def lockstep(be, base, draft, depth, T, steps, prompt_len, seed, cache_rows=512,
         assert dec.mask_index[:T].cpu().tolist() == mi.tolist()
         assert dec.draft_tokens[:T + 1].cpu().tolist() == dt[0].tolist() == bf.tokens[:T + 1].cpu().tolist()
         assert _u64(bf.mask[:T + 1]) == _bits(tm)
-        assert bf.pos[:T + 1].cpu().tolist() == (tpi + base_len).tolist() and int(bf.prefix) == base_len
+        assert bf.pos[:T + 1].cpu().tolist() == (tpi + base_len).tolist() and int(bf.prefix[0]) == base_len
         leaf_num, max_depth = dec.tree_info.cpu().tolist()
         assert (leaf_num, max_depth) == retrieve.shape
         got_r = dec.retrieve.cpu().numpy().reshape(-1, 9)[:leaf_num, :max_depth]

@@ -63,4 +63,4 @@ def test_forward_descriptor_validation_without_gpu(be):
     assert lib.b200_forward_workspace_bytes(ctypes.byref(d)) == 0
     d.hidden, d.head_dim = 3584, 96
     assert lib.b200_forward(ctypes.byref(d), None) == -1
-    assert ctypes.sizeof(be._lib.ForwardDesc) == 64 + 20 * 8 + 8 + 16 + 16 + 64 + 8  # layout of b200_forward_desc in the header
+    assert ctypes.sizeof(be._lib.ForwardDesc) == 64 + 20 * 8 + 8 + 16 + 16 + 64 + 8 + 8  # layout of b200_forward_desc in the header
