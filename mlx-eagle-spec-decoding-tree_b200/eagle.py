@@ -356,30 +356,41 @@ class BatchSpecDecoder:
             self.slots.append(s)
         self.max_steps = max_steps
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        # the per-request kernels of a step (tree levels, selection, acceptance, compaction) touch only their own
+        # request's state: they go to one side stream per request, so that the captured graph has parallel branches
+        self.side = [torch.cuda.Stream(device=self.device) for _ in range(R)]
         one = self.slots[0].kernel_launches_per_step
         fwd = (depth + 1) * draft_model.launches_per_forward + base_model.launches_per_forward
         self.kernel_launches_per_step = fwd + R * (one - fwd)
 
+    def _per_request(self, fn):
+        """Run ``fn(r, slot)`` for every request, each on its own side stream, between two joins with the main
+        stream (the shared passes before and after see all of them done)."""
+        main = torch.cuda.current_stream(self.device)
+        for r, s in enumerate(self.slots):
+            self.side[r].wait_stream(main)
+            with torch.cuda.stream(self.side[r]):
+                fn(r, s)
+        for r in range(self.requests):
+            main.wait_stream(self.side[r])
+
     def step(self):
         """One speculative step of every request (no host synchronisation)."""
         R, T, d, b = self.requests, self.T, self.draft, self.base
-        st = _lib.stream_ptr(self.device)
         V = d.args.vocab_size
-        for s in self.slots:
-            s._prep_catchup()
+        self._per_request(lambda r, s: s._prep_catchup())
         logits = d.forward_device(K * R, self.draft_cache, 0, K, logits_rows=1, row_index=self.sel_rows, requests=R)
-        for r, s in enumerate(self.slots):
-            s._expand(logits[r:r + 1], 1, V, -1, st)
+        self._per_request(lambda r, s: s._expand(logits[r:r + 1], 1, V, -1, _lib.stream_ptr(self.device)))
         for i in range(self.depth):
             logits = d.forward_device(K * R, self.draft_cache, K * i, K * (i + 1), requests=R)
-            for r, s in enumerate(self.slots):
-                s._expand(logits[r * K:(r + 1) * K], K, V, i, st)
-        for s in self.slots:
-            s._finalize()
+            self._per_request(lambda r, s: s._expand(logits[r * K:(r + 1) * K], K, V, i, _lib.stream_ptr(self.device)))
+        self._per_request(lambda r, s: s._finalize())
         bl = b.forward_device((T + 1) * R, self.base_cache, 0, T + 1, requests=R)
-        for r, s in enumerate(self.slots):
+
+        def accept(r, s):
             s.base_logits = bl[r * (T + 1):(r + 1) * (T + 1)]
             s._accept()
+        self._per_request(accept)
 
     def capture(self):
         torch.cuda.synchronize(self.device)
