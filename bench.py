@@ -16,7 +16,9 @@ the metric's second half (``qmm_sweep``: 8192 x 2048 at 1..32 rows, GB/s against
 parity check of the very models that are timed (``config.parity_checked``) and a CPU baseline (the CPU
 restatement of the reference's path on a bounded sample on this host's cores).  At N > 1 the ranks afterwards
 run the tensor-parallel workload ``tp70b`` for a few steps and attach its numbers under
-``config.tensor_parallel``.
+``config.tensor_parallel``.  At N = 1 two more attachments: ``config.batched_requests`` (the same step for as many
+requests as fit one 32-row pass, all passes shared) and ``config.accept_length_sensitivity`` (the step time at accept
+length 0 and above: random-init pairs accept nothing, so the headline counts one token per step).
 
 Other workloads: ``c2`` draft-only tree build (0.5B-shape draft, prompt 128, depth 3, 7 nodes), ``c4``
 Llama-3-8B-shape target + Llama-3.2-1B-shape draft (prompt 1024, depth 4, 31 verify tokens, also reports the
@@ -613,6 +615,43 @@ def timed_blocks(torch, dist, world, dec, K, snapshot, min_seconds=MIN_TIMED_SEC
     return secs, produced
 
 
+def accept_length_numbers(torch, be, draft, dname, depth, verify, prompt_len, dev):
+    """Does the step time depend on how many tokens are accepted?  Random-init pairs accept nothing, so the headline
+    runs at one token per step.  Here the draft-shape model is the target too, once with a different random model as
+    its draft (accept length 0) and once with itself (the draft agrees with the target wherever the 8-row and the
+    wider pass round alike): same shapes, same launch sequence, different accept lengths."""
+    other = be.Model.random_init(be.shape_preset(dname), seed=777, device=dev).relayout()
+    out = []
+    for name, d in (("a different random model as draft", other), ("the target as its own draft", draft)):
+        dec = be.SpecDecoder(draft, d, depth, verify, cache_rows=2048, max_out_tokens=2048, max_steps=256)
+        dec.warmup()
+        dec.prefill(torch.randint(0, draft.args.vocab_size, (prompt_len,), generator=torch.Generator().manual_seed(5),
+                                  dtype=torch.int32))
+        for _ in range(5):
+            dec.replay()
+        torch.cuda.synchronize()
+        ctl0, y0 = dec.ctl.clone(), dec.y.clone()
+        ts = []
+        for _ in range(5):
+            dec.ctl.copy_(ctl0)
+            dec.y.copy_(y0)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(50):
+                dec.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / 50)
+        out.append({"draft": name, "ms_per_step": statistics.median(ts),
+                    "tokens_per_step": (int(dec.ctl[3]) - int(ctl0[3])) / 50})
+        del dec
+    del other
+    torch.cuda.empty_cache()
+    return {"models": f"{dname} shape as target and draft, depth {depth}, verify {verify}", "cases": out,
+            "reading": "the step is a fixed launch sequence: its time does not depend on the accept length, tokens/s does"}
+
+
 def batched_requests_numbers(torch, be, base, draft, depth, verify, prompt_len, K, warmup, dev, min_seconds):
     """The same step for several requests at once on this GPU (``BatchSpecDecoder``: every pass is shared, so each
     weight read serves all requests): as many requests as fit a 32-row pass, K-step blocks replayed from one decode
@@ -872,6 +911,11 @@ def main():
                     torch, be, base, draft, DEPTH, VERIFY, PROMPT, K, warmup, dev, args.min_seconds)
             except Exception as e:                         # the attachment must not take the headline down with it
                 line["config"]["batched_requests"] = {"error": f"{type(e).__name__}: {e}"}
+            try:
+                line["config"]["accept_length_sensitivity"] = accept_length_numbers(torch, be, draft, dname, DEPTH, VERIFY,
+                                                                                    PROMPT, dev)
+            except Exception as e:
+                line["config"]["accept_length_sensitivity"] = {"error": f"{type(e).__name__}: {e}"}
     # ---- at N > 1: the tensor-parallel target on the same ranks (collective), attached to the line
     if world > 1 and extras and args.workload == "c3":
         tp = None

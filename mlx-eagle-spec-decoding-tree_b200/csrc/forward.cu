@@ -164,17 +164,20 @@ struct QDesc {
     PhasePlan pl;
     int xrows;                  // token rows of the pass
     int row_lo, row_cnt;        // token rows [row_lo, row_lo+row_cnt) are stored, as output rows 0.. (vocabulary projection)
-    int mr;                     // rows per request; 0 = one request.  Else request q = tok / mr stores its rows
-    const int* row_off;         //   [q*mr + row_off[q], +row_cnt) as output rows q*row_cnt .. (shared memory)
+    int orow_sel;               // several requests per pass: which table of out_row_tab() maps token rows to output rows
+                                //   (1: the vocabulary projection keeps rows_out rows per request; 0: all rows kept)
     bool y_tiled;               // output goes to the chunk-major padded layout (it is a later phase's matmul input)
 };
 
-// Output row of token row `tok` in a row-major result that keeps only selected rows, or -1.
-__device__ __forceinline__ int out_row(const QDesc& d, int tok) {
-    if (d.mr == 0) return (tok >= d.row_lo && tok < d.row_lo + d.row_cnt) ? tok - d.row_lo : -1;
-    const int q = tok / d.mr;
-    const int rel = tok - q * d.mr - d.row_off[q];
-    return (rel >= 0 && rel < d.row_cnt) ? q * d.row_cnt + rel : -1;
+// Small per-launch tables in static shared memory, reached through functions so that no pointer to them has to
+// stay in a register across the matmul loops (the kernel sits at its register limit).
+__device__ __forceinline__ int* req_prefix_tab() {       // committed length of every request of the pass
+    __shared__ int s_prefix[kMaxReq];
+    return s_prefix;
+}
+__device__ __forceinline__ int* out_row_tab() {          // [2][32] output row of a token row, or -1 = not stored:
+    __shared__ int s_orow[2 * 32];                       //   [0] every row kept, [1] the vocabulary projection's selection
+    return s_orow;
 }
 
 struct Ctx {
@@ -186,7 +189,6 @@ struct Ctx {
     unsigned char* scratch;
     const LayerPtrs* ltab;        // the layer pointer table, copied to shared memory at kernel start
     volatile int* abort_flag;
-    const int* req_prefix;        // committed length of every request of the pass (shared memory)
     volatile uint32_t* s_epoch;   // grid barriers this CTA has seen complete (written by thread 0)
     int* is_last;
     float* s_rstd;
@@ -729,7 +731,14 @@ __device__ __forceinline__ void qmm_produce(const FwdParams& p, Ctx& c, const QD
     }
 }
 
-template <int MT, bool DUAL, bool TP, bool FAST>
+// Output row of token row `tok` in a row-major result, or -1 if the row is not stored.
+template <bool BATCH>
+__device__ __forceinline__ int out_row(const QDesc& d, int tok) {
+    if (BATCH) return out_row_tab()[d.orow_sel * 32 + tok];
+    return (tok >= d.row_lo && tok < d.row_lo + d.row_cnt) ? tok - d.row_lo : -1;
+}
+
+template <int MT, bool DUAL, bool TP, bool FAST, bool BATCH>
 __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QDesc& d, const int EPI) {
     using G = Geo<MT>;
     constexpr int S = DUAL ? 2 : 1;
@@ -984,7 +993,7 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
                         if (d.y_tiled) {
                             *reinterpret_cast<uint4*>(d.y + xt_index(tok, n0, MP)) = *reinterpret_cast<const uint4*>(out);
                         } else {
-                            const int orow = out_row(d, tok);
+                            const int orow = out_row<BATCH>(d, tok);
                             if (orow >= 0) *reinterpret_cast<uint4*>(d.y + (size_t)orow * d.N + n0) = *reinterpret_cast<const uint4*>(out);
                         }
                     }
@@ -1065,7 +1074,7 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
                         if (d.y_tiled) {
                             d.y[xt_index(tok, nn, MP)] = o;
                         } else {
-                            const int orow = out_row(d, tok);
+                            const int orow = out_row<BATCH>(d, tok);
                             if (orow >= 0) d.y[(size_t)orow * d.N + nn] = o;
                         }
                     }
@@ -1422,19 +1431,21 @@ struct AGeo {
     static_assert(16 * OP * 4 + 16 * 8 <= SLOT, "a warp's partial state must fit its slot");
 };
 
-template <int MT, int HD>
+// BATCH: the pass holds several requests (compiled separately, so that the one-request kernel is unchanged by it).
+template <int MT, int HD, bool BATCH>
 __device__ __forceinline__ void attn_bp_produce(const FwdParams& p, Ctx& c, const ADesc& a, int layer) {
     using A = AGeo<MT, HD>;
     const int lane = c.lane;
     const int Gq = p.Hq / p.Hkv;
-    const int ntiles = (p.mr * Gq + 15) / 16;
-    const int nitems = p.nreq * p.Hkv * ntiles;           // item = (request, kv head, query tile)
+    const int nreq = BATCH ? p.nreq : 1, mr = BATCH ? p.mr : p.M;
+    const int ntiles = (mr * Gq + 15) / 16;
+    const int nitems = nreq * p.Hkv * ntiles;             // item = (request, kv head, query tile)
     if ((int)blockIdx.x >= nitems) return;
     if (*c.abort_flag || !drain_stages<MT>(p, c)) return;
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-        const int req = item / (p.Hkv * ntiles);
-        const int hk = (item / ntiles) % p.Hkv;
-        const int nact = p.nreq == 1 ? a.nact : min((c.req_prefix[req] + p.tail + kKeyBlock - 1) / kKeyBlock, p.nkb);
+        const int req = BATCH ? item / (p.Hkv * ntiles) : 0;
+        const int hk = BATCH ? (item / ntiles) % p.Hkv : item / ntiles;
+        const int nact = BATCH ? min((req_prefix_tab()[req] + p.tail + kKeyBlock - 1) / kKeyBlock, p.nkb) : a.nact;
         const int krow0 = req * p.kv_req_rows + ((layer * 2 + 0) * p.Hkv + hk) * p.cap;   // row of the cache viewed as [rows][HD]
         const int vrow0 = req * p.kv_req_rows + ((layer * 2 + 1) * p.Hkv + hk) * p.cap;
         for (int kb = 0; kb < nact; kb++, c.apos++) {
@@ -1459,7 +1470,7 @@ __device__ __forceinline__ void attn_bp_produce(const FwdParams& p, Ctx& c, cons
     }
 }
 
-template <int MT, int HD>
+template <int MT, int HD, bool BATCH>
 __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, const ADesc& a) {
     using A = AGeo<MT, HD>;
     constexpr int NS = A::NS, NBX = A::NBX, OP = A::OP;
@@ -1469,21 +1480,23 @@ __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, cons
     const int lane = c.lane, warp = c.warp;
     const int g = lane >> 2, t = lane & 3;
     const int Gq = p.Hq / p.Hkv;
-    const int QR = p.mr * Gq;                      // query rows (token, head of the group) of one request and kv head
+    const int nreq = BATCH ? p.nreq : 1, mr = BATCH ? p.mr : p.M;
+    const int QR = mr * Gq;                        // query rows (token, head of the group) of one request and kv head
     const int ntiles = (QR + 15) / 16;
-    const int nitems = p.nreq * p.Hkv * ntiles;
+    const int nitems = nreq * p.Hkv * ntiles;
     __half* sq = reinterpret_cast<__half*>(c.scratch);
     __half* nkv = sq + 16 * KS;                    // [2][M][HD]: rotated k rows, then v rows, of this pass
     static_assert(16 * KS * 2 + 2 * 32 * HD * 2 <= kScratch, "query tile and new K/V rows must fit the scratch area");
     unsigned char* myslot = c.ring + (warp < NS ? warp : 0) * A::SLOT;
 
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-        const int req = item / (p.Hkv * ntiles);
-        const int hk = (item / ntiles) % p.Hkv, rt = item % ntiles;
-        const int prefix = p.nreq == 1 ? a.prefix : c.req_prefix[req];
-        const int nact = p.nreq == 1 ? a.nact : min((prefix + p.tail + kKeyBlock - 1) / kKeyBlock, p.nkb);
+        const int req = BATCH ? item / (p.Hkv * ntiles) : 0;
+        const int hk = BATCH ? (item / ntiles) % p.Hkv : item / ntiles;
+        const int rt = item - (req * p.Hkv + hk) * ntiles;
+        const int prefix = BATCH ? req_prefix_tab()[req] : a.prefix;
+        const int nact = BATCH ? min((prefix + p.tail + kKeyBlock - 1) / kKeyBlock, p.nkb) : a.nact;
         const int new0 = prefix + p.write_off;
-        const int mbase = req * p.mr;                      // first token row of the request
+        const int mbase = req * mr;                        // first token row of the request
         __half* const kc = a.kc + (size_t)req * p.kv_req_stride;
         __half* const vc = a.vc + (size_t)req * p.kv_req_stride;
         const uint32_t n0 = c.apos;                        // first block of this item in the phase's block sequence
@@ -1527,12 +1540,12 @@ __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, cons
         //      tile's item of each kv head also appends them to the cache
         {
             const bool writer = (rt == 0);
-            for (int idx = threadIdx.x; idx < p.mr * VPR; idx += kNCons) {
+            for (int idx = threadIdx.x; idx < mr * VPR; idx += kNCons) {
                 const int m = idx / VPR, cv = idx - m * VPR;          // m: row inside the request
                 const int key = new0 + m;
                 const __half* src = p.qkv + (size_t)(mbase + m) * p.NQKV;
                 const uint4 vv = __ldcg(reinterpret_cast<const uint4*>(src + (size_t)(p.Hq + p.Hkv) * HD + (size_t)hk * HD + cv * 8));
-                *reinterpret_cast<uint4*>(nkv + (p.mr + m) * HD + cv * 8) = vv;
+                *reinterpret_cast<uint4*>(nkv + (mr + m) * HD + cv * 8) = vv;
                 if (writer && key < p.cap) *reinterpret_cast<uint4*>(vc + ((size_t)hk * p.cap + key) * HD + cv * 8) = vv;
                 if (cv < VPR / 2) {
                     const __half* ksrc = src + (size_t)p.Hq * HD + (size_t)hk * HD;
@@ -1598,14 +1611,14 @@ __device__ __forceinline__ void attn_bp_consume(const FwdParams& p, Ctx& c, cons
                 if (!ok) continue;
                 const uint32_t sk = smem_u32(myslot), sv = sk + NBX * kBox;
                 // this pass's own rows inside the block come from the rows prepared above
-                if (key0 + kKeyBlock > new0 && key0 < new0 + p.mr) {
-                    for (int idx = lane; idx < p.mr * VPR; idx += 32) {
+                if (key0 + kKeyBlock > new0 && key0 < new0 + mr) {
+                    for (int idx = lane; idx < mr * VPR; idx += 32) {
                         const int m = idx / VPR, cv = idx - m * VPR;
                         const int r = new0 + m - key0;
                         if (r < 0 || r >= kKeyBlock) continue;
                         *reinterpret_cast<uint4*>(myslot + swz(r, cv)) = *reinterpret_cast<const uint4*>(nkv + m * HD + cv * 8);
                         *reinterpret_cast<uint4*>(myslot + NBX * kBox + swz(r, cv)) =
-                            *reinterpret_cast<const uint4*>(nkv + (p.mr + m) * HD + cv * 8);
+                            *reinterpret_cast<const uint4*>(nkv + (mr + m) * HD + cv * 8);
                     }
                     __syncwarp();
                 }
@@ -1816,14 +1829,13 @@ __device__ __forceinline__ void attn_merge(const FwdParams& p, Ctx& c, const ADe
 }
 
 // ================================================================================ the kernel
-template <int MT, int HD, bool TP>
+template <int MT, int HD, bool TP, bool BATCH>
 __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_constant__ FwdParams p) {
     using G = Geo<MT>;
     extern __shared__ __align__(1024) unsigned char smem[];      // swizzled TMA boxes want 1024-byte aligned stages
     __shared__ int s_abort, s_is_last;
     __shared__ uint32_t s_epoch;
     __shared__ float s_rstd[32];
-    __shared__ int s_prefix[kMaxReq], s_rowoff[kMaxReq];
 
     Ctx c;
     c.ring = smem;
@@ -1848,7 +1860,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
     c.s_epoch = &s_epoch;
     c.is_last = &s_is_last;
     c.s_rstd = s_rstd;
-    c.req_prefix = s_prefix;
 
     c.pos = 0;
     c.epoch = 0;
@@ -1858,9 +1869,14 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
     c.lane = threadIdx.x & 31;
     c.warp = threadIdx.x >> 5;
 
-    if ((int)threadIdx.x < p.nreq) {
-        s_prefix[threadIdx.x] = p.prefix[threadIdx.x];
-        s_rowoff[threadIdx.x] = p.row_index ? p.row_index[threadIdx.x] : 0;
+    if (BATCH && (int)threadIdx.x < p.nreq) req_prefix_tab()[threadIdx.x] = p.prefix[threadIdx.x];
+    if (BATCH && threadIdx.x < 32) {
+        // the head keeps rows [row_index[q], +rows_out) of request q (of mr rows) as output rows q * rows_out ..
+        const int mr = BATCH ? p.mr : p.M;
+        const int tok = threadIdx.x, q = BATCH ? tok / mr : 0;
+        const int rel = tok - q * mr - ((p.row_index && tok < p.M) ? p.row_index[q] : 0);
+        out_row_tab()[tok] = tok < p.M ? tok : -1;
+        out_row_tab()[32 + tok] = (tok < p.M && rel >= 0 && rel < p.rows_out) ? q * p.rows_out + rel : -1;
     }
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -1910,8 +1926,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             ad.kc = p.kv + (size_t)l * p.kv_layer_stride;
             ad.vc = ad.kc + p.kv_half_stride;
             if (attn_fused) {
-                if (producer) attn_bp_produce<MT, HD>(p, c, ad, l);
-                else attn_bp_consume<MT, HD>(p, c, ad);
+                if (producer) attn_bp_produce<MT, HD, BATCH>(p, c, ad, l);
+                else attn_bp_consume<MT, HD, BATCH>(p, c, ad);
             } else {
                 if (producer) attn_produce<MT, HD>(p, c, ad);
                 else attn_consume<MT, HD>(p, c, ad);
@@ -1924,7 +1940,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             QDesc d;
             d.xrows = p.M;
             d.row_lo = 0; d.row_cnt = p.M;
-            d.mr = 0; d.row_off = s_rowoff;
+            d.orow_sel = 0;
             d.y_tiled = false;
             d.w1 = nullptr; d.bias = nullptr; d.wn = nullptr;
             int epi = TP ? EPI_TP : EPI_RESID;
@@ -1943,7 +1959,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
                 d.N = p.H; d.K = p.I; d.pl = p.plan[PLAN_E];
             } else {                                   // K_HEAD, on the selected rows
                 d.row_lo = row_off; d.row_cnt = p.rows_out;       // all rows are multiplied, the selected ones stored
-                if (p.nreq > 1) d.mr = p.mr;                      // ... rows_out per request
+                d.orow_sel = 1;
                 d.x = p.hw; d.w0 = p.head_w; d.y = p.logits;
                 d.N = p.head_rows; d.K = p.H; d.pl = p.plan[PLAN_HEAD]; epi = EPI_HEAD;
             }
@@ -1951,11 +1967,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) forward_kernel(const __grid_co
             if (producer) {
                 qmm_produce<MT>(p, c, d, c.lbar, kind == K_D, epi != EPI_RESID && epi != EPI_TP);
             } else if (p.fast_scales) {          // uniform: chosen once per launch by the host
-                if (kind == K_D) qmm_consume<MT, true, false, true>(p, c, d, EPI_SILU);
-                else qmm_consume<MT, false, TP, true>(p, c, d, epi);
+                if (kind == K_D) qmm_consume<MT, true, false, true, BATCH>(p, c, d, EPI_SILU);
+                else qmm_consume<MT, false, TP, true, BATCH>(p, c, d, epi);
             } else {
-                if (kind == K_D) qmm_consume<MT, true, false, false>(p, c, d, EPI_SILU);
-                else qmm_consume<MT, false, TP, false>(p, c, d, epi);
+                if (kind == K_D) qmm_consume<MT, true, false, false, BATCH>(p, c, d, EPI_SILU);
+                else qmm_consume<MT, false, TP, false, BATCH>(p, c, d, epi);
             }
         }
         const bool exchange = TP && (kind == K_C || kind == K_E);
@@ -2200,9 +2216,9 @@ int make_kv_map(CUtensorMap* map, void* cache, int layers, int hkv, int cap, int
     return B200_OK;
 }
 
-template <int MT, int HD, bool TP>
+template <int MT, int HD, bool TP, bool BATCH>
 int launch_forward(const FwdParams& p, int grid, cudaStream_t stream) {
-    auto kern = forward_kernel<MT, HD, TP>;
+    auto kern = forward_kernel<MT, HD, TP, BATCH>;
     bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<MT>::SMEM) != cudaSuccess)
@@ -2226,8 +2242,10 @@ int launch_forward(const FwdParams& p, int grid, cudaStream_t stream) {
 template <int MT>
 int launch_forward_hd(const FwdParams& p, int grid, cudaStream_t stream) {
     if (p.tp_world > 1)         // a shard: the variant with the exchange phases
-        return p.HD == 128 ? launch_forward<MT, 128, true>(p, grid, stream) : launch_forward<MT, 64, true>(p, grid, stream);
-    return p.HD == 128 ? launch_forward<MT, 128, false>(p, grid, stream) : launch_forward<MT, 64, false>(p, grid, stream);
+        return p.HD == 128 ? launch_forward<MT, 128, true, false>(p, grid, stream) : launch_forward<MT, 64, true, false>(p, grid, stream);
+    if (p.nreq > 1)             // several requests in the pass
+        return p.HD == 128 ? launch_forward<MT, 128, false, true>(p, grid, stream) : launch_forward<MT, 64, false, true>(p, grid, stream);
+    return p.HD == 128 ? launch_forward<MT, 128, false, false>(p, grid, stream) : launch_forward<MT, 64, false, false>(p, grid, stream);
 }
 
 }  // namespace

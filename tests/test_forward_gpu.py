@@ -208,3 +208,28 @@ def test_prompt_through_the_large_m_path_matches_the_oracle_and_the_32_row_passe
     _close(logits, small, 2.0 ** -6, 2e-2)
     last = m(torch.from_numpy(prompt)[None], cache=m.make_cache(384), logits_last_only=True)[0].cpu().numpy()
     _close(last[0], want[-1], 2.0 ** -6, 2e-2)
+
+
+def test_plan_hint_changes_the_work_split_not_the_result(be, pair):
+    """``b200_forward_plan_hint`` (a measurement aid) moves work between K-parts, stages and split-K; the logits stay
+    within the summation-order tolerance, hints that do not fit the shape are ignored, and "" restores the planner."""
+    args, m, _ = pair
+    lib = be._lib.lib()
+    rng = np.random.default_rng(3)
+    prompt = torch.from_numpy(rng.integers(0, args.vocab_size, 24))
+
+    def run():
+        m._fwd_ws = None                                     # the workspace size depends on the split
+        out = m(prompt[None], cache=m.make_cache(128))[0].float().cpu().numpy()
+        m.check_fused_error()
+        return out
+
+    want = run()
+    try:
+        lib.b200_forward_plan_hint(b"A=1:1:2,C=2:2:1,D=1:1:1,E=1:2:2,H=2:2:1")
+        _close(run(), want, 2.0 ** -8, 4e-3)
+        lib.b200_forward_plan_hint(b"A=8:99:99,E=3:1:1")   # infeasible values: the planner's own choice is used
+        assert np.array_equal(run(), want)
+    finally:
+        lib.b200_forward_plan_hint(b"")
+    assert np.array_equal(run(), want)
