@@ -233,3 +233,38 @@ def test_plan_hint_changes_the_work_split_not_the_result(be, pair):
     finally:
         lib.b200_forward_plan_hint(b"")
     assert np.array_equal(run(), want)
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_fused_pass_equals_per_op_kernels_at_tensor_parallel_shard_shapes(be, cuda, world):
+    """The layer shapes one rank of a 70B-shape target cut over 4 or 8 GPUs multiplies (hidden 8192, 64/8 heads
+    and 28672 MLP rows divided by the world size, a vocabulary shard), as a whole model on one GPU with a 24-row
+    tree pass: the planner's splits for these narrow, deep matrices against the per-op kernels."""
+    full = be.shape_preset("llama3-70b")
+    args = dataclasses.replace(full, num_hidden_layers=1, head_dim=128,
+                               num_attention_heads=full.num_attention_heads // world,
+                               num_key_value_heads=full.num_key_value_heads // world,
+                               intermediate_size=full.intermediate_size // world,
+                               vocab_size=full.vocab_size // world)
+    m = be.Model.random_init(args, seed=33, device=cuda).relayout()
+    assert m.can_fuse()
+    g = torch.Generator().manual_seed(4)
+    prompt = torch.randint(0, args.vocab_size, (140,), generator=g)
+    tree = torch.randint(0, args.vocab_size, (24,), generator=g)
+    tm = torch.tril(torch.ones(24, 24, dtype=torch.bool))
+    tm[13:, 6:12] = False
+    tm |= torch.eye(24, dtype=torch.bool)
+    pos = tm.sum(1) - 1
+    outs = {}
+    for fused in (True, False):
+        m.fused = fused
+        cache = m.make_cache(256)
+        m(prompt[None], cache=cache, logits_last_only=True)
+        t = be.eagle.tree_decoding(tree[None], tm, pos, m, cache)[0].float().cpu()
+        outs[fused] = (t, cache.data[:, :, :, :140 + 24].float().cpu())
+    m.fused = True
+    m.check_fused_error()
+    for a, b in zip(outs[True], outs[False]):
+        assert torch.isfinite(a).all()
+        # hidden 8192 with random weights gives logits of magnitude ~10: the absolute term follows their scale
+        _close(a.numpy(), b.numpy(), 2.0 ** -6, max(2e-2, 2.0 ** -8 * float(b.abs().max())))
