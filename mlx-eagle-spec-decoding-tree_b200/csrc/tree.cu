@@ -15,7 +15,9 @@ namespace b200 {
 namespace {
 
 constexpr int kK = 8;                 // children per node (hard-wired in the reference, mlx_eagle.py:750)
-constexpr int kTopkChunk = 4096;      // logits handled by one CTA of the row kernels
+constexpr int kTopkChunk = 4096;      // logits handled by one CTA of the top-k and argmax kernels
+constexpr int kStatChunk = 1024;      // ... of the max and sum-of-exponentials kernels: four elements per thread (the fp64
+                                      //     exponential is a long dependent chain; short chains, many CTAs)
 constexpr int kMaxDepth = 7;
 constexpr int kMaxPool = kK + kK * kK * kMaxDepth;
 
@@ -102,7 +104,7 @@ __global__ void row_max_kernel(const __half* __restrict__ logits, int V, uint32_
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.y;
-    const int begin = blockIdx.x * kTopkChunk, end = min(V, begin + kTopkChunk);
+    const int begin = blockIdx.x * kStatChunk, end = min(V, begin + kStatChunk);
     const __half* row = logits + (size_t)r * V;
     uint32_t best = 0;
     for (int i = begin + threadIdx.x; i < end; i += blockDim.x) best = max(best, order_bits(__half2float(row[i])));
@@ -116,7 +118,7 @@ __global__ void row_sumexp_kernel(const __half* __restrict__ logits, int V, cons
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.y;
-    const int begin = blockIdx.x * kTopkChunk, end = min(V, begin + kTopkChunk);
+    const int begin = blockIdx.x * kStatChunk, end = min(V, begin + kStatChunk);
     const __half* row = logits + (size_t)r * V;
     const double mx = (double)unorder_bits(row_max[r]);
     unsigned long long acc = 0;
@@ -564,7 +566,7 @@ int b200_logits_rowstats(const void* logits, int R, int V, uint32_t* row_max, un
                          void* stream) {
     if (!logits || !row_max || !row_sum || R < 1 || R > 32 || V < 1) return B200_EINVAL;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    dim3 grid(b200::nblk_for(V), R);
+    dim3 grid((V + b200::kStatChunk - 1) / b200::kStatChunk, R);
     b200::launch_kernel(b200::row_max_kernel, dim3(grid), dim3(256), 0, st, static_cast<const __half*>(logits), V, row_max);
     b200::launch_kernel(b200::row_sumexp_kernel, dim3(grid), dim3(256), 0, st, static_cast<const __half*>(logits), V, row_max, row_sum);
     return b200::check_launch();
