@@ -137,36 +137,49 @@ __global__ void __launch_bounds__(256) row_topk_kernel(const __half* __restrict_
                                                        int by_score, unsigned long long* __restrict__ cand) {
     pdl_wait();
     pdl_launch_dependents();
-    __shared__ unsigned long long keys[kTopkChunk];
-    __shared__ unsigned long long wbest[8];
+    // Every thread keeps its 16 keys in registers; each warp selects the top 8 of its 512 keys with warp
+    // shuffles only, then one warp selects the top 8 of the 64 survivors: one block-wide barrier in all.
+    constexpr int PER = kTopkChunk / 256;
+    __shared__ unsigned long long wtop[8 * kK];
     const int r = blockIdx.y;
     const int begin = blockIdx.x * kTopkChunk, end = min(V, begin + kTopkChunk);
-    const int cnt = end - begin;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const __half* row = logits + (size_t)r * V;
     double lse = 0.0;
     if (by_score) lse = row_lse(row_max[r], row_sum[r]);
-    for (int i = threadIdx.x; i < cnt; i += 256) {
-        const float l = __half2float(row[begin + i]);
-        keys[i] = make_key(by_score ? score_of(l, lse) : l, (uint32_t)(begin + i));
+    unsigned long long mine[PER];
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = begin + j * 256 + (int)threadIdx.x;
+        mine[j] = 0ull;                                        // past the end: never selected
+        if (i < end) {
+            const float l = __half2float(row[i]);
+            mine[j] = make_key(by_score ? score_of(l, lse) : l, (uint32_t)i);
+        }
     }
-    __syncthreads();
     unsigned long long bound = ~0ull;
-    unsigned long long* out = cand + ((size_t)r * gridDim.x + blockIdx.x) * kK;
     for (int round = 0; round < kK; round++) {
         unsigned long long best = 0;
-        for (int i = threadIdx.x; i < cnt; i += 256) {
-            const unsigned long long k = keys[i];
-            if (k < bound && k > best) best = k;
-        }
-        best = warp_max_key(best);
-        if ((threadIdx.x & 31) == 0) wbest[threadIdx.x >> 5] = best;
-        __syncthreads();
-        best = wbest[0];
 #pragma unroll
-        for (int w = 1; w < 8; w++) best = wbest[w] > best ? wbest[w] : best;
-        if (threadIdx.x == 0) out[round] = best;           // 0 when the chunk has run out
+        for (int j = 0; j < PER; j++)
+            if (mine[j] < bound && mine[j] > best) best = mine[j];
+        best = warp_max_key(best);
+        if (lane == 0) wtop[warp * kK + round] = best;         // 0 when the warp has run out
         bound = best ? best : 0ull;
-        __syncthreads();
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const unsigned long long k0 = wtop[lane], k1 = wtop[lane + 32];
+        unsigned long long* out = cand + ((size_t)r * gridDim.x + blockIdx.x) * kK;
+        bound = ~0ull;
+        for (int round = 0; round < kK; round++) {
+            unsigned long long best = 0;
+            if (k0 < bound && k0 > best) best = k0;
+            if (k1 < bound && k1 > best) best = k1;
+            best = warp_max_key(best);
+            if (lane == 0) out[round] = best;                  // 0 when the chunk has run out
+            bound = best ? best : 0ull;
+        }
     }
 }
 
@@ -226,10 +239,19 @@ __global__ void __launch_bounds__(256) tree_expand_kernel(const ExpandParams p) 
         const double lse = row_lse(p.row_max[r], p.row_sum[r]);
         const unsigned long long* c = p.cand + (size_t)r * p.nblk * kK;
         const int n = p.nblk * kK;
+        // the row's candidates stay in registers for the eight selection rounds (up to kCandRegs * 32 of them;
+        // a larger vocabulary re-reads them from memory)
+        constexpr int kCandRegs = 12;
+        unsigned long long mine[kCandRegs];
+#pragma unroll
+        for (int j = 0; j < kCandRegs; j++) mine[j] = (lane + 32 * j < n) ? c[lane + 32 * j] : 0ull;
         unsigned long long bound = ~0ull;
         for (int round = 0; round < kK; round++) {
             unsigned long long best = 0;
-            for (int i = lane; i < n; i += 32) {
+#pragma unroll
+            for (int j = 0; j < kCandRegs; j++)
+                if (mine[j] < bound && mine[j] > best) best = mine[j];
+            for (int i = lane + 32 * kCandRegs; i < n; i += 32) {
                 const unsigned long long k = c[i];
                 if (k < bound && k > best) best = k;
             }
