@@ -441,12 +441,9 @@ TPlan make_tplan(int M, int N, int K, bool dual, long long ws_bytes) {
 template <int MT, int S, int WN, bool DUAL>
 int launch_t(const TiledParams& p, const TPlan& pl, cudaStream_t stream) {
     auto kern = qmm_tiled_kernel<MT, S, WN, DUAL>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 111 * 1024) != cudaSuccess)
-            return check_launch();
-        attr_set = true;
-    }
+    // per launch: the attribute belongs to the current device, and a process may drive several
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 111 * 1024) != cudaSuccess)
+        return check_launch();
     launch_kernel(kern, dim3(pl.grid), dim3((WN + 1) * 32), pl.smem_bytes, stream, p);
     return check_launch();
 }
