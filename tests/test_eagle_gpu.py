@@ -131,3 +131,17 @@ def test_step_log_does_not_overflow_when_replayed_past_its_capacity(be, models):
     assert int(dec.ctl[4]) == 9                  # CTL_STEP
     assert bool((big[12:] == -7).all())          # nothing written behind the log
     assert bool((big[:12:2] >= 0).all())         # the six logged steps are there
+
+
+@pytest.mark.parametrize("depth,T", [(2, 10), (1, 3), (5, 20), (0, 7)])
+def test_tree_sizes_outside_the_reference_s_four_match_the_oracle(be, models, depth, T):
+    """The reference's kernel restricts verify_num_tokens to 7, 15, 23, 31 (README.md:18); here any size up to 31
+    and any depth up to 6 runs (the passes take any row count), and the result still equals the CPU oracle's."""
+    args, base, draft, states = models
+    rng = np.random.default_rng(100 + T)
+    prompt = rng.integers(0, args.vocab_size, 17)
+    res = be.generate_step(torch.from_numpy(prompt), base, draft, depth=depth, verify_num_tokens=T, max_tokens=24, N=24,
+                           verbose=False)
+    ob, od = model_ref.OracleModel(args, states[0]), model_ref.OracleModel(args, states[1])
+    ref = eagle_ref.generate_step(prompt, ob, od, depth=depth, verify_num_tokens=T, max_tokens=24, N=24)
+    assert res["tokens"] == ref["tokens"] and res["accept_lengths"] == ref["accept_lengths"]
