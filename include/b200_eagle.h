@@ -352,7 +352,8 @@ void b200_forward_plan_hint(const char* spec);
  * Draft tree, acceptance and compaction.  One request; k = 8 children per node.
  * ctl is int32[16]: [0] committed length of the target cache, [1] of the draft cache, [2] accept
  * length of the previous step, [3] tokens generated, [4] step, [5] draft cache length after the
- * catch-up pass, [6] capacity of out_tokens, [7] best path of the last step.
+ * catch-up pass, [6] capacity of out_tokens, [7] best path of the last step, [8] capacity of the step log, [9] end-of-sequence
+ * id + 1 (0 = none), [10] done flag, [11] token count at the stop, [12] seed and [13] draw count of sampling acceptance.
  * Ordering keys: (order-preserving image of the fp32 value) << 32 | (0xffffffff - index).
  * ------------------------------------------------------------------------------------------ */
 int b200_topk_blocks(int V);
@@ -390,6 +391,26 @@ int b200_argmax_key_shift(unsigned long long* best_key, int R, unsigned int inde
 int b200_tree_accept(int T, unsigned long long* argmax_key, const int* draft_tokens, const int* retrieve,
                      const int* tree_info, int* ctl, int* y, int* accept_rows, int* out_tokens,
                      int* step_log, void* stream);
+
+/* Sampling acceptance at temperature > 0 (no counterpart in the reference, which is greedy only: README.md:9;
+ * the same role as evaluate_posterior_greedy + the bookkeeping of generate_step, mlx_eagle.py:311-326,587-599).
+ * Speculative sampling on the verify tree: with p = softmax(logits[node] / temperature), walk down from the root; a
+ * node's children are tried in node order, a child with token x is accepted with probability p(x) of what is left of
+ * the node's distribution, a rejected token's mass is removed; when no child is accepted the bonus token is drawn from
+ * what is left, so every emitted token is distributed as if sampled from the target alone.  Integer arithmetic
+ * throughout (masses round(exp((l - max) / temperature) * 2^40) from the deterministic exponential of the tree
+ * scores, 40-bit draws from splitmix64(seed = ctl[12], draw index = ctl[13])): a CPU restatement takes the same
+ * decisions bit for bit.  logits [T+1, V] fp16 are the target logits of the tree nodes, mask_index[n] the parent of node
+ * n + 1 (b200_tree_finalize); row_max / row_sum: [T+1] scratch, zero on entry, zero again on exit; workspace:
+ * b200_tree_accept_sample_workspace_bytes(V) bytes, 16-byte aligned.  Outputs as b200_tree_accept (best path = 0). */
+size_t b200_tree_accept_sample_workspace_bytes(int V);
+int b200_tree_accept_sample(int T, int V, const void* logits, uint32_t* row_max, unsigned long long* row_sum,
+                            const int* draft_tokens, const int* mask_index, double temperature, int* ctl, int* y,
+                            int* accept_rows, int* out_tokens, int* step_log, void* workspace, size_t workspace_bytes,
+                            void* stream);
+/* b200_logits_rowstats with the logits divided by `temperature` before the exponential. */
+int b200_logits_rowstats_temp(const void* logits, int R, int V, uint32_t* row_max, unsigned long long* row_sum,
+                              double temperature, void* stream);
 /* accept_candidate (mlx_eagle.py:349-376) over all layers; cache is [layers][2][Hkv][cache_rows][hd]. */
 int b200_kv_compact(void* cache, int layers, int Hkv, int cache_rows, int hd, const int* accept_rows,
                     const int* ctl, void* stream);

@@ -98,6 +98,12 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_logits_argmax.argtypes = [vp, i32, i32, vp, vp]
     l.b200_tree_accept.restype = i32
     l.b200_tree_accept.argtypes = [i32] + [vp] * 10
+    l.b200_tree_accept_sample_workspace_bytes.restype = sz
+    l.b200_tree_accept_sample_workspace_bytes.argtypes = [i32]
+    l.b200_tree_accept_sample.restype = i32
+    l.b200_tree_accept_sample.argtypes = [i32, i32, vp, vp, vp, vp, vp, ctypes.c_double, vp, vp, vp, vp, vp, vp, sz, vp]
+    l.b200_logits_rowstats_temp.restype = i32
+    l.b200_logits_rowstats_temp.argtypes = [vp, i32, i32, vp, vp, ctypes.c_double, vp]
     l.b200_forward_plan_hint.restype = None
     l.b200_forward_plan_hint.argtypes = [ctypes.c_char_p]
     l.b200_forward_workspace_bytes.restype = sz

@@ -28,6 +28,8 @@ enum { CTL_BASE_LEN = 0, CTL_DRAFT_LEN = 1, CTL_ACCEPT = 2, CTL_NGEN = 3, CTL_ST
        CTL_EOS = 9,          // end-of-sequence token id + 1 (0 = none)
        CTL_DONE = 10,        // set once an accepted token was the end-of-sequence token
        CTL_STOP_N = 11,      // generated-token count up to and including that token
+       CTL_SEED = 12,        // sampling acceptance: seed of the request's random stream ...
+       CTL_DRAW = 13,        // ... and the number of draws made so far
        CTL_WORDS = 16 };
 
 // ---------------------------------------------------------------- ordering keys
@@ -113,8 +115,10 @@ __global__ void row_max_kernel(const __half* __restrict__ logits, int V, uint32_
     if ((threadIdx.x & 31) == 0) atomicMax(row_max + r, best);
 }
 
+// temp: temperature the logits are divided by before the exponential (1.0: the plain soft-max; dividing by 1.0 is exact,
+// so the draft tree's log-probabilities are what they were).
 __global__ void row_sumexp_kernel(const __half* __restrict__ logits, int V, const uint32_t* __restrict__ row_max,
-                                  unsigned long long* __restrict__ row_sum) {
+                                  unsigned long long* __restrict__ row_sum, double temp) {
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.y;
@@ -123,7 +127,7 @@ __global__ void row_sumexp_kernel(const __half* __restrict__ logits, int V, cons
     const double mx = (double)unorder_bits(row_max[r]);
     unsigned long long acc = 0;
     for (int i = begin + threadIdx.x; i < end; i += blockDim.x)
-        acc += (unsigned long long)exp_fixed(__dsub_rn((double)__half2float(row[i]), mx));
+        acc += (unsigned long long)exp_fixed(__ddiv_rn(__dsub_rn((double)__half2float(row[i]), mx), temp));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if ((threadIdx.x & 31) == 0) atomicAdd(row_sum + r, acc);
@@ -463,6 +467,37 @@ __global__ void __launch_bounds__(512) tree_finalize_kernel(const FinalizeParams
     }
 }
 
+// The end of a step (generate_step's bookkeeping, mlx_eagle.py:587-599), by one thread: the bonus token after the
+// `accept` accepted ones (already in y and out_tokens), the step log, the end-of-sequence test, cache lengths, counters.
+__device__ void commit_step(int* ctl, int* y, int* out_tokens, int* step_log, int accept, int best, int bonus) {
+    const int P = ctl[CTL_BASE_LEN];
+    const int n = ctl[CTL_NGEN];
+    const int cap = ctl[CTL_OUT_CAP];
+    y[accept] = bonus;
+    if (n + accept < cap) out_tokens[n + accept] = bonus;
+    const int step = ctl[CTL_STEP];
+    if (step < ctl[CTL_LOG_CAP]) {                                      // the log has a fixed capacity; CTL_STEP keeps counting
+        step_log[2 * step] = accept;
+        step_log[2 * step + 1] = best;
+    }
+    const int eos1 = ctl[CTL_EOS];
+    if (eos1 > 0 && !ctl[CTL_DONE]) {                                   // first end-of-sequence token among this step's tokens
+        for (int j = 0; j <= accept; j++) {
+            if (y[j] == eos1 - 1) {
+                ctl[CTL_DONE] = 1;
+                ctl[CTL_STOP_N] = n + j + 1;
+                break;
+            }
+        }
+    }
+    ctl[CTL_DRAFT_LEN] = ctl[CTL_DRAFT_OFF];                            // draft cache rewound (mlx_eagle.py:593-594)
+    ctl[CTL_BASE_LEN] = P + accept + 1;                                 // mlx_eagle.py:376
+    ctl[CTL_ACCEPT] = accept;
+    ctl[CTL_NGEN] = n + accept + 1;
+    ctl[CTL_STEP] = step + 1;
+    ctl[CTL_LAST_BEST] = best;
+}
+
 // ---------------------------------------------------------------- greedy acceptance (1 warp)
 struct AcceptParams {
     int T;
@@ -504,8 +539,7 @@ __global__ void tree_accept_kernel(const AcceptParams p) {
     const int accept = (int)(key >> 32);
     const int best = accept == 0 ? 0 : (int)key_index(key);
     if (lane == 0) {
-        const int P = p.ctl[CTL_BASE_LEN];
-        int n = p.ctl[CTL_NGEN];
+        const int n = p.ctl[CTL_NGEN];
         const int cap = p.ctl[CTL_OUT_CAP];
         p.accept_rows[0] = accept;
         for (int j = 0; j < kK; j++) p.y[j] = 0;
@@ -519,32 +553,181 @@ __global__ void tree_accept_kernel(const AcceptParams p) {
         int last = p.retrieve[best * RW + accept];
         last = last < 0 ? last + T + 1 : last;
         const int bonus = (int)key_index(p.argmax_key[last]);           // argmax(logits[best, accept])
-        p.y[accept] = bonus;
-        if (n + accept < cap) p.out_tokens[n + accept] = bonus;
-        const int step = p.ctl[CTL_STEP];
-        if (step < p.ctl[CTL_LOG_CAP]) {                                // the log has a fixed capacity; CTL_STEP keeps counting
-            p.step_log[2 * step] = accept;
-            p.step_log[2 * step + 1] = best;
-        }
-        const int eos1 = p.ctl[CTL_EOS];
-        if (eos1 > 0 && !p.ctl[CTL_DONE]) {                             // first end-of-sequence token among this step's tokens
-            for (int j = 0; j <= accept; j++) {
-                if (p.y[j] == eos1 - 1) {
-                    p.ctl[CTL_DONE] = 1;
-                    p.ctl[CTL_STOP_N] = n + j + 1;
-                    break;
-                }
-            }
-        }
-        p.ctl[CTL_DRAFT_LEN] = p.ctl[CTL_DRAFT_OFF];                    // draft cache rewound (mlx_eagle.py:593-594)
-        p.ctl[CTL_BASE_LEN] = P + accept + 1;                           // mlx_eagle.py:376
-        p.ctl[CTL_ACCEPT] = accept;
-        p.ctl[CTL_NGEN] = n + accept + 1;
-        p.ctl[CTL_STEP] = step + 1;
-        p.ctl[CTL_LAST_BEST] = best;
+        commit_step(p.ctl, p.y, p.out_tokens, p.step_log, accept, best, bonus);
     }
     __syncwarp();
     if (lane <= T) p.argmax_key[lane] = 0ull;
+}
+
+// ---------------------------------------------------------------- sampling acceptance
+// Speculative sampling on the verify tree at temperature `temp` (the reference is greedy only, README.md:9).  With
+// p = softmax(logits[node] / temp): walk down from the root; at a node, take its children in node order (descending
+// draft probability); child with token x is accepted with probability p(x) of what is left of the distribution; a
+// rejected token's mass is removed and the rest renormalised; when no child is accepted (or the node is a leaf) the
+// bonus token is drawn from what is left.  Every emitted token is then distributed exactly as sampling from the target
+// alone.  All arithmetic is in integers so that a CPU restatement takes the same decisions bit for bit: masses are
+// e(v) = round(exp((l_v - max) / temp) * 2^40) with the deterministic exponential above, their row sums come from
+// row_sumexp_kernel, random draws are 40-bit outputs of a counter-based generator (splitmix64 of seed and draw index).
+struct SampleState {                    // what the acceptance walk leaves for the bonus draw
+    int node, nremoved, accept, pad;
+    unsigned long long rem_total, u;    // remaining mass of the node's row; 40-bit draw for the bonus token
+    int removed[kK];
+};
+
+__device__ __forceinline__ unsigned long long rand40(unsigned int seed, unsigned int counter) {
+    unsigned long long z = ((unsigned long long)seed << 32 | counter) + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return z >> 24;
+}
+__device__ __forceinline__ unsigned long long mass_of(float logit, uint32_t max_enc, double temp) {
+    return (unsigned long long)exp_fixed(__ddiv_rn(__dsub_rn((double)logit, (double)unorder_bits(max_enc)), temp));
+}
+
+struct SampleParams {
+    int T, V;
+    const __half* logits;               // [T+1, V] target logits of the tree nodes
+    uint32_t* row_max;                  // [T+1] at temperature `temp` (cleared on exit)
+    unsigned long long* row_sum;        // [T+1]
+    const int* draft_tokens;            // [T+1]
+    const int* mask_index;              // [T] parent node of node n+1
+    double temp;
+    int* ctl;
+    int* y;
+    int* accept_rows;
+    int* out_tokens;
+    int* step_log;
+    SampleState* state;
+    unsigned long long* chunk_sums;     // [ceil(V / kStatChunk)]
+};
+
+// The acceptance walk, by one thread (at most 7 levels of at most 8 children).
+__global__ void tree_accept_sample_kernel(const SampleParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    if (threadIdx.x != 0) return;
+    const unsigned int seed = (unsigned int)p.ctl[CTL_SEED];
+    unsigned int draw = (unsigned int)p.ctl[CTL_DRAW];
+    const int n0 = p.ctl[CTL_NGEN], cap = p.ctl[CTL_OUT_CAP];
+    for (int j = 0; j < kK; j++) p.y[j] = 0;
+    int cur = 0, accept = 0, nrem = 0;
+    int removed[kK];
+    unsigned long long rem = p.row_sum[0];
+    while (true) {
+        rem = p.row_sum[cur];
+        nrem = 0;
+        int taken = -1;
+        for (int c = 1; c <= p.T && taken < 0 && accept < kK - 1; c++) {
+            if (p.mask_index[c - 1] != cur) continue;
+            const int x = p.draft_tokens[c];
+            const unsigned long long ex = mass_of(__half2float(p.logits[(size_t)cur * p.V + x]), p.row_max[cur], p.temp);
+            const unsigned long long u = rand40(seed, draw++);
+            // accept iff u / 2^40 < ex / rem, compared as 128-bit integers: u * rem < ex * 2^40
+            const unsigned long long lhi = __umul64hi(u, rem), llo = u * rem;
+            const unsigned long long rhi = ex >> 24, rlo = ex << 40;
+            if (lhi < rhi || (lhi == rhi && llo < rlo)) {
+                taken = c;
+            } else {
+                rem -= ex;
+                removed[nrem++] = x;
+            }
+        }
+        if (taken < 0) break;
+        p.accept_rows[1 + accept] = taken;
+        p.y[accept] = p.draft_tokens[taken];
+        if (n0 + accept < cap) p.out_tokens[n0 + accept] = p.draft_tokens[taken];
+        accept++;
+        cur = taken;
+    }
+    p.accept_rows[0] = accept;
+    p.state->node = cur;
+    p.state->nremoved = nrem;
+    p.state->accept = accept;
+    p.state->rem_total = rem;
+    p.state->u = rand40(seed, draw++);
+    for (int j = 0; j < kK; j++) p.state->removed[j] = j < nrem ? removed[j] : -1;
+    p.ctl[CTL_DRAW] = (int)draw;
+}
+
+// Mass of every 1024-token chunk of the chosen node's row, rejected tokens left out.
+__global__ void bonus_chunk_sums_kernel(const SampleParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int node = p.state->node, nrem = p.state->nremoved;
+    const int begin = blockIdx.x * kStatChunk, end = min(p.V, begin + kStatChunk);
+    const __half* row = p.logits + (size_t)node * p.V;
+    const uint32_t mx = p.row_max[node];
+    unsigned long long acc = 0;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        bool gone = false;
+        for (int j = 0; j < nrem; j++) gone = gone || (p.state->removed[j] == i);
+        if (!gone) acc += mass_of(__half2float(row[i]), mx, p.temp);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    __shared__ unsigned long long ws[8];
+    if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long t = 0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += ws[w];
+        p.chunk_sums[blockIdx.x] = t;
+    }
+}
+
+// The bonus token: the token whose cumulative mass (token order, rejected tokens left out) first exceeds
+// u * remaining / 2^40; then the step's bookkeeping.  One CTA of 256 threads.
+__global__ void __launch_bounds__(256) bonus_pick_kernel(const SampleParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ unsigned long long s_target, s_base;
+    __shared__ int s_chunk;
+    __shared__ unsigned long long s_mass[kStatChunk];
+    const int node = p.state->node, nrem = p.state->nremoved, accept = p.state->accept;
+    const int nchunks = (p.V + kStatChunk - 1) / kStatChunk;
+    if (threadIdx.x == 0) {
+        const unsigned long long u = p.state->u, rem = p.state->rem_total;
+        const unsigned long long target = (__umul64hi(u, rem) << 24) | ((u * rem) >> 40);     // floor(u * rem / 2^40) < rem
+        unsigned long long cum = 0;
+        int c = 0;
+        for (; c < nchunks - 1; c++) {
+            const unsigned long long t = p.chunk_sums[c];
+            if (cum + t > target) break;
+            cum += t;
+        }
+        s_target = target;
+        s_base = cum;
+        s_chunk = c;
+    }
+    __syncthreads();
+    const int begin = s_chunk * kStatChunk, end = min(p.V, begin + kStatChunk);
+    const __half* row = p.logits + (size_t)node * p.V;
+    const uint32_t mx = p.row_max[node];
+    for (int i = threadIdx.x; i < kStatChunk; i += 256) {
+        const int v = begin + i;
+        bool gone = v >= end;
+        for (int j = 0; j < nrem; j++) gone = gone || (p.state->removed[j] == v);
+        s_mass[i] = gone ? 0ull : mass_of(__half2float(row[v]), mx, p.temp);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long cum = s_base;
+        int bonus = -1, lastpos = -1;
+        for (int i = 0; i < end - begin; i++) {
+            if (s_mass[i] == 0ull) continue;
+            lastpos = i;
+            if (cum + s_mass[i] > s_target) { bonus = begin + i; break; }
+            cum += s_mass[i];
+        }
+        if (bonus < 0) bonus = begin + max(lastpos, 0);     // (unreachable when the sums are consistent)
+        commit_step(p.ctl, p.y, p.out_tokens, p.step_log, accept, 0, bonus);
+    }
+    __syncthreads();
+    if ((int)threadIdx.x <= p.T) {                          // the statistics buffers start every use at zero
+        p.row_max[threadIdx.x] = 0u;
+        p.row_sum[threadIdx.x] = 0ull;
+    }
 }
 
 // ---------------------------------------------------------------- KV compaction of the accepted path
@@ -590,7 +773,18 @@ int b200_logits_rowstats(const void* logits, int R, int V, uint32_t* row_max, un
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid((V + b200::kStatChunk - 1) / b200::kStatChunk, R);
     b200::launch_kernel(b200::row_max_kernel, dim3(grid), dim3(256), 0, st, static_cast<const __half*>(logits), V, row_max);
-    b200::launch_kernel(b200::row_sumexp_kernel, dim3(grid), dim3(256), 0, st, static_cast<const __half*>(logits), V, row_max, row_sum);
+    b200::launch_kernel(b200::row_sumexp_kernel, dim3(grid), dim3(256), 0, st, static_cast<const __half*>(logits), V, row_max, row_sum, 1.0);
+    return b200::check_launch();
+}
+
+int b200_logits_rowstats_temp(const void* logits, int R, int V, uint32_t* row_max, unsigned long long* row_sum,
+                              double temperature, void* stream) {
+    if (!logits || !row_max || !row_sum || R < 1 || R > 32 || V < 1 || !(temperature > 0.0)) return B200_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    dim3 grid((V + b200::kStatChunk - 1) / b200::kStatChunk, R);
+    b200::launch_kernel(b200::row_max_kernel, dim3(grid), dim3(256), 0, st, static_cast<const __half*>(logits), V, row_max);
+    b200::launch_kernel(b200::row_sumexp_kernel, dim3(grid), dim3(256), 0, st, static_cast<const __half*>(logits), V, row_max, row_sum,
+                        temperature);
     return b200::check_launch();
 }
 
@@ -682,6 +876,37 @@ int b200_tree_accept(int T, unsigned long long* argmax_key, const int* draft_tok
     p.tree_info = tree_info; p.ctl = ctl; p.y = y; p.accept_rows = accept_rows; p.out_tokens = out_tokens;
     p.step_log = step_log;
     b200::launch_kernel(b200::tree_accept_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), p);
+    return b200::check_launch();
+}
+
+size_t b200_tree_accept_sample_workspace_bytes(int V) {
+    if (V < 1) return 0;
+    return 128 + sizeof(unsigned long long) * (size_t)((V + b200::kStatChunk - 1) / b200::kStatChunk);
+}
+
+int b200_tree_accept_sample(int T, int V, const void* logits, uint32_t* row_max, unsigned long long* row_sum,
+                            const int* draft_tokens, const int* mask_index, double temperature, int* ctl, int* y,
+                            int* accept_rows, int* out_tokens, int* step_log, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+    if (T < 1 || T > 31 || V < 1 || !logits || !row_max || !row_sum || !draft_tokens || !mask_index || !ctl || !y ||
+        !accept_rows || !out_tokens || !step_log || !workspace || !(temperature > 0.0))
+        return B200_EINVAL;
+    if (workspace_bytes < b200_tree_accept_sample_workspace_bytes(V)) return B200_EWORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return B200_EALIGN;
+    static_assert(sizeof(b200::SampleState) <= 128, "the walk's state must fit the head of the workspace");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = b200_logits_rowstats_temp(logits, T + 1, V, row_max, row_sum, temperature, stream);
+    if (rc != B200_OK) return rc;
+    b200::SampleParams p{};
+    p.T = T; p.V = V; p.logits = static_cast<const __half*>(logits); p.row_max = row_max; p.row_sum = row_sum;
+    p.draft_tokens = draft_tokens; p.mask_index = mask_index; p.temp = temperature; p.ctl = ctl; p.y = y;
+    p.accept_rows = accept_rows; p.out_tokens = out_tokens; p.step_log = step_log;
+    p.state = static_cast<b200::SampleState*>(workspace);
+    p.chunk_sums = reinterpret_cast<unsigned long long*>(static_cast<char*>(workspace) + 128);
+    const int nchunks = (V + b200::kStatChunk - 1) / b200::kStatChunk;
+    b200::launch_kernel(b200::tree_accept_sample_kernel, dim3(1), dim3(32), 0, st, p);
+    b200::launch_kernel(b200::bonus_chunk_sums_kernel, dim3(nchunks), dim3(256), 0, st, p);
+    b200::launch_kernel(b200::bonus_pick_kernel, dim3(1), dim3(256), 0, st, p);
     return b200::check_launch();
 }
 

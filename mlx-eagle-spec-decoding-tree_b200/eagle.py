@@ -30,7 +30,7 @@ from .llama import KVCache, Model, ModelArgs, MAX_ROWS, MAX_REQUESTS, shape_pres
 K = 8                      # children per node (mlx_eagle.py:750)
 RETRIEVE_W = 9             # row width of the retrieve-index matrix (max depth 7 + 2)
 CTL_BASE_LEN, CTL_DRAFT_LEN, CTL_ACCEPT, CTL_NGEN, CTL_STEP, CTL_DRAFT_OFF, CTL_OUT_CAP, CTL_BEST = range(8)
-CTL_LOG_CAP, CTL_EOS, CTL_DONE, CTL_STOP_N = 8, 9, 10, 11
+CTL_LOG_CAP, CTL_EOS, CTL_DONE, CTL_STOP_N, CTL_SEED, CTL_DRAW = 8, 9, 10, 11, 12, 13
 
 
 class SpecDecoder:
@@ -38,7 +38,8 @@ class SpecDecoder:
 
     def __init__(self, base_model: Model, draft_model: Model, depth: int, verify_num_tokens: int,
                  cache_rows: int, max_out_tokens: int = 4096, max_steps: int = 4096, k: int = K,
-                 base_cache: Optional[KVCache] = None, draft_cache: Optional[KVCache] = None, req: int = 0):
+                 base_cache: Optional[KVCache] = None, draft_cache: Optional[KVCache] = None, req: int = 0,
+                 temperature: float = 0.0, seed: int = 0):
         if k != K:
             raise _lib.B200Error("k is fixed to 8, as in the reference (mlx_eagle.py:750)")
         if not (0 <= depth <= 6):
@@ -48,6 +49,11 @@ class SpecDecoder:
             raise _lib.B200Error("verify_num_tokens must be <= 31 and <= pool size (README: 7, 15, 23 or 31)")
         self.base, self.draft = base_model, draft_model
         self.depth, self.T = depth, T
+        # temperature > 0: speculative sampling instead of greedy acceptance (b200_tree_accept_sample); the reference
+        # is greedy only (README.md:9).  The first token (from the prompt's logits) stays greedy.
+        self.temperature, self.seed = float(temperature), int(seed)
+        if self.temperature > 0.0 and base_model.tp is not None:
+            raise _lib.B200Error("sampling acceptance needs the whole vocabulary on one GPU (no tensor-parallel target)")
         dev = base_model.device
         self.device = dev
         # (a request of a BatchSpecDecoder gets its slabs of the shared caches and its row group ``req``)
@@ -76,6 +82,8 @@ class SpecDecoder:
         self.retrieve = torch.full((MAX_ROWS * RETRIEVE_W,), -1, **i32)
         self.tree_info = torch.zeros(2, **i32)
         self.accept_rows = torch.zeros(16, **i32)
+        nws = _lib.lib().b200_tree_accept_sample_workspace_bytes(base_model.args.vocab_size)
+        self.sample_ws = torch.zeros(nws, dtype=torch.uint8, device=dev) if self.temperature > 0.0 else None
         self.out_tokens = torch.zeros(max_out_tokens, **i32)
         self.step_log = torch.zeros(2 * max_steps, **i32)
         self.max_steps = max_steps
@@ -108,6 +116,8 @@ class SpecDecoder:
         host[CTL_OUT_CAP] = self.out_tokens.numel()
         host[CTL_LOG_CAP] = self.max_steps
         host[CTL_EOS] = 0 if eos_token_id is None else int(eos_token_id) + 1
+        host[CTL_SEED] = ((self.seed + 0x80000000) % (1 << 32)) - 0x80000000       # the 32-bit pattern of the seed
+        host[CTL_DRAW] = 0
         if eos_token_id is not None and first == int(eos_token_id):
             host[CTL_DONE], host[CTL_STOP_N] = 1, 0
         self.ctl.copy_(host)
@@ -181,6 +191,15 @@ class SpecDecoder:
         st = _lib.stream_ptr(self.device)
         a = self.base.args
         base = self.base
+        if self.temperature > 0.0:
+            ck(L.b200_tree_accept_sample(self.T, a.vocab_size, p(self.base_logits), p(self.row_max), p(self.row_sum),
+                                         p(self.draft_tokens), p(self.mask_index), self.temperature, p(self.ctl), p(self.y),
+                                         p(self.accept_rows), p(self.out_tokens), p(self.step_log), p(self.sample_ws),
+                                         self.sample_ws.numel(), st), "b200_tree_accept_sample")
+            ck(L.b200_kv_compact(p(self.base_cache.data), a.num_hidden_layers, a.num_key_value_heads,
+                                 self.base_cache.rows, a.head_dim, p(self.accept_rows), p(self.ctl), st),
+               "b200_kv_compact")
+            return
         ck(L.b200_logits_argmax(p(self.base_logits), self.T + 1, base.vocab_local, p(self.argmax_key), st),
            "b200_logits_argmax")
         if base.tp is not None and base.tp.peers is not None:
@@ -533,16 +552,16 @@ def spec_step(dec: SpecDecoder):
 def generate_step(prompt: torch.Tensor, base_model: Model, draft_model: Model, prefill_step_size: int = 512,
                   k: int = 8, depth: int = 5, verify_num_tokens: int = 31, max_tokens: int = 128, tokenizer=None,
                   N: int = 20, use_graph: bool = True, verbose: bool = True, eos_token_id: Optional[int] = None,
-                  clip: bool = False):
+                  clip: bool = False, temperature: float = 0.0, seed: int = 0):
     """Greedy tree-speculative generation (``mlx_eagle.py:503-606``), same arguments as the reference
     (``verify_num_tokens`` is limited to 31 here) plus the two stop rules of ``SpecDecoder.generate``
-    (``eos_token_id``, ``clip``).  Builds a ``SpecDecoder`` for the request, captures
+    (``eos_token_id``, ``clip``) and, with ``temperature > 0``, sampling acceptance from the random stream ``seed``.  Builds a ``SpecDecoder`` for the request, captures
     its step graph and calls ``SpecDecoder.generate``; prints the reference's three summary lines.
     Returns the result dict of ``generate`` plus the decoder under ``"decoder"``."""
     rows = prompt.numel() + max_tokens + 8 * (depth + 2) + verify_num_tokens + 128
     rows = ((rows + 63) // 64) * 64
     dec = SpecDecoder(base_model, draft_model, depth, verify_num_tokens, rows,
-                      max_out_tokens=max_tokens + 128, max_steps=N + 8, k=k)
+                      max_out_tokens=max_tokens + 128, max_steps=N + 8, k=k, temperature=temperature, seed=seed)
     dec.warmup(capture=use_graph)
     stats = dec.generate(prompt, max_tokens=max_tokens, N=N, prefill_step_size=prefill_step_size,
                          eos_token_id=eos_token_id, clip=clip)
@@ -573,6 +592,8 @@ def parse_args(argv=None):
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--eos-token-id", type=int, default=None, help="stop at the first generated token with this id")
     p.add_argument("--clip", action="store_true", help="cut the output to exactly --max-tokens tokens")
+    p.add_argument("--temp", type=float, default=0.0,
+                   help="0: greedy acceptance (the reference); > 0: sampling acceptance at this temperature, stream --seed")
     return p.parse_args(argv)
 
 
@@ -609,7 +630,7 @@ def main(argv=None):
         eos = int(tokenizer.eos_token_id)
     generate_step(ids, base, draft, k=8, depth=args.depth, verify_num_tokens=args.verify_num_tokens,
                   max_tokens=args.max_tokens, prefill_step_size=512, N=args.max_generation_steps,
-                  eos_token_id=eos, clip=args.clip, tokenizer=tokenizer)
+                  eos_token_id=eos, clip=args.clip, tokenizer=tokenizer, temperature=args.temp, seed=args.seed)
 
 
 if __name__ == "__main__":

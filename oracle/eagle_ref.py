@@ -67,11 +67,14 @@ def spec_step(y, base_model, draft_model, base_cache, draft_cache, accept_length
 
 
 def generate_step(prompt, base_model: OracleModel, draft_model: OracleModel, prefill_step_size=512, k=8, depth=5,
-                  verify_num_tokens=15, max_tokens=128, N=20, cache_rows=None, eos_token_id=None, clip=False):
+                  verify_num_tokens=15, max_tokens=128, N=20, cache_rows=None, eos_token_id=None, clip=False,
+                  temperature=0.0, seed=0):
     """Returns ``dict(tokens, accept_lengths, steps, seconds, tokens_per_second)``; timer starts after
     prompt ingestion (``mlx_eagle.py:541``).  ``eos_token_id`` / ``clip`` are the two stop rules the
     product adds to the reference loop (stop after the first end-of-sequence token; cut to exactly
-    ``max_tokens``), restated here so the GPU loop can be checked against them."""
+    ``max_tokens``), restated here so the GPU loop can be checked against them.  ``temperature > 0`` switches the
+    acceptance from greedy to speculative sampling (``tree_ref.evaluate_posterior_sample``; the first token, taken
+    from the prompt's logits, stays greedy) with the random stream ``seed``."""
     y = np.asarray(prompt).reshape(-1)
     rows = cache_rows or (y.size + max_tokens + 8 * (depth + 2) + verify_num_tokens + 128)
     base_cache = make_prompt_cache(base_model, rows)
@@ -89,23 +92,29 @@ def generate_step(prompt, base_model: OracleModel, draft_model: OracleModel, pre
     steps = 0
     finish = "steps"
     stop_n = 0 if (eos_token_id is not None and tokens[0] == eos_token_id) else None
+    draw = 0
     for _ in range(N):
         if n >= max_tokens or stop_n is not None:
             break
         tpi, mi, dt, logits, base_offset, draft_offset = spec_step(
             y, base_model, draft_model, base_cache, draft_cache, accept_length, k, depth, verify_num_tokens)
-        retrieve = tr.post_process_draft_tree(tpi, verify_num_tokens, mi)
-        candidates = dt[0][retrieve]
-        best, accept_length, sample_p = tr.evaluate_posterior_greedy(logits[retrieve], candidates)
-        accept_indices = retrieve[best, 1: 1 + accept_length]
-        accepted_tokens = candidates[best, 1: 1 + accept_length]
+        if temperature > 0.0:
+            accept_indices, accepted_tokens, sampled, draw = tr.evaluate_posterior_sample(
+                logits, dt[0], mi, temperature, seed, draw)
+            accept_length = int(accept_indices.size)
+        else:
+            retrieve = tr.post_process_draft_tree(tpi, verify_num_tokens, mi)
+            candidates = dt[0][retrieve]
+            best, accept_length, sample_p = tr.evaluate_posterior_greedy(logits[retrieve], candidates)
+            accept_indices = retrieve[best, 1: 1 + accept_length]
+            accepted_tokens = candidates[best, 1: 1 + accept_length]
         tr.accept_candidate([c.keys for c in base_cache], [c.values for c in base_cache], accept_indices,
                             accept_length, base_offset)
         for c in base_cache:
             c.offset = base_offset + accept_length + 1
         for c in draft_cache:
             c.offset = draft_offset
-        next_token = int(tr.first_argmax(sample_p.astype(np.float32)))
+        next_token = sampled if temperature > 0.0 else int(tr.first_argmax(sample_p.astype(np.float32)))
         y = np.concatenate([accepted_tokens.astype(np.int64), [next_token]])
         tokens.extend(int(t) for t in y)
         accept_lengths.append(int(accept_length))

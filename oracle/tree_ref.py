@@ -211,6 +211,74 @@ def evaluate_posterior_from_node_argmax(node_argmax: np.ndarray, draft_tokens: n
     return best, a, accept_indices, accepted_tokens, bonus
 
 
+# ----------------------------------------------------------------------------- sampling acceptance
+# The reference is greedy only (README.md:9: "no sampling yet").  This is the restatement of the product's
+# speculative sampling on the verify tree (include/b200_eagle.h, b200_tree_accept_sample): integer arithmetic on the
+# masses e(v) = round(exp((l_v - max) / temperature) * 2^40) of detmath.exp_fixed and a counter-based generator, so
+# that CPU and GPU take the same decisions.
+_M64 = (1 << 64) - 1
+
+
+def rand40(seed: int, counter: int) -> int:
+    """40-bit draw number ``counter`` of the stream ``seed`` (splitmix64 of the pair)."""
+    z = ((((seed & 0xFFFFFFFF) << 32) | (counter & 0xFFFFFFFF)) + 0x9E3779B97F4A7C15) & _M64
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+    z ^= z >> 31
+    return z >> 24
+
+
+def node_masses(logits_row: np.ndarray, temperature: float) -> np.ndarray:
+    """Fixed-point masses of one row of fp16 logits at ``temperature`` (int64, 2^40 scale)."""
+    from .detmath import exp_fixed
+    x = np.asarray(logits_row).astype(np.float64)
+    return exp_fixed((x - x.max()) / np.float64(temperature))
+
+
+def evaluate_posterior_sample(node_logits: np.ndarray, draft_tokens: np.ndarray, mask_index: np.ndarray,
+                              temperature: float, seed: int, draw: int):
+    """Walk the verify tree from the root: a node's children (ascending node index) are accepted with probability
+    mass(token) / remaining mass of the node's row, a rejected token's mass is removed; the bonus token is drawn from
+    what is left at the node where the walk stops.  ``node_logits`` ``(T+1, V)``, ``draft_tokens`` ``(T+1,)``,
+    ``mask_index[n]`` = parent of node ``n + 1``.  Returns ``accept_indices`` (node indices), ``accepted_tokens``,
+    ``bonus`` and the advanced draw counter."""
+    dt = np.asarray(draft_tokens).reshape(-1)
+    mi = np.asarray(mask_index).reshape(-1)
+    T = mi.size
+    cur, accepted = 0, []
+    while True:
+        e = node_masses(node_logits[cur], temperature)
+        rem = int(e.sum(dtype=np.int64))
+        removed = []
+        taken = -1
+        for c in range(1, T + 1):
+            if int(mi[c - 1]) != cur or len(accepted) >= 7:
+                continue
+            x = int(dt[c])
+            ex = int(e[x])
+            u = rand40(seed, draw)
+            draw += 1
+            if u * rem < (ex << 40):
+                taken = c
+                break
+            rem -= ex
+            removed.append(x)
+        if taken < 0:
+            break
+        accepted.append(taken)
+        cur = taken
+    u = rand40(seed, draw)
+    draw += 1
+    target = (u * rem) >> 40
+    e = e.copy()
+    for x in removed:
+        e[x] = 0
+    cum = np.cumsum(e.astype(object))                      # exact Python integers
+    bonus = int(np.searchsorted(np.asarray(cum, dtype=object), target, side="right"))
+    accept_indices = np.asarray(accepted, dtype=np.int64)
+    return accept_indices, dt[accept_indices] if accepted else np.zeros(0, dtype=dt.dtype), bonus, draw
+
+
 # ----------------------------------------------------------------------------- mlx_eagle.py:349-376
 def accept_candidate(keys: List[np.ndarray], values: List[np.ndarray], accept_indices: np.ndarray,
                      accept_length: int, offset: int) -> int:
