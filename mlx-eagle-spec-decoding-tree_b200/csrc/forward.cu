@@ -50,12 +50,13 @@ constexpr int kFwdThreads = kNCons + 32;      // + one producer warp
 constexpr int kRec = 1152;                    // bytes per 16-row x 128-k weight record
 constexpr int kWArea = 8 * 4 * kRec;          // weight bytes of a ring stage: 8 (block, chunk) cells of 4 records
 // Matmul inputs that a phase of this kernel writes for a later phase (h*w, attention output, MLP
-// activations) live in a chunk-major, padded layout: [k chunk of 128][token row (MP of them)][160
-// halves], so that the activations of a stage's K range are ONE contiguous run (one bulk copy; a
-// copy costs 60-150 cycles to issue whatever its size) whose rows are already padded for
-// conflict-free fragment loads (320-byte pitch).
-constexpr int kXRowH = 160;                   // halves per padded row of one chunk
+// activations) live in a chunk-major layout: [k chunk of 128][token row (MP of them)][128 halves], so that the
+// activations of a stage's K range are ONE contiguous run (one bulk copy).  Inside a row the sixteen 16-byte
+// units are swizzled, unit u of token row r sits at u ^ ((r & 1) << 2): the fragment loads of a quarter warp (rows
+// g and g + 1, four units each) then hit eight different bank groups without any padding.
+constexpr int kXRowH = 128;                   // halves per row of one chunk
 constexpr int kXRow = kXRowH * 2;             // bytes
+constexpr int kStageBytes = 57344;            // one ring stage (every row count)
 constexpr int kMaxLayers = 128;               // layer pointer table kept in shared memory (64 bytes per layer)
 constexpr int kLtabBytes = kMaxLayers * 64;
 constexpr int kScratch = 36864;               // shared scratch for the K-part reduction of a tile
@@ -147,8 +148,7 @@ struct FwdParams {
 template <int MT>
 struct Geo {
     static constexpr int MP = MT * 8;
-    static constexpr int CPS_MAX = MT == 1 ? 8 : (MT == 2 ? 4 : 2);    // chunks of activations a stage can hold
-    static constexpr int STAGE = kWArea + CPS_MAX * MP * kXRow;
+    static constexpr int STAGE = kStageBytes;
     static constexpr int NST = 3;
     static constexpr int SMEM = NST * STAGE + 256 + kScratch + kLtabBytes;
 };
@@ -211,7 +211,8 @@ __device__ __forceinline__ bool fwd_wait(uint32_t bar, uint32_t parity) {
 }
 
 __device__ __forceinline__ size_t xt_index(int tok, int n, int mp) {
-    return ((size_t)(n >> 7) * mp + tok) * kXRowH + (n & 127);
+    const int k = n & 127;
+    return ((size_t)(n >> 7) * mp + tok) * kXRowH + ((((k >> 3) ^ ((tok & 1) << 2)) << 3) | (k & 7));
 }
 
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;\n" ::: "memory"); }
@@ -809,7 +810,7 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
                         uint4 xb[MT];
 #pragma unroll
                         for (int mt = 0; mt < MT; mt++)
-                            xb[mt] = *reinterpret_cast<const uint4*>(xrow + mt * 8 * kXRow + j * 64);
+                            xb[mt] = *reinterpret_cast<const uint4*>(xrow + mt * 8 * kXRow + ((j ^ (g & 1)) << 6));
 #pragma unroll
                         for (int s = 0; s < S; s++) {
                             const __half2 p0 = u32_as_h2((j < 2) ? sb[s][0].x : sb[s][0].y);   // {scale, bias}
@@ -1822,9 +1823,8 @@ __device__ __forceinline__ void attn_merge(const FwdParams& p, Ctx& c, const ADe
             }
         }
         const float inv = denom > 0.f ? 1.f / denom : 0.f;
-        __half* orow = p.attn + xt_index(m, head * HD, p.mp);
 #pragma unroll
-        for (int cc = 0; cc < CPT; cc++) orow[lane + 32 * cc] = __float2half_rn(acc[cc] * inv);
+        for (int cc = 0; cc < CPT; cc++) p.attn[xt_index(m, head * HD + lane + 32 * cc, p.mp)] = __float2half_rn(acc[cc] * inv);
     }
 }
 
@@ -2052,7 +2052,7 @@ PhasePlan make_plan(int N, int K, int grid, int mt, bool dual, int which, bool h
     const int nchunks = K / kChunkK;
     const int tiles = (N + 15) / 16;
     const int nmat = dual ? 2 : 1;
-    const int stage_bytes = kWArea + (mt == 1 ? 8 : (mt == 2 ? 4 : 2)) * mt * 8 * kXRow;   // Geo<MT>::STAGE
+    const int stage_bytes = kStageBytes;
     const double t_rec = 0.19 * (mt == 1 ? 0.85 : (mt == 2 ? 1.0 : (mt == 3 ? 1.3 : 1.6)));
     PhasePlan best{};
     double best_cost = 1e30;

@@ -289,10 +289,10 @@ class Model:
         self.logits = torch.zeros(MAX_ROWS, args.vocab_size, **f16)
         self._attn_ws = None
         self._attn_ws_rows = 0
-        # matmul inputs of the fused forward, chunk-major padded: [width/128][rows <= 32][160]
-        self.hw = torch.zeros(H // 128 * MAX_ROWS * 160 if H % 128 == 0 else 0, **f16)      # h * norm weight
-        self.xt_attn = torch.zeros(self.nq // 128 * MAX_ROWS * 160 if self.nq % 128 == 0 else 0, **f16)
-        self.xt_act = torch.zeros(args.intermediate_size // 128 * MAX_ROWS * 160
+        # matmul inputs of the fused forward, chunk-major padded: [width/128][rows <= 32][128], 16-byte units swizzled by the row parity
+        self.hw = torch.zeros(H // 128 * MAX_ROWS * 128 if H % 128 == 0 else 0, **f16)      # h * norm weight
+        self.xt_attn = torch.zeros(self.nq // 128 * MAX_ROWS * 128 if self.nq % 128 == 0 else 0, **f16)
+        self.xt_act = torch.zeros(args.intermediate_size // 128 * MAX_ROWS * 128
                                   if args.intermediate_size % 128 == 0 else 0, **f16)
         self.fused = True                                # one persistent kernel per pass when possible
         self._fwd_ws = None
