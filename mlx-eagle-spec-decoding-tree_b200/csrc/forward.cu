@@ -2045,9 +2045,10 @@ const PlanOverride* plan_override(int which) {
 // a record costs a warp ~0.19 us (two warps per scheduler), the first stage lands ~1.1 us after the barrier,
 // every further generation of the three-stage ring another ~1 us unless the arithmetic hides it, adding the
 // K-parts through shared memory 0.4 us, a split through global memory (partial sums out, ticket, partial sums
-// in) ~3 us on the last CTA; an SM takes ~55 KB per us through its ring (weights from HBM and activations from
-// L2 together), which is what keeps wide-K phases on split-K: without it every CTA re-reads all of x.
-constexpr double kRingBytesPerUs = 55e3;
+// in) 1.4 to 4 us on the last CTA, growing with the partial slab (token rows x tiles) and the splits; an SM takes ~45 KB per
+// us through its ring (weights from HBM and activations from L2 together), which is what keeps wide-K phases on
+// split-K: without it every CTA re-reads all of x.
+constexpr double kRingBytesPerUs = 45e3;
 PhasePlan make_plan(int N, int K, int grid, int mt, bool dual, int which, bool hinted = true) {
     const int nchunks = K / kChunkK;
     const int tiles = (N + 15) / 16;
@@ -2082,7 +2083,7 @@ PhasePlan make_plan(int N, int K, int grid, int mt, bool dual, int which, bool h
             const double refill = ((stages + 2) / 3 - 1) * 1.0;
             const double stream = (double)per_split * (nmat * tpi * kRec + mt * 8 * kXRow) / kRingBytesPerUs;
             const double cost = rounds * (1.1 + std::max(std::max(compute, refill), stream) + 0.02 * stages + (kw > 1 ? 0.4 : 0.0) +
-                                          (splits > 1 ? 3.0 : 0.0) + 0.8);
+                                          (splits > 1 ? 1.0 + 0.08 * mt * tpi + 0.12 * splits : 0.0) + 0.8);
             if (cost < best_cost - 1e-9) {
                 best_cost = cost;
                 best.row_items = row_items; best.splits = splits; best.chunks_per_split = per_split; best.kw = kw; best.cps = cps;
