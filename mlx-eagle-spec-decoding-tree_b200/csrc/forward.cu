@@ -2043,7 +2043,7 @@ const PlanOverride* plan_override(int which) {
 // items (few tiles) therefore take many chunks per stage, and a K of a few thousand is wholly in flight when
 // the barrier before the phase opens.  The cost model is in microseconds, fitted to phase timelines on B200:
 // a record costs a warp ~0.19 us (two warps per scheduler), the first stage lands ~1.1 us after the barrier,
-// every further generation of the three-stage ring another ~1 us unless the arithmetic hides it, adding the
+// every further generation of the three-stage ring adds ~0.5 us that the arithmetic does not hide, adding the
 // K-parts through shared memory 0.4 us, a split through global memory (partial sums out, ticket, partial sums
 // in) 1.4 to 4 us on the last CTA, growing with the partial slab (token rows x tiles) and the splits; an SM takes ~45 KB per
 // us through its ring (weights from HBM and activations from L2 together), which is what keeps wide-K phases on
@@ -2082,7 +2082,7 @@ PhasePlan make_plan(int N, int K, int grid, int mt, bool dual, int which, bool h
             const double compute = rec_per_warp * t_rec;
             const double refill = ((stages + 2) / 3 - 1) * 1.0;
             const double stream = (double)per_split * (nmat * tpi * kRec + mt * 8 * kXRow) / kRingBytesPerUs;
-            const double cost = rounds * (1.1 + std::max(std::max(compute, refill), stream) + 0.02 * stages + (kw > 1 ? 0.4 : 0.0) +
+            const double cost = rounds * (1.1 + std::max(compute, stream) + 0.5 * refill + 0.02 * stages + (kw > 1 ? 0.4 : 0.0) +
                                           (splits > 1 ? 1.0 + 0.08 * mt * tpi + 0.12 * splits : 0.0) + 0.8);
             if (cost < best_cost - 1e-9) {
                 best_cost = cost;
