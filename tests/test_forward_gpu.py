@@ -133,7 +133,9 @@ def test_fused_pass_equals_per_op_kernels_at_benchmark_shapes(be, cuda, name, la
         assert torch.isfinite(a).all()
         _close(a.numpy(), b.numpy(), 2.0 ** -6, 2e-2)
     # the row-0 logits of the tree pass and the one-row pass agree up to the fp32 summation order
-    _close(outs[True][1][0].numpy(), outs[True][2].numpy(), 2.0 ** -8, 4e-3)
+    # (different row counts take different work splits; through full-width layers a hidden state can move by one fp16
+    # unit, which at logits of magnitude 4..8 is 3.9e-3: two such units as the absolute term)
+    _close(outs[True][1][0].numpy(), outs[True][2].numpy(), 2.0 ** -8, 8e-3)
 
 
 def test_forward_rejects_bad_descriptors(be, pair):
