@@ -408,6 +408,13 @@ int b200_tree_accept_sample(int T, int V, const void* logits, uint32_t* row_max,
                             const int* draft_tokens, const int* mask_index, double temperature, int* ctl, int* y,
                             int* accept_rows, int* out_tokens, int* step_log, void* workspace, size_t workspace_bytes,
                             void* stream);
+/* One draw from softmax(logits_row / temperature) with the same integer arithmetic and generator (draw number `counter`
+ * of the stream `seed`): the first token of a request in sampling mode (the reference takes it greedily,
+ * mlx_eagle.py:536-538).  logits_row [V] fp16; row_max / row_sum: one word each, zero on entry and on exit; workspace as
+ * for b200_tree_accept_sample; out_token: device int. */
+int b200_sample_token(const void* logits_row, int V, double temperature, unsigned int seed, unsigned int counter,
+                      uint32_t* row_max, unsigned long long* row_sum, void* workspace, size_t workspace_bytes,
+                      int* out_token, void* stream);
 /* b200_logits_rowstats with the logits divided by `temperature` before the exponential. */
 int b200_logits_rowstats_temp(const void* logits, int R, int V, uint32_t* row_max, unsigned long long* row_sum,
                               double temperature, void* stream);

@@ -102,6 +102,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.b200_tree_accept_sample_workspace_bytes.argtypes = [i32]
     l.b200_tree_accept_sample.restype = i32
     l.b200_tree_accept_sample.argtypes = [i32, i32, vp, vp, vp, vp, vp, ctypes.c_double, vp, vp, vp, vp, vp, vp, sz, vp]
+    l.b200_sample_token.restype = i32
+    l.b200_sample_token.argtypes = [vp, i32, ctypes.c_double, ctypes.c_uint, ctypes.c_uint, vp, vp, vp, sz, vp, vp]
     l.b200_logits_rowstats_temp.restype = i32
     l.b200_logits_rowstats_temp.argtypes = [vp, i32, i32, vp, vp, ctypes.c_double, vp]
     l.b200_forward_plan_hint.restype = None

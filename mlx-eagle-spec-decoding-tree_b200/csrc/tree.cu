@@ -600,7 +600,23 @@ struct SampleParams {
     int* step_log;
     SampleState* state;
     unsigned long long* chunk_sums;     // [ceil(V / kStatChunk)]
+    int* out_token;                     // non-null: a plain draw from row 0 (the first token of a request); the token
+                                        //   goes here and the step's bookkeeping is skipped
+    unsigned int seed, counter;         // ... with this draw
 };
+
+// A plain draw from one row: the state the bonus kernels expect, without a tree walk.
+__global__ void sample_init_kernel(const SampleParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    if (threadIdx.x != 0) return;
+    p.state->node = 0;
+    p.state->nremoved = 0;
+    p.state->accept = 0;
+    p.state->rem_total = p.row_sum[0];
+    p.state->u = rand40(p.seed, p.counter);
+    for (int j = 0; j < kK; j++) p.state->removed[j] = -1;
+}
 
 // The acceptance walk, by one thread (at most 7 levels of at most 8 children).
 __global__ void tree_accept_sample_kernel(const SampleParams p) {
@@ -721,7 +737,8 @@ __global__ void __launch_bounds__(256) bonus_pick_kernel(const SampleParams p) {
             cum += s_mass[i];
         }
         if (bonus < 0) bonus = begin + max(lastpos, 0);     // (unreachable when the sums are consistent)
-        commit_step(p.ctl, p.y, p.out_tokens, p.step_log, accept, 0, bonus);
+        if (p.out_token != nullptr) *p.out_token = bonus;
+        else commit_step(p.ctl, p.y, p.out_tokens, p.step_log, accept, 0, bonus);
     }
     __syncthreads();
     if ((int)threadIdx.x <= p.T) {                          // the statistics buffers start every use at zero
@@ -905,6 +922,27 @@ int b200_tree_accept_sample(int T, int V, const void* logits, uint32_t* row_max,
     p.chunk_sums = reinterpret_cast<unsigned long long*>(static_cast<char*>(workspace) + 128);
     const int nchunks = (V + b200::kStatChunk - 1) / b200::kStatChunk;
     b200::launch_kernel(b200::tree_accept_sample_kernel, dim3(1), dim3(32), 0, st, p);
+    b200::launch_kernel(b200::bonus_chunk_sums_kernel, dim3(nchunks), dim3(256), 0, st, p);
+    b200::launch_kernel(b200::bonus_pick_kernel, dim3(1), dim3(256), 0, st, p);
+    return b200::check_launch();
+}
+
+int b200_sample_token(const void* logits_row, int V, double temperature, unsigned int seed, unsigned int counter,
+                      uint32_t* row_max, unsigned long long* row_sum, void* workspace, size_t workspace_bytes,
+                      int* out_token, void* stream) {
+    if (V < 1 || !logits_row || !row_max || !row_sum || !workspace || !out_token || !(temperature > 0.0)) return B200_EINVAL;
+    if (workspace_bytes < b200_tree_accept_sample_workspace_bytes(V)) return B200_EWORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return B200_EALIGN;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = b200_logits_rowstats_temp(logits_row, 1, V, row_max, row_sum, temperature, stream);
+    if (rc != B200_OK) return rc;
+    b200::SampleParams p{};
+    p.T = 0; p.V = V; p.logits = static_cast<const __half*>(logits_row); p.row_max = row_max; p.row_sum = row_sum;
+    p.temp = temperature; p.out_token = out_token; p.seed = seed; p.counter = counter;
+    p.state = static_cast<b200::SampleState*>(workspace);
+    p.chunk_sums = reinterpret_cast<unsigned long long*>(static_cast<char*>(workspace) + 128);
+    const int nchunks = (V + b200::kStatChunk - 1) / b200::kStatChunk;
+    b200::launch_kernel(b200::sample_init_kernel, dim3(1), dim3(32), 0, st, p);
     b200::launch_kernel(b200::bonus_chunk_sums_kernel, dim3(nchunks), dim3(256), 0, st, p);
     b200::launch_kernel(b200::bonus_pick_kernel, dim3(1), dim3(256), 0, st, p);
     return b200::check_launch();

@@ -49,8 +49,8 @@ class SpecDecoder:
             raise _lib.B200Error("verify_num_tokens must be <= 31 and <= pool size (README: 7, 15, 23 or 31)")
         self.base, self.draft = base_model, draft_model
         self.depth, self.T = depth, T
-        # temperature > 0: speculative sampling instead of greedy acceptance (b200_tree_accept_sample); the reference
-        # is greedy only (README.md:9).  The first token (from the prompt's logits) stays greedy.
+        # temperature > 0: speculative sampling instead of greedy acceptance (b200_tree_accept_sample), the first
+        # token drawn from the prompt's last logits (b200_sample_token); the reference is greedy only (README.md:9).
         self.temperature, self.seed = float(temperature), int(seed)
         if self.temperature > 0.0 and base_model.tp is not None:
             raise _lib.B200Error("sampling acceptance needs the whole vocabulary on one GPU (no tensor-parallel target)")
@@ -108,7 +108,20 @@ class SpecDecoder:
         self.draft_cache.offset = 0
         self.draft(prompt[None], cache=self.draft_cache, logits_last_only=True)
         logits = self.base(prompt[None], cache=self.base_cache, logits_last_only=True)
-        first = self.base.greedy_token(logits[0, -1])
+        draws = 0
+        if self.temperature > 0.0:
+            # sampling mode: the first token is a draw from the prompt's last logits (draw 0 of the stream)
+            self.row_max.zero_()
+            self.row_sum.zero_()
+            tok = torch.zeros(1, dtype=torch.int32, device=self.device)
+            row = logits[0, -1].contiguous()
+            _lib.check(_lib.lib().b200_sample_token(
+                _lib.ptr(row), self.base.args.vocab_size, self.temperature, self.seed & 0xFFFFFFFF, 0,
+                _lib.ptr(self.row_max), _lib.ptr(self.row_sum), _lib.ptr(self.sample_ws), self.sample_ws.numel(),
+                _lib.ptr(tok), _lib.stream_ptr(self.device)), "b200_sample_token")
+            first, draws = int(tok), 1
+        else:
+            first = self.base.greedy_token(logits[0, -1])
         self.ctl.zero_()
         host = torch.zeros(16, dtype=torch.int32)
         host[CTL_BASE_LEN] = n
@@ -117,7 +130,7 @@ class SpecDecoder:
         host[CTL_LOG_CAP] = self.max_steps
         host[CTL_EOS] = 0 if eos_token_id is None else int(eos_token_id) + 1
         host[CTL_SEED] = ((self.seed + 0x80000000) % (1 << 32)) - 0x80000000       # the 32-bit pattern of the seed
-        host[CTL_DRAW] = 0
+        host[CTL_DRAW] = draws
         if eos_token_id is not None and first == int(eos_token_id):
             host[CTL_DONE], host[CTL_STOP_N] = 1, 0
         self.ctl.copy_(host)

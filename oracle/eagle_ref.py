@@ -73,8 +73,8 @@ def generate_step(prompt, base_model: OracleModel, draft_model: OracleModel, pre
     prompt ingestion (``mlx_eagle.py:541``).  ``eos_token_id`` / ``clip`` are the two stop rules the
     product adds to the reference loop (stop after the first end-of-sequence token; cut to exactly
     ``max_tokens``), restated here so the GPU loop can be checked against them.  ``temperature > 0`` switches the
-    acceptance from greedy to speculative sampling (``tree_ref.evaluate_posterior_sample``; the first token, taken
-    from the prompt's logits, stays greedy) with the random stream ``seed``."""
+    acceptance from greedy to speculative sampling (``tree_ref.evaluate_posterior_sample``; the first token is a draw
+    from the prompt's last logits, ``tree_ref.sample_token``) with the random stream ``seed``."""
     y = np.asarray(prompt).reshape(-1)
     rows = cache_rows or (y.size + max_tokens + 8 * (depth + 2) + verify_num_tokens + 128)
     base_cache = make_prompt_cache(base_model, rows)
@@ -85,14 +85,17 @@ def generate_step(prompt, base_model: OracleModel, draft_model: OracleModel, pre
         y = y[prefill_step_size:]
     draft_model(y, draft_cache)
     base_logits = base_model(y, base_cache)
-    y = np.array([int(tr.first_argmax(base_logits[-1].astype(np.float32)))])
+    if temperature > 0.0:
+        y = np.array([tr.sample_token(base_logits[-1], temperature, seed, 0)])
+    else:
+        y = np.array([int(tr.first_argmax(base_logits[-1].astype(np.float32)))])
     tokens = [int(y[0])]
     n, accept_length, accept_lengths = 0, 0, []
     tic = time.perf_counter()
     steps = 0
     finish = "steps"
     stop_n = 0 if (eos_token_id is not None and tokens[0] == eos_token_id) else None
-    draw = 0
+    draw = 1 if temperature > 0.0 else 0                    # the first token took draw 0
     for _ in range(N):
         if n >= max_tokens or stop_n is not None:
             break

@@ -235,6 +235,16 @@ def node_masses(logits_row: np.ndarray, temperature: float) -> np.ndarray:
     return exp_fixed((x - x.max()) / np.float64(temperature))
 
 
+def sample_token(logits_row: np.ndarray, temperature: float, seed: int, counter: int) -> int:
+    """One draw from softmax(logits_row / temperature): the token whose cumulative mass (token order) first exceeds
+    rand40(seed, counter) * total / 2^40."""
+    e = node_masses(logits_row, temperature)
+    total = int(e.sum(dtype=np.int64))
+    target = (rand40(seed, counter) * total) >> 40
+    cum = np.cumsum(e.astype(object))
+    return int(np.searchsorted(np.asarray(cum, dtype=object), target, side="right"))
+
+
 def evaluate_posterior_sample(node_logits: np.ndarray, draft_tokens: np.ndarray, mask_index: np.ndarray,
                               temperature: float, seed: int, draw: int):
     """Walk the verify tree from the root: a node's children (ascending node index) are accepted with probability

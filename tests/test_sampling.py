@@ -117,8 +117,10 @@ def test_gpu_sampling_generation_in_lock_step_with_the_restatement(be, cuda):
     accepted = []
     for temp, seed, d in ((0.8, 5, draft), (1.2, 9, base)):
         dec = be.SpecDecoder(base, d, 3, 15, cache_rows=512, temperature=temp, seed=seed)
-        dec.prefill(prompt)
-        draw = 0
+        first = dec.prefill(prompt)
+        plogits = base(prompt[None].to(torch.int32), cache=base.make_cache(512), logits_last_only=True)[0, -1]
+        assert first == tr.sample_token(plogits.float().cpu().numpy().astype(np.float16), temp, seed, 0)
+        draw = 1                                               # the first token took draw 0
         for _ in range(12):
             dec._draft_tree()
             logits = dec._finalize_and_verify().float().cpu().numpy().astype(np.float16)
@@ -139,6 +141,28 @@ def test_gpu_sampling_generation_in_lock_step_with_the_restatement(be, cuda):
                           temperature=0.9, seed=3)
     g = be.generate_step(prompt, base, draft, depth=3, verify_num_tokens=15, max_tokens=30, N=30, verbose=False)
     assert s1["tokens"] == s2["tokens"] and s1["tokens"] != g["tokens"]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("V", [1000, 151936])
+def test_first_token_draw_equals_the_restatement(be, cuda, V):
+    lib, p = be._lib.lib(), be._lib.ptr
+    rng = np.random.default_rng(V)
+    ws = torch.zeros(lib.b200_tree_accept_sample_workspace_bytes(V), dtype=torch.uint8, device=cuda)
+    row_max = torch.zeros(32, dtype=torch.int32, device=cuda)
+    row_sum = torch.zeros(32, dtype=torch.int64, device=cuda)
+    tok = torch.zeros(1, dtype=torch.int32, device=cuda)
+    seen = set()
+    for trial in range(10):
+        logits = (rng.normal(size=V) * 3).astype(np.float16)
+        seed, counter, temp = int(rng.integers(0, 2 ** 31)), int(rng.integers(0, 50)), float(rng.choice([0.6, 1.0, 1.5]))
+        assert lib.b200_sample_token(p(torch.from_numpy(logits).to(cuda)), V, temp, seed, counter, p(row_max), p(row_sum),
+                                     p(ws), ws.numel(), p(tok), be._lib.stream_ptr(cuda)) == 0
+        torch.cuda.synchronize()
+        assert int(tok) == tr.sample_token(logits, temp, seed, counter)
+        assert not row_max.any() and not row_sum.any()
+        seen.add(int(tok))
+    assert len(seen) >= 5
 
 
 @pytest.mark.gpu
