@@ -367,7 +367,8 @@ class BatchSpecDecoder:
     verify tokens, 4 at 7."""
 
     def __init__(self, base_model: Model, draft_model: Model, depth: int, verify_num_tokens: int, cache_rows: int,
-                 requests: int, max_out_tokens: int = 4096, max_steps: int = 4096):
+                 requests: int, max_out_tokens: int = 4096, max_steps: int = 4096, temperature: float = 0.0,
+                 seed: int = 0):
         R, T = int(requests), verify_num_tokens
         if not (1 <= R <= MAX_REQUESTS) or R * (T + 1) > MAX_ROWS or R * K > MAX_ROWS:
             raise _lib.B200Error("requests x (verify_num_tokens + 1) rows must fit one 32-row pass")
@@ -381,8 +382,10 @@ class BatchSpecDecoder:
         self.sel_rows = torch.zeros(R, dtype=torch.int32, device=self.device)
         self.slots: List[SpecDecoder] = []
         for r in range(R):
+            # (sampling acceptance: request r draws from the stream seed + r)
             s = SpecDecoder(base_model, draft_model, depth, T, cache_rows, max_out_tokens, max_steps,
-                            base_cache=self.base_cache.slabs[r], draft_cache=self.draft_cache.slabs[r], req=r)
+                            base_cache=self.base_cache.slabs[r], draft_cache=self.draft_cache.slabs[r], req=r,
+                            temperature=temperature, seed=seed + r)
             s.ctl = self.ctl[r]                       # one device array for all requests: one read-back per step
             s.sel_row = self.sel_rows[r:r + 1]
             self.slots.append(s)

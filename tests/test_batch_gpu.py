@@ -146,3 +146,17 @@ def test_bad_batch_shapes_are_rejected(be, cuda, models):
     long_cache = base.make_batch_cache(4096, 2)                                                       # single-phase attention only
     with pytest.raises(be._lib.B200Error):
         base.forward_device(16, long_cache, 0, 8, requests=2)
+
+
+def test_batched_sampling_is_reproducible_per_seed(be, cuda, models):
+    args, base, draft, _ = models
+    rng = np.random.default_rng(8)
+    prompts = [torch.from_numpy(rng.integers(0, args.vocab_size, n)) for n in (14, 22)]
+    outs = []
+    for seed in (3, 3, 4):
+        dec = be.BatchSpecDecoder(base, draft, depth=3, verify_num_tokens=15, cache_rows=512, requests=2,
+                                  max_out_tokens=512, max_steps=128, temperature=0.9, seed=seed)
+        dec.warmup()
+        outs.append([r["tokens"] for r in dec.generate(prompts, max_tokens=24, N=40)])
+    assert outs[0] == outs[1] and outs[0] != outs[2]
+    assert all(len(t) >= 25 for t in outs[0])
