@@ -449,13 +449,21 @@ def tensor_parallel_numbers(torch, dist, be, workload, rank, world, dev, K, warm
     torch.cuda.synchronize()
     nccl_sec = n0e.elapsed_time(n1e) / 1e3 / 5
     base.fused = True
+    # the same pass in the pull form of the exchange (every GPU reads the peers' partial products after the barrier)
+    chosen = base.tp_two_shot
+    base.tp.reset_exchange()
+    base.tp_two_shot = 4
+    _, pull_sec = forward_roofline(torch, base, dec.base_cache, verify + 1, prefix_now, reps=10)
+    base.check_fused_error()
+    base.tp.reset_exchange()
+    base.tp_two_shot = chosen
 
-    t = torch.tensor([sec, e2e_sec, fsec, nccl_sec, dsec], dtype=torch.float64, device=dev)
+    t = torch.tensor([sec, e2e_sec, fsec, nccl_sec, dsec, pull_sec], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    sec, e2e_sec, fsec, nccl_sec, dsec = (float(v) for v in t)
+    sec, e2e_sec, fsec, nccl_sec, dsec, pull_sec = (float(v) for v in t)
     step_bytes = base.linear_weight_bytes() + (depth + 1) * draft.linear_weight_bytes()
     out = dict(tname=tname, dname=dname, prompt_len=prompt_len, depth=depth, verify=verify, sec=sec, produced=produced,
-               mean_accept=mean_accept, clocks=clocks, res=res, e2e_sec=e2e_sec, alg=alg, fsec=fsec, nccl_sec=nccl_sec,
+               mean_accept=mean_accept, clocks=clocks, res=res, e2e_sec=e2e_sec, alg=alg, fsec=fsec, nccl_sec=nccl_sec, pull_sec=pull_sec,
                dsec=dsec, step_bytes=step_bytes, prefix_now=prefix_now, launches=dec.kernel_launches_per_step * K,
                head_dim=tshape.head_dim, draft_mode="layers cut across the GPUs, whole vocabulary projection" if shard_draft
                else "replicated")
@@ -499,6 +507,7 @@ def run_tensor_parallel(args, rank, world, local_rank):
                        "weight_bytes_per_step_per_gpu": r["step_bytes"],
                        "step_weight_stream_frac_of_peak": r["step_bytes"] / (sec / K) / 1e9 / peak,
                        "target_pass_ms": {"persistent_kernel_peer_memory_allreduce": 1e3 * r["fsec"],
+                                          "persistent_kernel_pull_form_of_the_exchange": 1e3 * r["pull_sec"],
                                           "per_op_kernels_nccl_allreduce_eager": 1e3 * r["nccl_sec"]},
                        "draft_pass_ms": 1e3 * r["dsec"], "draft": r["draft_mode"]},
             "clocks": r["clocks"],
@@ -935,6 +944,7 @@ def main():
                   "tokens_per_second": r["produced"] / r["sec"], "ms_per_step": 1e3 * r["sec"] / 20, "steps": 20,
                   "mean_accept_length": r["mean_accept"],
                   "target_pass_ms": {"persistent_kernel_peer_memory_allreduce": 1e3 * r["fsec"],
+                                     "persistent_kernel_pull_form_of_the_exchange": 1e3 * r["pull_sec"],
                                      "per_op_kernels_nccl_allreduce_eager": 1e3 * r["nccl_sec"]},
                   "draft_pass_ms": 1e3 * r["dsec"], "draft": r["draft_mode"]}
         except Exception as e:                             # the attachment must not take the headline down with it

@@ -275,11 +275,12 @@ typedef struct b200_forward_desc {
      * embedding and the norms are whole.  tp_peers[r] is rank r's exchange buffer
      * (b200_forward_tp_buffer_bytes(hidden) bytes, zero before the first launch, 16-byte aligned) as
      * mapped into this process: peer-accessible device memory, e.g. a CUDA IPC or symmetric-memory
-     * mapping.  o_proj and down_proj leave fp32 partial products in the GPU's own buffer; every CTA then
+     * mapping.  o_proj and down_proj store their fp32 partial products into their rank's slot of every
+     * GPU's buffer (or, in the pull form, leave them in the GPU's own buffer); every CTA then
      * adds one to an arrival counter in every GPU's buffer (remote atomics) and waits (bounded; error
      * code 12 in the workspace's error word on timeout) until its own GPU's counter shows all CTAs of all
-     * GPUs; then every GPU adds all partial products in rank order with plain loads over NVLink, so
-     * every GPU holds bit-identical hidden states.  The running count of
+     * GPUs; then every GPU adds all partial products in rank order (from its own memory; in the pull
+     * form with plain loads over NVLink), so every GPU holds bit-identical hidden states.  The running count of
      * exchanges lives in the buffer (flags only grow), so a launch can be replayed from a CUDA graph.
      * Every rank must launch the same sequence of passes; the kernels of one pass run concurrently,
      * one per GPU, never two ranks on one GPU.  After an error code 12 the buffers of all ranks must
@@ -295,12 +296,20 @@ typedef struct b200_forward_desc {
                                  * fp16 exponent field in 1..10 (2^-14 <= |scale| < 2^-4, never zero or subnormal): the
                                  * kernel then expands the nibbles with a shorter instruction sequence that gives the
                                  * same bits.  0 is always safe. */
-    int tp_two_shot;            /* exchange of the row-parallel layers: 0 = every GPU reads all ranks' partial products
-                                 * in full (one all-GPU barrier per exchange; the default: fastest measured at 2 and 4
-                                 * GPUs); 1 = two-step form: each GPU reduces its slice of the columns and stores the
-                                 * result to every GPU (a second all-GPU barrier; needs hidden % (16 * tp_world) == 0).
-                                 * Same bits either way.  The same value on every rank; zero the exchange buffers when
-                                 * switching. */
+    int tp_two_shot;            /* exchange of the row-parallel layers (o_proj, down_proj); the same value on every rank,
+                                 * the same bits whichever form runs; zero the exchange buffers when switching.
+                                 * 0 = the library's choice (the push form).
+                                 * 3 = push form: every GPU stores its partial products into its slot of EVERY GPU's
+                                 * buffer while the matmul phase runs (posted stores over NVLink); after one all-GPU
+                                 * barrier each GPU adds up the slots in its own memory, so no load crosses NVLink.
+                                 * 4 = pull form: every GPU keeps its partial products in its own buffer and, after the
+                                 * all-GPU barrier, reads all ranks' products in full over NVLink.
+                                 * 2 = the pull form behind a hierarchical all-GPU barrier: the CTAs of a GPU meet on a
+                                 * local counter and only the last one adds to the peers' counters (7 remote atomics per
+                                 * exchange and GPU at 8 GPUs instead of 148 x 7).
+                                 * 1 = two-step form: each GPU reduces its slice of the columns (pulled) and stores the
+                                 * result to every GPU (a second all-GPU barrier; needs hidden % (16 * tp_world) == 0,
+                                 * else the pull form runs). */
     int requests;               /* 0 or 1: one request.  2..4: the M rows are `requests` groups of M / requests rows, one
                                  * group per request, so that several requests share every weight read (no counterpart in
                                  * the reference, which decodes one request).  Request r then has its own committed length

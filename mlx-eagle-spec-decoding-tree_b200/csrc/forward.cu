@@ -133,6 +133,8 @@ struct FwdParams {
     // The count of exchanges done by earlier launches lives in the buffer (flags only ever grow).
     int tp_world, tp_rank;
     int tp_two_shot;               // reduce-scatter + all-gather through the exchange buffers instead of reading every peer in full
+    int tp_hier;                   // all-GPU barrier with one remote arrival per GPU (the last CTA's) instead of one per CTA
+    int tp_push;                   // partial products are stored into every GPU's buffer as they are made; the reduce reads local memory only
     unsigned char* tp_peers[kMaxTp];
     int head_rows;                 // rows of the vocabulary projection held here (a vocabulary shard under TP)
     int attn_fused_max;            // single-phase attention while the cache spans at most this many key blocks
@@ -344,6 +346,20 @@ __device__ __forceinline__ float* tp_partial_of(const FwdParams& p, int rank, ui
 __device__ __forceinline__ float* tp_partial(const FwdParams& p, const Ctx& c) {
     return tp_partial_of(p, p.tp_rank, c.tp_seq0 + c.tpx);
 }
+// Push form: the buffer of GPU `dst` holds one slot of partial products per source rank (again two sets used in
+// turn); a GPU stores its products into its slot on every GPU, so that after the all-GPU barrier each GPU adds up
+// what lies in its own memory.
+constexpr int kTpPushMinWorld = 2;      // groups of at least this many GPUs use the push form unless told otherwise
+__device__ __forceinline__ size_t tp_push_base(const FwdParams& p) {
+    return (size_t)kTpHeader + (size_t)2 * 32 * p.H * sizeof(float) + (size_t)2 * 32 * p.H * sizeof(__half);
+}
+__device__ __forceinline__ float* tp_push_of(const FwdParams& p, int dst, int src, uint32_t x) {
+    return reinterpret_cast<float*>(p.tp_peers[dst] + tp_push_base(p)) + ((size_t)(x & 1u) * kMaxTp + src) * 32 * p.H;
+}
+// Where rank `r`'s partial products of exchange x are read from by this GPU.
+__device__ __forceinline__ const float* tp_source_of(const FwdParams& p, int r, uint32_t x) {
+    return p.tp_push ? tp_push_of(p, p.tp_rank, r, x) : tp_partial_of(p, r, x);
+}
 __device__ __forceinline__ float4 ld_sys_f4(const float* q) {
     float4 v;
     asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];\n"
@@ -352,10 +368,10 @@ __device__ __forceinline__ float4 ld_sys_f4(const float* q) {
 }
 
 // Barrier over all CTAs of all GPUs of the group.  Thread 0 of every CTA makes the CTA's writes visible
-// system-wide; then, with the two-step exchange, it takes a ticket on its own GPU's CTA
-// counter, and the CTA that takes the last ticket adds one to the GPU-level arrival counter in every GPU's
-// exchange buffer (its own included, release at system scope): ONE remote atomic per peer and barrier instead of
-// one per CTA; with the one-step exchange every CTA adds one to every GPU's counter itself.  Every CTA then waits
+// system-wide; then, in the hierarchical form (always with the two-step exchange, on request with the one-step
+// exchange), it takes a ticket on its own GPU's CTA counter, and the CTA that takes the last ticket adds one to the
+// GPU-level arrival counter in every GPU's exchange buffer (its own included, release at system scope): ONE remote
+// atomic per peer and barrier instead of one per CTA; otherwise every CTA adds one to every GPU's counter itself.  Every CTA then waits
 // (bounded) until its own GPU's counter shows all arrivals.  `nbar` = all-GPU barriers completed since
 // the buffers were last zeroed (the same on every GPU); counters only grow (compared modulo 2^32).
 __device__ void tp_all_barrier(const FwdParams& p, Ctx& c, uint32_t nbar) {
@@ -371,8 +387,8 @@ __device__ void tp_all_barrier(const FwdParams& p, Ctx& c, uint32_t nbar) {
         fence_proxy_async_all();
         unsigned char* own = p.tp_peers[p.tp_rank];
         unsigned target;
-        if (p.tp_two_shot) {
-            // two-step exchange: one remote atomic per GPU and barrier (the last CTA's), not one per CTA
+        if (p.tp_hier) {
+            // one remote atomic per GPU and barrier (the last CTA's), not one per CTA
             const unsigned ticket = atomicAdd(reinterpret_cast<unsigned*>(own + kTpFwdLocal), 1u);
             if (ticket + 1u == (nbar + 1u) * gridDim.x) {      // the last CTA of this GPU: tell every GPU
                 __threadfence_system();                        // the other CTAs' writes, ordered before their tickets
@@ -384,7 +400,7 @@ __device__ void tp_all_barrier(const FwdParams& p, Ctx& c, uint32_t nbar) {
             }
             target = (nbar + 1u) * (unsigned)p.tp_world;
         } else {
-            // one-step exchange: every CTA adds one to every GPU's counter directly (one hop less on the critical path)
+            // every CTA adds one to every GPU's counter directly (one hop less on the critical path)
             for (int r = 0; r < p.tp_world; r++) {
                 const int q = (p.tp_rank + r) % p.tp_world;
                 unsigned* cnt = reinterpret_cast<unsigned*>(p.tp_peers[q] + kTpFwdArrive);
@@ -408,7 +424,8 @@ __device__ void tp_all_barrier(const FwdParams& p, Ctx& c, uint32_t nbar) {
 }
 
 // The all-reduce of a row-parallel layer, after the all-GPU barrier that follows the partial products: all
-// consumer threads add the ranks' partial products in rank order (plain loads, the peers' over NVLink), add
+// consumer threads add the ranks' partial products in rank order (pull form: plain loads, the peers' over NVLink;
+// push form: the slots the ranks stored into this GPU's buffer during the matmul phase), add
 // the residual and write h, h*w and the sums of squares exactly like the single-GPU epilogue.
 // (Not inlined: its registers, one pair of loads per rank, stay out of the matmul phases' allocation.)
 __device__ __noinline__ void tp_reduce_rows(const FwdParams& p, const __half* wn, uint32_t xchg) {
@@ -430,7 +447,7 @@ __device__ __noinline__ void tp_reduce_rows(const FwdParams& p, const __half* wn
 #pragma unroll
             for (int r = 0; r < kMaxTp; r++)
                 if (r < p.tp_world && valid[j])
-                    u[j][r] = ld_sys_f4(tp_partial_of(p, r, xchg) + (size_t)tok[j] * p.H + n0[j]);
+                    u[j][r] = ld_sys_f4(tp_source_of(p, r, xchg) + (size_t)tok[j] * p.H + n0[j]);
         }
 #pragma unroll
         for (int j = 0; j < 2; j++) {
@@ -464,7 +481,7 @@ __device__ __noinline__ void tp_reduce_rows(const FwdParams& p, const __half* wn
     }
 }
 
-// Two-step variant, on request (the one-step form makes every GPU read (N-1) whole partial buffers per exchange;
+// Two-step variant, on request (the pull form makes every GPU read (N-1) whole partial buffers per exchange;
 // measured on 4 GPUs the second all-GPU barrier of this form costs more than the reads it saves, so it is not the default).
 // Shot one: GPU r adds, for ITS slice of H / N columns only, the partial products of all ranks (rank order) and
 // the residual, and stores the fp16 result into the gather area of every GPU's exchange buffer (plain stores,
@@ -953,7 +970,14 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
                     }
                     __align__(16) __half out[8];
                     if (TP && EPI == EPI_TP) {
-                        if (valid) {
+                        if (valid && p.tp_push) {
+                            const size_t at = (size_t)tok * d.N + n0;
+                            for (int r = 1; r <= p.tp_world; r++) {                   // the peers first, this GPU last
+                                float* dst = tp_push_of(p, (p.tp_rank + r) % p.tp_world, p.tp_rank, c.tp_seq0 + c.tpx) + at;
+                                *reinterpret_cast<float4*>(dst) = make_float4(a0[0], a0[1], a0[2], a0[3]);
+                                *reinterpret_cast<float4*>(dst + 4) = make_float4(a0[4], a0[5], a0[6], a0[7]);
+                            }
+                        } else if (valid) {
                             float* dst = tp_partial(p, c) + (size_t)tok * d.N + n0;
                             *reinterpret_cast<float4*>(dst) = make_float4(a0[0], a0[1], a0[2], a0[3]);
                             *reinterpret_cast<float4*>(dst + 4) = make_float4(a0[4], a0[5], a0[6], a0[7]);
@@ -1005,14 +1029,18 @@ __device__ __forceinline__ void qmm_consume(const FwdParams& p, Ctx& c, const QD
             // ---- direct epilogue from the registers of the tile's first warp
             const int nbase = tile_global * 16 + g;
             if (TP && EPI == EPI_TP) {
-                float* dst = tp_partial(p, c);
+                const int ndst = p.tp_push ? p.tp_world : 1;
+                for (int r = 1; r <= ndst; r++) {                                     // push form: the peers first, this GPU last
+                    float* dst = p.tp_push ? tp_push_of(p, (p.tp_rank + r) % p.tp_world, p.tp_rank, c.tp_seq0 + c.tpx)
+                                           : tp_partial(p, c);
 #pragma unroll
-                for (int mt = 0; mt < MT; mt++) {
+                    for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int tok = mt * 8 + 2 * t + (i & 1);
-                        const int nn = nbase + ((i >> 1) ? 8 : 0);
-                        if (tok < d.xrows && nn < d.N) dst[(size_t)tok * d.N + nn] = acc[0][mt][i];
+                        for (int i = 0; i < 4; i++) {
+                            const int tok = mt * 8 + 2 * t + (i & 1);
+                            const int nn = nbase + ((i >> 1) ? 8 : 0);
+                            if (tok < d.xrows && nn < d.N) dst[(size_t)tok * d.N + nn] = acc[0][mt][i];
+                        }
                     }
                 }
             } else if (EPI == EPI_RESID) {
@@ -2258,7 +2286,8 @@ using namespace b200;
 
 size_t b200_forward_tp_buffer_bytes(int hidden) {
     if (hidden < 128 || (hidden % 128) != 0) return 0;
-    return (size_t)kTpHeader + (size_t)2 * 32 * hidden * sizeof(float) + (size_t)2 * 32 * hidden * sizeof(__half);
+    return (size_t)kTpHeader + (size_t)2 * 32 * hidden * sizeof(float) + (size_t)2 * 32 * hidden * sizeof(__half) +
+           (size_t)2 * kMaxTp * 32 * hidden * sizeof(float);       // partial products, gather area, push slots
 }
 
 void b200_forward_plan_hint(const char* spec) { parse_plan_hint(spec); }
@@ -2324,7 +2353,9 @@ int b200_forward(const b200_forward_desc* d, void* stream) {
     p.tp_world = d->tp_world > 1 ? d->tp_world : 1;
     p.tp_rank = d->tp_world > 1 ? d->tp_rank : 0;
     p.tp_two_shot = (p.tp_world > 1 && (p.H % (16 * p.tp_world)) == 0 &&
-                     d->tp_two_shot > 0) ? 1 : 0;
+                     d->tp_two_shot == 1) ? 1 : 0;
+    p.tp_hier = (p.tp_world > 1 && (p.tp_two_shot || d->tp_two_shot == 2)) ? 1 : 0;
+    p.tp_push = (p.tp_world > 1 && (d->tp_two_shot == 3 || (d->tp_two_shot == 0 && p.tp_world >= kTpPushMinWorld))) ? 1 : 0;
     if (p.tp_world > 1) {
         for (int r = 0; r < p.tp_world; r++) {
             if (!d->tp_peers[r]) return B200_EINVAL;

@@ -1,7 +1,8 @@
 // Layout of a tensor-parallel exchange buffer (one per GPU, mapped by every process of the group).
 // Header: flag lines and counters of the two users, then the key slots of the argmax combine; after the
 // header two buffers of [32][hidden] fp32 partial products, used in turn, then two gather areas of [32][hidden] fp16
-// (the reduced hidden states of the two-shot exchange), used in turn.
+// (the reduced hidden states of the two-shot exchange), used in turn, then two sets, used in turn, of kMaxTp slots
+// of [32][hidden] fp32: slot r of a set holds the partial products rank r stored here (push form of the exchange).
 #pragma once
 
 namespace b200 {

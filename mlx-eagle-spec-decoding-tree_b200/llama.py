@@ -306,7 +306,7 @@ class Model:
         self.phase_mask = 0                              # profiling: run only some phase kinds (0 = all)
         self.grid_ctas = 0                               # CTAs of the persistent kernel (0 = one per SM)
         self.fast_dequant = True                         # allow the short nibble expansion when every scale permits it
-        self.tp_two_shot = 0                             # tensor-parallel exchange: 0 one-step (default), 1 two-step form
+        self.tp_two_shot = 0                             # tensor-parallel exchange: 0 library's choice (push), 1 two-step, 2 pull behind a hierarchical barrier, 3 push, 4 pull
         self.prefill_large_m = True                      # prompts: 128 rows per weight read through b200_qmm_umma
         self._pf = None                                  # buffers of that path, made on first use
         self.prefill_graphs = True                       # replay full 128-row chunks from a CUDA graph

@@ -63,6 +63,22 @@ def _rank(rank, world, port, out):
     two = shard(prompt[None], cache=shard.make_cache(128))[0].float().cpu()
     shard.check_fused_error()
     assert torch.equal(two, fused)
+    # ... and the one-step exchange behind the hierarchical all-GPU barrier (one remote arrival per GPU)
+    shard.tp.reset_exchange()
+    shard.tp_two_shot = 2
+    hier = shard(prompt[None], cache=shard.make_cache(128))[0].float().cpu()
+    shard.check_fused_error()
+    assert torch.equal(hier, fused)
+    # ... and the push form (partial products stored into every GPU's buffer, the reduce reads local memory only)
+    # and the pull form (every GPU reads the peers' partial products after the barrier), each forced
+    for form in (3, 4):
+        shard.tp.reset_exchange()
+        shard.tp_two_shot = form
+        forced = shard(prompt[None], cache=shard.make_cache(128))[0].float().cpu()
+        shard.check_fused_error()
+        assert torch.equal(forced, fused)
+    shard.tp.reset_exchange()
+    shard.tp_two_shot = 0
     # a tensor-parallel DRAFT next to the tensor-parallel target: layers cut, vocabulary projection whole
     draft2 = be.Model.random_init(args, seed=12, device=dev, gen_device="cpu")
     draft2.norm.mul_(8.0)
