@@ -43,6 +43,14 @@ def test_workspace_query(be):
     assert be.qmm_kernel.workspace_bytes(16, 3584, 18944) > 4096     # narrow, deep layer: split-K
 
 
+def test_exchange_buffer_size_query(be):
+    lib = be._lib.lib()
+    # header, two buffers of partial products (fp32), two gather areas (fp16), two sets of 8 push slots (fp32), 32 rows each
+    for hidden in (896, 3584, 8192):
+        assert lib.b200_forward_tp_buffer_bytes(hidden) == 4096 + 32 * hidden * (2 * 4 + 2 * 2 + 2 * 8 * 4)
+    assert lib.b200_forward_tp_buffer_bytes(100) == 0 and lib.b200_forward_tp_buffer_bytes(0) == 0
+
+
 def test_missing_library_fails_loudly(be, monkeypatch):
     import pytest
     monkeypatch.setattr(be._lib, "_lib", None)
